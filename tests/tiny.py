@@ -1,0 +1,44 @@
+"""Tiny configurations for the tests.  A and B differ in every size and option: layers,
+width, heads and groups, head width, feed-forward width (200 is no multiple of 128),
+vocabulary, rope base, eps, tied or untied head, spread of the weights.  C adds sliding
+layers (window 24) between full ones, with sizes of its own."""
+from __future__ import annotations
+
+import tempfile
+from pathlib import Path
+
+import torch
+
+from tiny_llm_infer_b200.config import Qwen3Config
+from tiny_llm_infer_b200.weights import write_random_model
+
+FULL, SLIDING = "full_attention", "sliding_attention"
+
+TINY_A = dict(cfg=Qwen3Config(hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                              num_attention_heads=4, num_key_value_heads=2, head_dim=16, vocab_size=256,
+                              max_position_embeddings=512, rms_norm_eps=1e-6, rope_theta=1e4,
+                              tie_word_embeddings=True, layer_types=(FULL,) * 2),
+              seed=0, std=0.02, norm_range=(0.8, 1.2), page_size=16)
+TINY_B = dict(cfg=Qwen3Config(hidden_size=96, intermediate_size=200, num_hidden_layers=3,
+                              num_attention_heads=6, num_key_value_heads=2, head_dim=32, vocab_size=384,
+                              max_position_embeddings=512, rms_norm_eps=1e-5, rope_theta=1e6,
+                              tie_word_embeddings=False, layer_types=(FULL,) * 3),
+              seed=1, std=0.05, norm_range=(0.5, 1.5), page_size=8)
+TINY_C = dict(cfg=Qwen3Config(hidden_size=80, intermediate_size=176, num_hidden_layers=4,
+                              num_attention_heads=5, num_key_value_heads=5, head_dim=48, vocab_size=300,
+                              max_position_embeddings=512, rms_norm_eps=1e-5, rope_theta=5e4,
+                              tie_word_embeddings=False, sliding_window=24,
+                              layer_types=(SLIDING, FULL, SLIDING, SLIDING)),
+              seed=2, std=0.08, norm_range=(0.6, 1.4), page_size=16)
+TINIES = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+
+
+def make_folder(tiny, folder=None, dtype=torch.bfloat16, shards=1) -> Path:
+    folder = Path(folder or tempfile.mkdtemp(prefix="tllm_tiny_"))
+    return write_random_model(folder, tiny["cfg"], tiny["seed"], tiny["std"], tiny["norm_range"],
+                              dtype=dtype, shards=shards)
+
+
+def prompt(seed: int, length: int, vocab: int):
+    g = torch.Generator().manual_seed(1000 + seed)
+    return torch.randint(0, vocab, (length,), generator=g).tolist()

@@ -1,0 +1,64 @@
+// Shared device helpers of the sm_100a kernels: storage-type conversion, warp and
+// block reductions, error reporting of the C entry points.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tllm {
+
+// Storage types are selected at run time by these codes in every C entry point.
+enum DType : int { kF32 = 0, kBF16 = 1 };
+
+using bf16 = __nv_bfloat16;
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<bf16>(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; `scratch` holds 32 floats.  Every thread
+// gets the result.  The order of the additions depends on the block size only.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();  // scratch may still be read from an earlier call
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = (lane < nwarps) ? scratch[lane] : 0.0f;
+    return warp_sum(r);
+}
+
+// Host side: the last error text of this thread's most recent failing entry point.
+void set_error(const char* fmt, ...);
+
+// Result of an entry point: 0 on success, a cudaError_t (> 0) from the launch, or
+// -1 for an argument the kernel refuses (text in tllm_last_error()).
+int finish_launch(const char* what);
+
+#define TLLM_REQUIRE(cond, ...)                 \
+    do {                                        \
+        if (!(cond)) {                          \
+            ::tllm::set_error(__VA_ARGS__);     \
+            return -1;                          \
+        }                                       \
+    } while (0)
+
+}  // namespace tllm

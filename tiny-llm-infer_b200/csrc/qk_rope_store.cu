@@ -1,0 +1,133 @@
+// Per-head RMSNorm of queries and keys, rotary position encoding and the write of keys
+// and values into the paged cache, in one pass over the fused q|k|v projection.
+//
+// The reference runs these as four launches per layer: head norm of q and of k
+// (model/src/qwen3_paged_batch.cpp:160-177 through rmsnorm_kernel_cuda.cu:8-39), the
+// rotate-half rotation with angle pos * theta^(-2i/hd) (rope_kernel_cuda.cu:228-261,
+// table built at :186-198) and the scatter into the cache (paged_attention_cuda.cu:48-68).
+// Here one warp owns one head of one token: it reads the head once, and what it
+// writes is the rotated query (to `q_out`) or the rotated key / the value (to their
+// page).  Norm sum, angle, sine, cosine and the rotation are float32.
+//
+// Cache layout of one layer: [page][0 = keys, 1 = values][kv head][slot in page][head_dim].
+#include "common.cuh"
+
+namespace tllm {
+
+constexpr int kFlagNorm = 1;   // RMSNorm q and k heads with q_gain / k_gain
+constexpr int kFlagRope = 2;   // rotate q and k
+constexpr int kFlagStore = 4;  // write k and v into the cache
+constexpr int kFlagQOut = 8;   // write q to q_out
+constexpr int kFlagKvOut = 16; // write the processed k and v back into qkv (in place)
+
+constexpr int kMaxHeadDim = 512;
+
+template <typename T, typename TG>
+__global__ void qk_norm_rope_store_kernel(
+    T* __restrict__ qkv, const TG* __restrict__ q_gain, const TG* __restrict__ k_gain, float eps,
+    const float* __restrict__ inv_freq, int rotary_dim, const int* __restrict__ positions,
+    const int* __restrict__ token_slot, const int* __restrict__ block_table, int max_pages,
+    T* __restrict__ cache, int page_size, T* __restrict__ q_out, int tokens, int q_heads,
+    int kv_heads, int head_dim, int flags) {
+    extern __shared__ float smem[];  // one head vector per warp
+    const int warps_per_block = blockDim.x >> 5;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads_total = q_heads + 2 * kv_heads;
+    const long long unit = (long long)blockIdx.x * warps_per_block + warp;
+    if (unit >= (long long)tokens * heads_total) return;
+    const int t = (int)(unit / heads_total);
+    const int head = (int)(unit - (long long)t * heads_total);
+    const int slot = token_slot[t];
+    if (slot < 0) return;  // padding row
+    const int pos = positions[t];
+
+    T* src = qkv + (size_t)t * heads_total * head_dim + (size_t)head * head_dim;
+    float* vec = smem + warp * head_dim;
+    const bool is_q = head < q_heads;
+    const bool is_k = !is_q && head < q_heads + kv_heads;
+
+    float sumsq = 0.0f;
+    for (int e = lane; e < head_dim; e += 32) {
+        const float v = to_f32<T>(src[e]);
+        vec[e] = v;
+        sumsq += v * v;
+    }
+    if ((is_q || is_k) && (flags & kFlagNorm)) {
+        sumsq = warp_sum(sumsq);
+        const float scale = 1.0f / sqrtf(sumsq / (float)head_dim + eps);
+        const TG* gain = is_q ? q_gain : k_gain;
+        for (int e = lane; e < head_dim; e += 32) vec[e] = to_f32<TG>(gain[e]) * vec[e] * scale;
+    }
+    __syncwarp();
+
+    T* dst = nullptr;
+    if (is_q) {
+        if (flags & kFlagQOut) dst = q_out + (size_t)t * q_heads * head_dim + (size_t)head * head_dim;
+    } else if (flags & kFlagStore) {
+        const int kvh = is_k ? head - q_heads : head - q_heads - kv_heads;
+        const int page = block_table[(size_t)slot * max_pages + pos / page_size];
+        if (page >= 0) {
+            dst = cache + ((((size_t)page * 2 + (is_k ? 0 : 1)) * kv_heads + kvh) * page_size +
+                           (pos % page_size)) * head_dim;
+        }
+    }
+    T* dst2 = (!is_q && (flags & kFlagKvOut)) ? src : nullptr;
+    if (!dst && !dst2) return;
+
+    const int half = rotary_dim >> 1;
+    const bool rotate = (is_q || is_k) && (flags & kFlagRope) && half > 0;
+    for (int e = lane; e < head_dim; e += 32) {
+        float v = vec[e];
+        if (rotate && e < rotary_dim) {
+            // pair (i, i + half): x'_i = x_i cos a - x_{i+half} sin a; x'_{i+half} = x_i sin a + x_{i+half} cos a
+            const int i = e < half ? e : e - half;
+            float s, c;
+            sincosf((float)pos * inv_freq[i], &s, &c);
+            v = e < half ? vec[e] * c - vec[e + half] * s : vec[e - half] * s + vec[e] * c;
+        }
+        if (dst) dst[e] = from_f32<T>(v);
+        if (dst2) dst2[e] = from_f32<T>(v);
+    }
+}
+
+}  // namespace tllm
+
+using namespace tllm;
+
+extern "C" int tllm_qk_norm_rope_store(
+    void* qkv, const void* q_gain, const void* k_gain, int gain_dtype, float eps,
+    const float* inv_freq, int rotary_dim, const int* positions, const int* token_slot,
+    const int* block_table, int max_pages, void* cache, int page_size, void* q_out, int dtype,
+    int tokens, int q_heads, int kv_heads, int head_dim, int flags, cudaStream_t stream) {
+    TLLM_REQUIRE(tokens >= 0 && q_heads > 0 && kv_heads > 0, "qk_norm_rope_store: bad sizes");
+    TLLM_REQUIRE(head_dim > 0 && head_dim <= kMaxHeadDim,
+                 "qk_norm_rope_store: head_dim %d outside 1..%d", head_dim, kMaxHeadDim);
+    TLLM_REQUIRE(rotary_dim >= 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0,
+                 "qk_norm_rope_store: rotary_dim %d must be even and at most head_dim %d",
+                 rotary_dim, head_dim);
+    TLLM_REQUIRE(!(flags & kFlagRope) || inv_freq != nullptr, "qk_norm_rope_store: rotation without frequencies");
+    TLLM_REQUIRE(!(flags & kFlagNorm) || (q_gain && k_gain), "qk_norm_rope_store: norm without gains");
+    TLLM_REQUIRE(!(flags & kFlagStore) || (cache && block_table && page_size > 0 && max_pages > 0),
+                 "qk_norm_rope_store: store without cache");
+    TLLM_REQUIRE(!(flags & kFlagQOut) || q_out, "qk_norm_rope_store: no query output");
+    TLLM_REQUIRE(gain_dtype == kBF16 || gain_dtype == kF32, "qk_norm_rope_store: unknown gain dtype");
+    if (tokens == 0) return 0;
+    const int warps = 4, block = warps * 32;
+    const long long units = (long long)tokens * (q_heads + 2 * kv_heads);
+    const int grid = (int)((units + warps - 1) / warps);
+    const size_t smem = (size_t)warps * head_dim * sizeof(float);
+#define LAUNCH(T, TG)                                                                            \
+    qk_norm_rope_store_kernel<T, TG><<<grid, block, smem, stream>>>(                             \
+        (T*)qkv, (const TG*)q_gain, (const TG*)k_gain, eps, inv_freq, rotary_dim, positions,     \
+        token_slot, block_table, max_pages, (T*)cache, page_size, (T*)q_out, tokens, q_heads,    \
+        kv_heads, head_dim, flags)
+    if (dtype == kBF16) {
+        if (gain_dtype == kBF16) LAUNCH(bf16, bf16); else LAUNCH(bf16, float);
+    } else if (dtype == kF32) {
+        if (gain_dtype == kBF16) LAUNCH(float, bf16); else LAUNCH(float, float);
+    } else {
+        TLLM_REQUIRE(false, "qk_norm_rope_store: unknown dtype %d", dtype);
+    }
+#undef LAUNCH
+    return finish_launch("qk_norm_rope_store");
+}

@@ -1,0 +1,169 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+``ModelRunner.step`` runs only the tokens it is given, as one batch, from the cache that
+earlier steps left, and returns the logits at the wanted places.  Portions of prompts
+and single decoded tokens may share a step and a prompt may be cut anywhere.  It is what
+generation, the scheduler and trace replay all call; there is no second forward pass.
+
+Reference counterpart: ``Qwen3Model::forward_paged_batch`` and the adapter in front of it
+(model/src/qwen3_paged_batch.cpp:44-366, engine/src/qwen3_runner.cpp:11-54).
+"""
+from __future__ import annotations
+
+from pathlib import Path
+from typing import Dict, Hashable, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .. import models as _models  # noqa: F401  (registers the architectures)
+from ..cache.manager import CacheManager
+from ..config.base import ModelConfig, describe_model, load_config
+from ..models.model import Model, expected_tensors
+from ..weights.loader import load_weights
+from ..weights.random_init import random_tensors
+from .batch import Segment, StepContext, StepEntry
+
+DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
+          "fp32": torch.float32}
+
+
+class StepError(ValueError):
+    pass
+
+
+def strict_float32() -> None:
+    """Switch the library's reduced-precision matrix modes off (process-wide)."""
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    torch.set_float32_matmul_precision("highest")
+    if hasattr(torch.backends.cuda.matmul, "allow_bf16_reduced_precision_reduction"):
+        torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+
+
+def load_model(model_path, dtype: torch.dtype, device) -> Tuple[Model, ModelConfig]:
+    """Model folder (config.json + safetensors) -> model with weights on ``device``."""
+    config = load_config(model_path)
+    desc = describe_model(config)
+    model = Model(desc, dtype, device)
+    expected, ignorable = expected_tensors(desc)
+    model.load(load_weights(model_path, expected, dtype, device, ignorable))
+    return model, config
+
+
+def random_model(config: ModelConfig, seed: int, dtype: torch.dtype, device, std: float = 0.02,
+                 norm_range=(0.8, 1.2)) -> Model:
+    """Random-weights mode without a folder: tensors are drawn on ``device``, part by part."""
+    config.validate()
+    desc = describe_model(config)
+    model = Model(desc, dtype, device)
+    expected, _ = expected_tensors(desc)
+
+    class _Lazy(dict):
+        def pop(self, name):
+            from ..weights.random_init import random_tensor
+            store = torch.bfloat16 if dtype == torch.bfloat16 else torch.float32
+            t = random_tensor(name, expected[name], seed, std, norm_range, torch.bfloat16, device)
+            return t.to(store)
+
+    model.load(_Lazy())
+    return model
+
+
+class ModelRunner:
+    def __init__(self, model: Model, cache: CacheManager, max_batch_tokens: int = 8192):
+        self.model, self.cache = model, cache
+        self.device = model.device
+        self.vocab = model.desc.vocab_size
+        self.max_batch_tokens = int(max_batch_tokens)
+        self.is_cuda = torch.device(self.device).type == "cuda"
+        strict_float32()
+        n = self.max_batch_tokens
+        # one packed int32 buffer per step: token ids | positions | slots | wanted rows | segments
+        self._host = torch.empty(8 * n, dtype=torch.int32)
+        if self.is_cuda:
+            self._host = self._host.pin_memory()
+        self._dev = torch.empty(8 * n, dtype=torch.int32, device=self.device)
+        self._uploaded: Optional[torch.cuda.Event] = None
+
+    # ------------------------------------------------------------------ requests
+    def release(self, request: Hashable) -> None:
+        if self.cache.has(request):
+            self.cache.release(request)
+
+    # ------------------------------------------------------------------ the step
+    def build_context(self, entries: Sequence[StepEntry]) -> Tuple[StepContext, List[Tuple[Hashable, int]]]:
+        """Reserve pages, lay the rows out, upload them.  Returns the context and, per
+        entry, (request, length after this step) to commit once the step has run."""
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        seen = set()
+        total = wanted = 0
+        for e in entries:
+            if e.request in seen:
+                raise StepError(f"request {e.request!r} appears twice in one step")
+            seen.add(e.request)
+            if len(e.tokens) == 0:
+                raise StepError(f"request {e.request!r} brings no tokens")
+            total += len(e.tokens)
+            wanted += len(e.want)
+        if total > self.max_batch_tokens:
+            raise StepError(f"{total} tokens exceed the step's limit of {self.max_batch_tokens}")
+        host = self._host.numpy()
+        o_ids, o_pos, o_slot, o_want = 0, total, 2 * total, 3 * total
+        o_seg = o_want + wanted
+        used = o_seg + 4 * len(entries)
+        if self._uploaded is not None:
+            self._uploaded.synchronize()
+        segments: List[Segment] = []
+        commits: List[Tuple[Hashable, int]] = []
+        row = n_want = max_ctx = max_seg = 0
+        for e in entries:
+            if not self.cache.has(e.request):
+                self.cache.admit(e.request)
+            toks = np.asarray(e.tokens, dtype=np.int64)
+            if toks.min() < 0 or toks.max() >= self.vocab:
+                raise StepError(f"request {e.request!r}: token id outside [0, {self.vocab})")
+            n = len(toks)
+            pos0 = self.cache.computed(e.request)
+            self.cache.reserve(e.request, pos0 + n)
+            slot = self.cache.slot_of(e.request)
+            host[o_ids + row:o_ids + row + n] = toks
+            host[o_pos + row:o_pos + row + n] = np.arange(pos0, pos0 + n)
+            host[o_slot + row:o_slot + row + n] = slot
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise StepError(f"request {e.request!r}: wanted place {w} outside its {n} tokens")
+                host[o_want + n_want] = row + w
+                n_want += 1
+            s = len(segments)
+            host[o_seg + 4 * s:o_seg + 4 * s + 4] = (slot, row, n, pos0)
+            segments.append(Segment(e.request, slot, row, n, pos0))
+            commits.append((e.request, pos0 + n))
+            row += n
+            max_ctx = max(max_ctx, pos0 + n)
+            max_seg = max(max_seg, n)
+        self.cache.sync()
+        if self.is_cuda:
+            self._dev[:used].copy_(self._host[:used], non_blocking=True)
+            self._uploaded = torch.cuda.Event()
+            self._uploaded.record()
+        else:
+            self._dev[:used].copy_(self._host[:used])
+        d = self._dev
+        ctx = StepContext(
+            tokens=row, token_ids=d[o_ids:o_ids + row], positions=d[o_pos:o_pos + row],
+            token_slot=d[o_slot:o_slot + row], want_rows=d[o_want:o_want + n_want],
+            segments=segments, seg_info=d[o_seg:o_seg + 4 * len(segments)].view(-1, 4),
+            decode_only=(max_seg == 1), max_context=max_ctx, max_segment=max_seg)
+        return ctx, commits
+
+    @torch.no_grad()
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Run one batch; logits [wanted, vocab] float32 on the device, in the order of
+        the entries and of their ``want`` lists."""
+        ctx, commits = self.build_context(entries)
+        logits = self.model.forward(ctx, self.cache)
+        for request, length in commits:
+            self.cache.commit(request, length)
+        return logits

@@ -1,0 +1,218 @@
+"""Python face of the hand-written CUDA kernels (``csrc/*.cu``) and of the library matrix
+product.  Every function here works on CUDA tensors on the current stream and has no
+other implementation: if the kernel library cannot be built or loaded, the first call
+raises ``KernelLibraryError``.
+
+The matrix product is the library's (cuBLAS through ``torch.mm``), as in the reference,
+which calls ``cublasHgemm`` for every projection with more than one row
+(kernels/src/matmul_kernel_cuda.cu:83-91); in float32 mode it runs with the
+reduced-precision matrix modes switched off.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from ..csrc import build as _build
+
+F32, BF16 = 0, 1
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+# flags of qk_norm_rope_store (csrc/qk_rope_store.cu)
+QK_NORM, QK_ROPE, QK_STORE, QK_QOUT, QK_KVOUT = 1, 2, 4, 8, 16
+
+
+class KernelLibraryError(RuntimeError):
+    pass
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def lib():
+    """The loaded kernel library (built on first use)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    try:
+        path = _build.library_path()
+    except Exception as exc:  # BuildError and anything the toolchain throws
+        raise KernelLibraryError(f"the CUDA kernel library is not available: {exc}") from exc
+    try:
+        handle = ctypes.CDLL(str(path))
+    except OSError as exc:
+        raise KernelLibraryError(f"cannot load {path}: {exc}") from exc
+    _declare(handle)
+    _lib = handle
+    return handle
+
+
+def _declare(h) -> None:
+    vp, i32, f32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+    h.tllm_last_error.restype = ctypes.c_char_p
+    h.tllm_last_error.argtypes = []
+    sigs = {
+        "tllm_embedding": [vp, vp, i32, vp, i32, i32, i32, vp],
+        "tllm_add_rmsnorm": [vp, vp, vp, i32, f32, vp, i32, vp, i32, i32, vp],
+        "tllm_swiglu": [vp, vp, i32, i32, i32, vp],
+        "tllm_cast": [vp, i32, vp, i32, i64, vp],
+        "tllm_qk_norm_rope_store": [vp, vp, vp, i32, f32, vp, i32, vp, vp, vp, i32, vp, i32, vp,
+                                    i32, i32, i32, i32, i32, i32, vp],
+        "tllm_paged_attention_general": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32,
+                                         i32, f32, vp, vp],
+        "tllm_sample": [vp, i32, i32, i64, vp, vp, vp, vp],
+    }
+    for name, args in sigs.items():
+        fn = getattr(h, name)
+        fn.argtypes = args
+        fn.restype = i32
+    h.tllm_uniform_of.argtypes = [ctypes.c_ulonglong, i32]
+    h.tllm_uniform_of.restype = f32
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise KernelError(f"{what}: {lib().tllm_last_error().decode(errors='replace')} (code {code})")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and (not t.is_cuda or not t.is_contiguous()):
+            raise KernelError("kernels take contiguous CUDA tensors")
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise KernelError(f"unsupported dtype {t.dtype}") from None
+
+
+# --------------------------------------------------------------------------- ops
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = table[ids[t]] as float32; rows with a negative id become zero."""
+    _cuda(ids, table, out)
+    assert ids.dtype == torch.int32 and out.dtype == torch.float32
+    vocab, hidden = table.shape
+    _check(lib().tllm_embedding(_p(ids), _p(table), _dt(table), _p(out), ids.numel(), hidden, vocab,
+                                _stream()), "embedding")
+    return out
+
+
+def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], gain: torch.Tensor, eps: float,
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """h += delta (float32 sum, written back) and out = gain * h / sqrt(mean(h^2) + eps).
+    With ``rows`` only those rows are normed, into out[0..len(rows)), and h is not written."""
+    _cuda(h, delta, gain, out, rows)
+    assert h.dtype == torch.float32
+    if delta is not None:
+        assert delta.dtype == out.dtype and delta.shape == h.shape
+    n_out = out.shape[0] if rows is None else rows.numel()
+    _check(lib().tllm_add_rmsnorm(_p(h), _p(delta), _p(gain), _dt(gain), float(eps), _p(out), _dt(out),
+                                  _p(rows), n_out, h.shape[-1], _stream()), "add_rmsnorm")
+    return out
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+    _cuda(gate_up, out)
+    tokens, two_i = gate_up.shape
+    assert out.shape == (tokens, two_i // 2) and out.dtype == gate_up.dtype
+    _check(lib().tllm_swiglu(_p(gate_up), _p(out), _dt(out), tokens, two_i // 2, _stream()), "swiglu")
+    return out
+
+
+def cast(src: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    _cuda(src)
+    if src.dtype == dtype:
+        return src
+    dst = torch.empty_like(src, dtype=dtype)
+    _check(lib().tllm_cast(_p(src), _dt(src), _p(dst), _dt(dst), src.numel(), _stream()), "cast")
+    return dst
+
+
+def qk_norm_rope_store(qkv: torch.Tensor, q_gain, k_gain, eps: float, inv_freq, rotary_dim: int,
+                       positions: torch.Tensor, token_slot: torch.Tensor, block_table, cache,
+                       page_size: int, q_out, q_heads: int, kv_heads: int, head_dim: int,
+                       flags: int) -> None:
+    """One pass over the fused q|k|v rows [T, (q_heads + 2 kv_heads) * head_dim]: per-head
+    RMSNorm of q and k (QK_NORM), rotate-half rotation (QK_ROPE), write of k and v into
+    their page (QK_STORE), write of q to ``q_out`` (QK_QOUT), write of the processed k back
+    in place (QK_KVOUT).  Rows whose token_slot is negative are skipped."""
+    _cuda(qkv, q_gain, k_gain, inv_freq, positions, token_slot, block_table, cache, q_out)
+    tokens = qkv.shape[0]
+    assert qkv.shape[1] == (q_heads + 2 * kv_heads) * head_dim
+    gain_dt = _dt(q_gain) if q_gain is not None else F32
+    max_pages = block_table.shape[1] if block_table is not None else 0
+    if cache is not None:
+        assert cache.dtype == qkv.dtype and tuple(cache.shape[1:]) == (2, kv_heads, page_size, head_dim)
+    _check(lib().tllm_qk_norm_rope_store(
+        _p(qkv), _p(q_gain), _p(k_gain), gain_dt, float(eps), _p(inv_freq), rotary_dim,
+        _p(positions), _p(token_slot), _p(block_table), max_pages, _p(cache), page_size, _p(q_out),
+        _dt(qkv), tokens, q_heads, kv_heads, head_dim, flags, _stream()), "qk_norm_rope_store")
+
+
+def paged_attention(q: torch.Tensor, cache: torch.Tensor, positions, token_slot, block_table,
+                    page_size: int, q_heads: int, kv_heads: int, head_dim: int,
+                    window: Optional[int], scale: float, out: torch.Tensor, ctx=None) -> torch.Tensor:
+    """Attention of every row of ``q`` over the keys of its own request in the paged cache:
+    positions max(0, pos - window + 1) .. pos.  ``ctx`` (the step's context) lets faster
+    kernels see how rows group into requests; the general kernel does not need it."""
+    _cuda(q, cache, positions, token_slot, block_table, out)
+    tokens = q.shape[0]
+    assert tuple(cache.shape[1:]) == (2, kv_heads, page_size, head_dim) and cache.dtype == q.dtype
+    _check(lib().tllm_paged_attention_general(
+        _p(q), _p(cache), _p(positions), _p(token_slot), _p(block_table), block_table.shape[1],
+        page_size, _dt(q), tokens, q_heads, kv_heads, head_dim, int(window or 0), float(scale),
+        _p(out), _stream()), "paged_attention")
+    return out
+
+
+def sample(logits: torch.Tensor, params: torch.Tensor, seeds: torch.Tensor,
+           out: torch.Tensor) -> torch.Tensor:
+    """Token per row of float32 ``logits`` [S, V]: params[s] = (temperature, top_p), seeds[s]
+    an int64 key.  temperature <= 1e-6 is argmax (lowest id on ties)."""
+    _cuda(logits, params, seeds, out)
+    assert logits.dtype == torch.float32 and params.dtype == torch.float32
+    assert seeds.dtype == torch.int64 and out.dtype == torch.int32
+    rows, vocab = logits.shape
+    _check(lib().tllm_sample(_p(logits), rows, vocab, logits.stride(0), _p(params), _p(seeds),
+                             _p(out), _stream()), "sample")
+    return out
+
+
+def uniform_of(seed: int, token: int) -> float:
+    """The uniform number the sampler draws for (seed, token); for host-side checks."""
+    return float(lib().tllm_uniform_of(seed & 0xFFFFFFFFFFFFFFFF, token))
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """y[T, N] = x[T, K] . weight[N, K]^T with float32 accumulation.  A weight kept in
+    float32 is multiplied in float32 whatever the activations are stored in."""
+    if not x.is_cuda:
+        raise KernelError("linear takes CUDA tensors")
+    want = out_dtype or x.dtype
+    if weight.dtype == torch.float32:
+        if torch.backends.cuda.matmul.allow_tf32 or torch.get_float32_matmul_precision() != "highest":
+            raise KernelError("float32 products need the reduced-precision matrix modes off")
+        y = torch.mm(cast(x, torch.float32), weight.t())
+        return y if want == torch.float32 else cast(y, want)
+    if x.dtype != weight.dtype:
+        x = cast(x, weight.dtype)
+    if want == weight.dtype:
+        return torch.mm(x, weight.t())
+    return torch.mm(x, weight.t(), out_dtype=want)
