@@ -1,0 +1,300 @@
+"""Each CUDA kernel alone against a plain torch restatement of the same operation, at
+sizes other than the tiny models': widths and vocabularies that are no power of two, head
+widths in steps of 16, odd head counts and groups.  Inputs are shaped so that faults show:
+one far key that dominates, a window's edge, a page's edge, pages in scrambled order."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype, scale=1.0):
+    return (2e-5 if dtype == torch.float32 else 1.6e-2) * scale
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from tiny_llm_infer_b200 import ops as o
+    o.lib()
+    from tiny_llm_infer_b200.engine.runner import strict_float32
+    strict_float32()
+    return o
+
+
+def dev(t):
+    return t.cuda().contiguous()
+
+
+def rnd(*shape, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(*shape, generator=g, dtype=torch.float64) * scale
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("vocab,hidden", [(1000, 136), (517, 4104)])
+def test_embedding(ops, dtype, vocab, hidden):
+    table = rnd(vocab, hidden, seed=1).to(dtype)
+    ids = torch.tensor([0, vocab - 1, 5, -1, 17, 5, -1, 3], dtype=torch.int32)
+    out = torch.full((len(ids), hidden), 7.0, dtype=torch.float32, device="cuda")
+    ops.embedding(dev(ids), dev(table), out)
+    want = table.float()[ids.clamp(min=0).long()]
+    want[ids < 0] = 0
+    assert torch.equal(out.cpu(), want)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [72, 1000, 4104])
+@pytest.mark.parametrize("eps", [1e-6, 1e-2])
+def test_add_rmsnorm(ops, dtype, width, eps):
+    T = 7
+    h = rnd(T, width, seed=2, scale=3.0).float()
+    delta = rnd(T, width, seed=3).to(dtype)
+    gain = (rnd(width, seed=4) * 0.2 + 1).to(dtype)
+    v = h.double() + delta.double()
+    want = gain.double() * v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps)
+    hd = dev(h)
+    out = torch.empty((T, width), dtype=dtype, device="cuda")
+    ops.add_rmsnorm(hd, dev(delta), dev(gain), eps, out)
+    assert (hd.cpu().double() - v).abs().max() < 1e-6 * 10          # residual sum written back in float32
+    assert (out.cpu().double() - want).abs().max() < tol(dtype, want.abs().max().item())
+    # without a delta nothing is written back; with rows only those rows are normed, h untouched
+    h2 = dev(h)
+    rows = torch.tensor([5, 0, 5], dtype=torch.int32)
+    out2 = torch.empty((3, width), dtype=dtype, device="cuda")
+    ops.add_rmsnorm(h2, dev(delta), dev(gain), eps, out2, dev(rows))
+    assert torch.equal(h2.cpu(), h)
+    assert (out2.cpu().double() - want[rows.long()]).abs().max() < tol(dtype, want.abs().max().item())
+    out3 = torch.empty((T, width), dtype=dtype, device="cuda")
+    ops.add_rmsnorm(h2, None, dev(gain.float()), eps, out3)          # float32 gain with any storage
+    w3 = gain.double() * h.double() * torch.rsqrt((h.double() ** 2).mean(-1, keepdim=True) + eps)
+    assert (out3.cpu().double() - w3).abs().max() < tol(dtype, w3.abs().max().item())
+    assert torch.equal(h2.cpu(), h)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("inter", [200, 1000])
+def test_swiglu(ops, dtype, inter):
+    gu = rnd(9, 2 * inter, seed=5, scale=3.0).to(dtype)
+    out = torch.empty((9, inter), dtype=dtype, device="cuda")
+    ops.swiglu(dev(gu), out)
+    g, u = gu[:, :inter].double(), gu[:, inter:].double()
+    want = plain.silu(g) * u
+    assert (out.cpu().double() - want).abs().max() < tol(dtype, want.abs().max().item())
+
+
+def scrambled_tables(slots, max_pages, num_pages, seed):
+    """Every slot gets distinct pages in a scrambled order."""
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(num_pages, generator=g)[:slots * max_pages]
+    return perm.view(slots, max_pages).to(torch.int32)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,rot", [(6, 2, 48, 48), (5, 5, 80, 32), (8, 1, 128, 128), (3, 3, 16, 16),
+                                           (2, 1, 256, 256)])
+def test_qk_norm_rope_store(ops, dtype, nh, nkv, hd, rot):
+    T, ps, slots, max_pages = 11, 8, 3, 6
+    eps, theta = 1e-5, 5e4
+    qkv = rnd(T, (nh + 2 * nkv) * hd, seed=6, scale=2.0).to(dtype)
+    qg = (rnd(hd, seed=7) * 0.3 + 1).to(dtype)
+    kg = (rnd(hd, seed=8) * 0.3 + 1).to(dtype)
+    positions = torch.tensor([0, 1, 7, 8, 9, 15, 16, 40, 3, 47, 5], dtype=torch.int32)
+    slot = torch.tensor([0, 0, 0, 0, 1, 1, 1, 2, -1, 2, 1], dtype=torch.int32)
+    table = scrambled_tables(slots, max_pages, 20, seed=9)
+    inv_freq = (theta ** (-2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot)).float()
+    cache = torch.zeros((20, 2, nkv, ps, hd), dtype=dtype, device="cuda")
+    q_out = torch.full((T, nh * hd), 9.0, dtype=dtype, device="cuda")
+    flags = ops.QK_NORM | ops.QK_ROPE | ops.QK_STORE | ops.QK_QOUT
+    ops.qk_norm_rope_store(dev(qkv), dev(qg), dev(kg), eps, dev(inv_freq), rot, dev(positions), dev(slot),
+                           dev(table), cache, ps, q_out, nh, nkv, hd, flags)
+    x = qkv.double().view(T, nh + 2 * nkv, hd)
+    q, k, v = x[:, :nh], x[:, nh:nh + nkv], x[:, nh + nkv:]
+
+    def rope(t):      # rotate the first `rot` elements with the plain implementation's rule
+        r = plain.rotary_half(t[..., :rot], positions, theta)
+        return torch.cat([r, t[..., rot:]], -1)
+    qn = rope(plain.rms_norm(q, qg.double(), eps))
+    kn = rope(plain.rms_norm(k, kg.double(), eps))
+    scale = max(qn.abs().max().item(), 1.0)
+    cache_h, q_h = cache.cpu().double(), q_out.cpu().double().view(T, nh, hd)
+    touched = torch.zeros(20, ps, dtype=torch.bool)
+    for t in range(T):
+        if slot[t] < 0:
+            assert (q_out[t].cpu() == 9.0).all()          # padding rows are skipped
+            continue
+        assert (q_h[t] - qn[t]).abs().max() < tol(dtype, scale)
+        page, off = int(table[slot[t], positions[t] // ps]), int(positions[t] % ps)
+        touched[page, off] = True
+        assert (cache_h[page, 0, :, off] - kn[t]).abs().max() < tol(dtype, scale)
+        assert (cache_h[page, 1, :, off] - v[t]).abs().max() < tol(dtype, scale)
+    untouched = cache_h.permute(0, 3, 1, 2, 4)[~touched]
+    assert (untouched == 0).all()                        # nothing else was written
+
+
+def fill_cache(cache, table, slot, keys, vals, ps):
+    """Write keys/vals [n, nkv, hd] of one request into its pages."""
+    for j in range(keys.shape[0]):
+        page = int(table[slot, j // ps])
+        cache[page, 0, :, j % ps] = keys[j].to(cache.dtype)
+        cache[page, 1, :, j % ps] = vals[j].to(cache.dtype)
+
+
+def plain_rows(q, keys, vals, positions, window):
+    """Rows of the plain implementation's attention for queries at ``positions``."""
+    n = keys.shape[0]
+    full_q = torch.zeros((n,) + q.shape[1:], dtype=torch.float64)
+    full_q[positions] = q
+    return plain.causal_attention(full_q, keys, vals, window)[positions]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,ps,window", [
+    (6, 2, 48, 8, None), (4, 4, 16, 16, None), (8, 1, 128, 16, None), (5, 5, 80, 4, 37),
+    (32, 8, 128, 16, None), (2, 2, 256, 32, 64), (16, 8, 64, 16, None), (3, 1, 112, 64, 130)])
+def test_paged_attention_far_key_and_edges(ops, dtype, nh, nkv, hd, ps, window):
+    """One request of 300 keys.  For every query one far key dominates the softmax (its
+    score is lifted), placed at a page's edge or on the first key the window still admits;
+    the key just outside the window is made just as strong and must not count."""
+    n = 300
+    max_pages = -(-n // ps) + 1
+    table = scrambled_tables(2, max_pages, 2 * max_pages + 3, seed=11)
+    keys = rnd(n, nkv, hd, seed=12).to(dtype).double()
+    vals = rnd(n, nkv, hd, seed=13).to(dtype).double()
+    positions = torch.tensor([0, 1, ps - 1, ps, ps + 1, 37, 130, 131, 255, 256, 299])
+    q = rnd(len(positions), nh, hd, seed=14).to(dtype).double()
+    group = nh // nkv
+    for r, pos in enumerate(positions.tolist()):
+        lo = max(0, pos - window + 1) if window else 0
+        target = lo if r % 2 == 0 else (pos // ps) * ps - 1 if pos >= ps else lo   # window edge or page edge
+        target = min(max(target, lo), pos)
+        for h in range(nh):
+            q[r, h] = (keys[target, h // group] * 4.0 + q[r, h] * 0.1).to(dtype).double()
+        if window and lo > 0:
+            keys[lo - 1] = keys[target]               # as strong, but outside the window
+    scale = 1.0 / math.sqrt(hd)
+    want = plain_rows(q, keys, vals, positions, window)
+    cache = torch.zeros((2 * max_pages + 3, 2, nkv, ps, hd), dtype=dtype, device="cuda")
+    cache.normal_()                                   # stale data in every page
+    fill_cache(cache, table, 1, keys, vals, ps)
+    T = len(positions) + 2
+    qd = torch.zeros((T, nh * hd), dtype=dtype)
+    qd[1:-1] = q.reshape(len(positions), -1).to(dtype)
+    pos_d = torch.zeros(T, dtype=torch.int32)
+    pos_d[1:-1] = positions.int()
+    slot_d = torch.full((T,), -1, dtype=torch.int32)
+    slot_d[1:-1] = 1
+    out = torch.full((T, nh * hd), 5.0, dtype=dtype, device="cuda")
+    ops.paged_attention(dev(qd), cache, dev(pos_d), dev(slot_d), dev(table), ps, nh, nkv, hd, window,
+                        scale, out)
+    got = out.cpu().double()
+    assert (got[0] == 0).all() and (got[-1] == 0).all()          # padding rows give zeros
+    err = (got[1:-1].view(len(positions), nh, hd) - want).abs().max().item()
+    assert err < tol(dtype, want.abs().max().item()), err
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_paged_attention_many_requests(ops, dtype):
+    """Rows of several requests interleaved, prompt portions beside single tokens."""
+    nh, nkv, hd, ps = 6, 3, 32, 8
+    lens = [45, 9, 130, 1]
+    max_pages = 20
+    table = scrambled_tables(4, max_pages, 90, seed=21)
+    cache = torch.zeros((90, 2, nkv, ps, hd), dtype=dtype, device="cuda").normal_()
+    K = [rnd(n, nkv, hd, seed=30 + i).to(dtype).double() for i, n in enumerate(lens)]
+    V = [rnd(n, nkv, hd, seed=40 + i).to(dtype).double() for i, n in enumerate(lens)]
+    for s in range(4):
+        fill_cache(cache, table, s, K[s], V[s], ps)
+    rows = [(0, p) for p in range(30, 45)] + [(1, 8)] + [(2, p) for p in range(0, 130, 7)] + [(3, 0)]
+    q = rnd(len(rows), nh, hd, seed=50, scale=2.0).to(dtype).double()
+    out = torch.empty((len(rows), nh * hd), dtype=dtype, device="cuda")
+    ops.paged_attention(dev(q.reshape(len(rows), -1).to(dtype)), cache,
+                        dev(torch.tensor([p for _, p in rows], dtype=torch.int32)),
+                        dev(torch.tensor([s for s, _ in rows], dtype=torch.int32)), dev(table), ps,
+                        nh, nkv, hd, None, 1 / math.sqrt(hd), out)
+    got = out.cpu().double().view(len(rows), nh, hd)
+    for s in range(4):
+        idx = [i for i, (ss, _) in enumerate(rows) if ss == s]
+        pos = torch.tensor([rows[i][1] for i in idx])
+        want = plain_rows(q[idx], K[s], V[s], pos, None)
+        assert (got[idx] - want).abs().max() < tol(dtype, want.abs().max().item())
+
+
+def test_sample_greedy_ties_and_temperature(ops):
+    V = 5003
+    logits = rnd(6, V, seed=60, scale=2.0).float()
+    logits[0, 4000] = logits[0, 17] = 9.0                # tie: the lower id wins
+    logits[1, V - 1] = 12.0
+    params = torch.tensor([[0.0, 1.0], [0.0, 1.0], [0.7, 1.0], [1.3, 1.0], [0.7, 0.6], [1.0, 0.05]])
+    seeds = torch.tensor([1, 2, 3, 2 ** 62 + 12345, -5, 77], dtype=torch.int64)
+    out = torch.empty(6, dtype=torch.int32, device="cuda")
+    ops.sample(dev(logits), dev(params), dev(seeds), out)
+    got = out.cpu().tolist()
+    assert got[0] == 17 and got[1] == V - 1
+    for r in range(2, 6):
+        temp, top_p = params[r].tolist()
+        seed = int(seeds[r]) & ((1 << 64) - 1)
+        scores = plain.gumbel_scores(logits[r].numpy(), temp, seed)
+        if top_p < 1:
+            keep = plain.nucleus(logits[r].numpy(), temp, top_p)
+            assert got[r] in set(keep.tolist())
+            best = max(scores[keep])
+        else:
+            best = scores.max()
+        assert scores[got[r]] >= best - 1e-4, (r, got[r], int(np.argmax(scores)))
+    assert abs(ops.uniform_of(12345, 678) - plain.uniform_of(12345, 678)) < 1e-9
+
+
+def test_sample_distribution(ops):
+    """Frequencies of many seeds follow softmax(logits / T)."""
+    V, n, temp = 11, 4000, 0.8
+    lg = torch.tensor([0.0, 1.0, 2.0, -1.0, 0.5, 3.0, -2.0, 1.5, 0.2, 2.5, -0.5])
+    logits = lg.repeat(n, 1)
+    params = torch.tensor([[temp, 1.0]]).repeat(n, 1)
+    seeds = torch.arange(n, dtype=torch.int64) * 7919 + 13
+    out = torch.empty(n, dtype=torch.int32, device="cuda")
+    ops.sample(dev(logits), dev(params), dev(seeds), out)
+    freq = torch.bincount(out.cpu().long(), minlength=V).double() / n
+    p = torch.softmax(lg.double() / temp, 0)
+    assert (freq - p).abs().max() < 4 * math.sqrt(0.25 / n)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_linear_precision(ops, dtype):
+    """float32 products must be true float32 (a reduced-precision matrix mode would miss
+    this bound by two orders of magnitude); bfloat16 inputs accumulate in float32."""
+    x = rnd(33, 1000, seed=70).to(dtype)
+    w = rnd(200, 1000, seed=71).to(dtype)
+    want = x.double() @ w.double().T
+    got32 = ops.linear(dev(x), dev(w), out_dtype=torch.float32).cpu().double()
+    assert (got32 - want).abs().max() < (3e-4 if dtype == torch.float32 else 1e-3)
+    got = ops.linear(dev(x), dev(w)).cpu().double()
+    assert (got - want).abs().max() < tol(dtype, want.abs().max().item()) * 2
+
+
+def test_mixed_storage_linear(ops):
+    """A weight kept in float32 is multiplied in float32 under bfloat16 activations."""
+    x = rnd(5, 64, seed=72).to(torch.bfloat16)
+    w = rnd(24, 64, seed=73).float()
+    got = ops.linear(dev(x), dev(w), out_dtype=torch.float32).cpu().double()
+    assert (got - x.double() @ w.double().T).abs().max() < 1e-4
+
+
+def test_refusals(ops):
+    """Sizes a kernel does not take are refused with an error, never computed wrongly."""
+    q = torch.zeros((1, 2 * 1024), dtype=torch.bfloat16, device="cuda")
+    cache = torch.zeros((2, 2, 2, 16, 1024), dtype=torch.bfloat16, device="cuda")
+    z = torch.zeros(1, dtype=torch.int32, device="cuda")
+    table = torch.zeros((1, 2), dtype=torch.int32, device="cuda")
+    with pytest.raises(ops.KernelError, match="head_dim"):
+        ops.paged_attention(q, cache, z, z, table, 16, 2, 2, 1024, None, 1.0, torch.empty_like(q))
+    q3 = torch.zeros((1, 3 * 32), dtype=torch.bfloat16, device="cuda")
+    cache3 = torch.zeros((2, 2, 2, 16, 32), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ops.KernelError, match="heads"):
+        ops.paged_attention(q3, cache3, z, z, table, 16, 3, 2, 32, None, 1.0, torch.empty_like(q3))

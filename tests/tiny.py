@@ -42,3 +42,24 @@ def make_folder(tiny, folder=None, dtype=torch.bfloat16, shards=1) -> Path:
 def prompt(seed: int, length: int, vocab: int):
     g = torch.Generator().manual_seed(1000 + seed)
     return torch.randint(0, vocab, (length,), generator=g).tolist()
+
+
+def sharpen(folder, factor: float) -> None:
+    """Scale the q/k head-norm gains so that attention scores spread out and single keys
+    dominate: a wrong or missing key then changes the logits visibly."""
+    from safetensors import safe_open
+    from tiny_llm_infer_b200.weights import save_file
+    path = Path(folder) / "model.safetensors"
+    tensors = {}
+    with safe_open(str(path), framework="pt") as fh:
+        for name in fh.keys():
+            t = fh.get_tensor(name).clone()      # the file is rewritten below
+            if name.endswith("q_norm.weight") or name.endswith("k_norm.weight"):
+                t = (t.float() * factor).to(t.dtype)
+            tensors[name] = t
+    save_file(tensors, path)
+
+
+def requests_for(tiny, lengths=(70, 97, 130, 41, 66, 35)):
+    vocab = tiny["cfg"].vocab_size
+    return {str(i): prompt(i, n, vocab) for i, n in enumerate(lengths)}
