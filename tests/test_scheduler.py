@@ -1,0 +1,133 @@
+"""The scheduler's decisions with a fake model: decode first, budget split, one portion
+per prompt per step, rotation, what happens when pages run out, finishing."""
+import pytest
+
+from tiny_llm_infer_b200.cache import CacheManager
+from tiny_llm_infer_b200.engine.scheduler import (Scheduler, SchedulerConfig, SchedulerError, Sequence,
+                                                  Status)
+from tiny_llm_infer_b200.parts.spec import CacheSpec
+from tiny_llm_infer_b200.sampling import SamplingParams
+
+NEEDS = {0: (CacheSpec(1, 16, None), None)}
+
+
+def make(pages=16, budget=32, seqs=4, page=8):
+    cache = CacheManager(NEEDS, page, pages, seqs, 256)
+    return Scheduler(SchedulerConfig(seqs, budget, page, pages), cache), cache
+
+
+def seq(i, n, max_tokens=4, **kw):
+    return Sequence(i, list(range(n)), SamplingParams(max_tokens=max_tokens, ignore_eos=True, **kw))
+
+
+def run_step(sched, cache, token=7, eos=()):
+    """What the engine does around a step, with a model that always says ``token``."""
+    plan = sched.schedule()
+    for item in plan.sequences:                      # the step function's bookkeeping
+        assert cache.computed(item.sequence.id) == item.token_start
+        cache.reserve(item.sequence.id, item.token_start + item.token_count)
+        cache.commit(item.sequence.id, item.token_start + item.token_count)
+    sampled = [token if item.samples else -1 for item in plan.sequences]
+    done = sched.postprocess(plan, sampled, lambda t: t in eos)
+    cache.audit()
+    return plan, done
+
+
+def shape(plan):
+    return [(s.sequence.id, s.token_start, s.token_count, s.is_prefill) for s in plan.sequences]
+
+
+def test_prompts_are_cut_under_the_budget_and_rotate():
+    sched, cache = make(pages=32, budget=32)
+    for i, n in enumerate((40, 9, 70)):
+        sched.add(seq(i + 1, n))
+    plan, _ = run_step(sched, cache)
+    assert shape(plan) == [(1, 0, 32, True)] and plan.num_tokens == 32 and plan.is_prefill
+    plan, _ = run_step(sched, cache)                 # 1 went to the back: 2 and 3 come first
+    assert shape(plan) == [(2, 0, 9, True), (3, 0, 23, True)]
+    assert [s.samples for s in plan.sequences] == [True, False]
+    plan, _ = run_step(sched, cache)                 # decode of 2 first, then portions
+    assert shape(plan) == [(2, 9, 1, False), (1, 32, 8, True), (3, 23, 23, True)]
+    assert not plan.is_prefill
+    plan, _ = run_step(sched, cache)
+    assert shape(plan) == [(2, 10, 1, False), (1, 40, 1, False), (3, 46, 24, True)]
+
+
+def test_finishes_on_max_tokens_and_eos_and_frees():
+    sched, cache = make()
+    sched.add(seq(1, 5, max_tokens=2))
+    s2 = Sequence(2, [1, 2, 3], SamplingParams(max_tokens=50))
+    sched.add(s2)
+    _, done = run_step(sched, cache, token=9)
+    assert done == []
+    _, done = run_step(sched, cache, token=9)
+    assert [d.id for d in done] == [1] and done[0].completion == [9, 9] and done[0].status is Status.FINISHED
+    _, done = run_step(sched, cache, token=3, eos={3})
+    assert [d.id for d in done] == [2] and s2.completion == [9, 9, 3]
+    assert sched.is_finished() and cache.free_pages() == {None: 16} and cache.free_slots == 4
+
+
+def test_waiting_for_pages_without_preemption():
+    sched, cache = make(pages=4, budget=64)
+    sched.add(seq(1, 17, max_tokens=3))                # 3 pages
+    sched.add(seq(2, 16, max_tokens=3))                # 2 pages, 3 when it grows: must wait
+    plan, _ = run_step(sched, cache)
+    assert shape(plan) == [(1, 0, 17, True)]
+    steps = 1
+    while not sched.is_finished():
+        run_step(sched, cache)
+        steps += 1
+        assert steps < 20
+    assert sched.num_preemptions == 0
+
+
+def test_out_of_pages_preempts_the_oldest_that_cannot_grow_and_recomputes():
+    sched, cache = make(pages=4, budget=64, page=8)
+    a, b = seq(1, 15, max_tokens=6), seq(2, 15, max_tokens=6)
+    sched.add(a), sched.add(b)
+    run_step(sched, cache)                             # both prompts whole: 2 pages each
+    plan, _ = run_step(sched, cache)                   # position 15 still fits their pages
+    assert shape(plan) == [(1, 15, 1, False), (2, 15, 1, False)]
+    plan, _ = run_step(sched, cache)                   # position 16 needs a third page: none free
+    assert [s.id for s in plan.preempted] == [1] and sched.num_preemptions == 1
+    assert shape(plan) == [(2, 16, 1, False)]          # 1 gave its pages back, 2 grows into them
+    assert a.num_cached_tokens == 0 and a.status is Status.WAITING and len(a) == 17
+    done_ids = []
+    for _ in range(40):
+        if sched.is_finished():
+            break
+        plan, done = run_step(sched, cache)
+        done_ids += [d.id for d in done]
+        for s in plan.sequences:
+            if s.sequence is a and s.is_prefill:
+                assert (s.token_start, s.token_count) == (0, 17)    # its prompt and its two generated tokens again
+    assert sorted(done_ids) == [1, 2] and a.completion == [7] * 6 and b.completion == [7] * 6
+    assert cache.free_pages() == {None: 4}
+
+
+def test_prompt_larger_than_the_pool_is_an_error():
+    sched, cache = make(pages=2, page=8)
+    sched.add(seq(1, 17))
+    with pytest.raises(SchedulerError, match="more KV blocks"):
+        sched.schedule()
+
+
+def test_slots_bound_live_requests():
+    sched, cache = make(seqs=2, budget=64)
+    for i in range(3):
+        sched.add(seq(i + 1, 4, max_tokens=2))
+    plan, _ = run_step(sched, cache)
+    assert [s.sequence.id for s in plan.sequences] == [1, 2]
+    run_step(sched, cache)
+    plan, _ = run_step(sched, cache)
+    assert 3 in [s.sequence.id for s in plan.sequences]
+
+
+def test_empty_request_and_wrong_sample_count():
+    sched, cache = make()
+    with pytest.raises(ValueError):
+        sched.add(Sequence(1, [], SamplingParams()))
+    sched.add(seq(1, 3))
+    plan = sched.schedule()
+    with pytest.raises(SchedulerError, match="wrong number"):
+        sched.postprocess(plan, [], lambda t: False)

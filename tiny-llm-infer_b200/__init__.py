@@ -8,3 +8,14 @@ assembly), ``cache`` (paged keys and values, per-request state slots), ``engine`
 function, scheduler, LLMEngine), ``sampling``, ``ops`` and ``csrc`` (the CUDA kernels).
 """
 __version__ = "0.1.0"
+
+
+def __getattr__(name):
+    # the public names, resolved lazily so that importing the package stays cheap
+    if name in ("LLM", "LLMEngine", "EngineConfig", "GenerationResult", "SchedulerConfig"):
+        from . import engine
+        return getattr(engine, name)
+    if name == "SamplingParams":
+        from .sampling import SamplingParams
+        return SamplingParams
+    raise AttributeError(name)

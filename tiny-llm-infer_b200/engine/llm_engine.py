@@ -1,0 +1,231 @@
+"""``LLMEngine`` (add_request / step / generate / is_finished) and the ``LLM`` entry point.
+
+Mirrors the reference's engine (engine/include/llm_engine.h:14-56,
+engine/src/llm_engine.cpp:29-323): requests are validated on entry, a step asks the
+scheduler for a plan, flattens it into one batch (decode tokens first, then portions of
+prompts), runs the step function, samples on the device and books the result.  Prompts
+are token ids; text in and out is an optional extra through a ``tokenizers`` tokenizer.
+"""
+from __future__ import annotations
+
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence as Seq, Union
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler, draw_key
+from .batch import StepEntry
+from .runner import DTYPES, ModelRunner, load_model
+from .scheduler import BatchPlan, Scheduler, SchedulerConfig, Sequence, Status
+
+
+@dataclass
+class EngineConfig:
+    """Reference: engine/include/llm_engine.h:14-18."""
+    scheduler: SchedulerConfig = field(default_factory=SchedulerConfig)
+    max_model_len: int = 2048
+
+
+@dataclass
+class GenerationResult:
+    request_id: int
+    token_ids: List[int]
+    text: str = ""
+    prompt_len: int = 0
+    preemptions: int = 0
+
+
+@dataclass
+class EngineCounters:
+    steps: int = 0
+    prefill_tokens: int = 0
+    decode_tokens: int = 0
+    generated_tokens: int = 0
+    preemptions: int = 0
+
+
+class LLMEngine:
+    def __init__(self, runner: ModelRunner, config: EngineConfig, eos_token_ids: Seq[int] = (),
+                 detokenize=None):
+        if config.max_model_len <= 0:
+            raise ValueError("max_model_len must be positive")
+        config.scheduler.validate()
+        self.runner, self.config = runner, config
+        self.scheduler = Scheduler(config.scheduler, runner.cache)
+        self.sampler = Sampler(runner.device, config.scheduler.max_num_seqs)
+        self.eos = frozenset(int(t) for t in eos_token_ids)
+        self.detokenize = detokenize
+        self.counters = EngineCounters()
+        self._next_id = 1
+        self._lock = threading.Lock()      # add_request may come from another thread
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, prompt_tokens: Seq[int], sampling: Optional[SamplingParams] = None) -> int:
+        """Checks of the reference (engine/src/llm_engine.cpp:41-64)."""
+        sampling = sampling or SamplingParams()
+        sampling.validate()
+        if sampling.max_tokens == 0:
+            raise ValueError("max_tokens must be greater than zero.")
+        prompt = [int(t) for t in prompt_tokens]
+        if not prompt:
+            raise ValueError("A prompt must encode to at least one token.")
+        if len(prompt) > self.config.max_model_len:
+            raise ValueError("The prompt exceeds max_model_len.")
+        if sampling.max_tokens > self.config.max_model_len - len(prompt) + 1:
+            raise ValueError("The requested completion exceeds max_model_len.")
+        vocab = self.runner.vocab
+        if min(prompt) < 0 or max(prompt) >= vocab:
+            raise ValueError(f"A prompt token id is outside [0, {vocab}).")
+        with self._lock:
+            request_id = self._next_id
+            self._next_id += 1
+            self.scheduler.add(Sequence(request_id, prompt, sampling))
+        return request_id
+
+    def is_finished(self) -> bool:
+        with self._lock:
+            return self.scheduler.is_finished()
+
+    @property
+    def total_generated_tokens(self) -> int:
+        return self.counters.generated_tokens
+
+    # ------------------------------------------------------------------ one step
+    def step(self) -> List[GenerationResult]:
+        with self._lock:
+            plan = self.scheduler.schedule()
+        if not plan.sequences:
+            return []
+        entries, rows, row_of = [], [], []
+        for item in plan.sequences:
+            seq = item.sequence
+            toks = seq.tokens[item.token_start:item.token_start + item.token_count]
+            want = [item.token_count - 1] if item.samples else []
+            entries.append(StepEntry(seq.id, toks, want))
+            if item.samples:
+                rows.append((seq.sampling.temperature, seq.sampling.top_p,
+                             draw_key(seq.seed, len(seq.completion))))
+                row_of.append(len(entries) - 1)
+        logits = self.runner.step(entries)
+        tokens = self.sampler.sample(logits, rows)
+        sampled = [-1] * len(plan.sequences)
+        for idx, tok in zip(row_of, tokens):
+            sampled[idx] = tok
+        with self._lock:
+            finished = self.scheduler.postprocess(plan, sampled, lambda t: t in self.eos)
+        c = self.counters
+        c.steps += 1
+        c.generated_tokens += len(tokens)
+        c.preemptions = self.scheduler.num_preemptions
+        for item in plan.sequences:
+            if item.is_prefill:
+                c.prefill_tokens += item.token_count
+            else:
+                c.decode_tokens += item.token_count
+        out = []
+        for seq in finished:
+            ids = seq.completion
+            text = self.detokenize(ids) if self.detokenize else ""
+            out.append(GenerationResult(seq.id, ids, text, seq.prompt_len, seq.preemptions))
+        return out
+
+    def generate(self, prompts: Seq[Seq[int]], sampling: Union[SamplingParams, Seq[SamplingParams], None] = None
+                 ) -> List[GenerationResult]:
+        """All prompts to completion; results in the order of the prompts
+        (engine/src/llm_engine.cpp:250-317)."""
+        if not prompts:
+            return []
+        if not self.is_finished():
+            raise ValueError("Finish or step existing requests before calling generate.")
+        if sampling is None or isinstance(sampling, SamplingParams):
+            params = [sampling or SamplingParams()] * len(prompts)
+        else:
+            params = list(sampling)
+            if len(params) == 1:
+                params = params * len(prompts)
+            if len(params) != len(prompts):
+                raise ValueError("Pass one SamplingParams object or one per prompt.")
+        ids = [self.add_request(p, s) for p, s in zip(prompts, params)]
+        results: Dict[int, GenerationResult] = {}
+        while not self.is_finished():
+            for r in self.step():
+                results[r.request_id] = r
+        return [results[i] for i in ids]
+
+
+# ---------------------------------------------------------------------- pool sizing
+def estimate_num_kv_blocks(model, block_size: int, dtype: torch.dtype, max_num_batched_tokens: int,
+                           gpu_memory_utilization: float, device) -> int:
+    """Pages that fit beside the weights: budget = total * utilization - used now; a
+    reserve of max(256 MiB, total / 20, the step's workspace) stays free (the reference's
+    rule, model/src/qwen3.cpp:96-151, with this engine's workspace: the widest
+    activations of a step)."""
+    if not 0.0 < gpu_memory_utilization <= 0.95:
+        raise ValueError("gpu_memory_utilization must be in (0, 0.95]")
+    free, total = torch.cuda.mem_get_info(device)
+    used = total - free
+    per_page = sum(CacheManager.bytes_per_page(model.cache_needs(), block_size, dtype).values())
+    d = model.desc
+    widest = max([d.hidden_size] + [p.params.get("intermediate_size", 0) * 3 for l in d.layers
+                                    for p in l.parts.values()])
+    workspace = 4 * max_num_batched_tokens * (6 * d.hidden_size + widest)
+    reserve = max(256 << 20, total // 20, workspace)
+    budget = int(total * gpu_memory_utilization) - used - reserve
+    return max(0, budget // max(per_page, 1))
+
+
+class LLM:
+    """The Python entry point: a model folder in, generated token ids out.
+
+    Option names follow the reference's command line and engine configuration
+    (model/model_main.cpp:403-428, 470-475): ``max_model_len`` (``--max-seq-len``),
+    ``num_kv_blocks`` (0: sized from free memory and ``gpu_memory_utilization``),
+    ``block_size`` 16, ``max_num_batched_tokens`` min(max_model_len, 256),
+    ``max_num_seqs`` 16.
+    """
+
+    def __init__(self, model: str, dtype: str = "bfloat16", max_model_len: int = 2048,
+                 num_kv_blocks: int = 0, block_size: int = 16, max_num_batched_tokens: Optional[int] = None,
+                 max_num_seqs: int = 16, gpu_memory_utilization: float = 0.9, device: str = "cuda:0",
+                 tokenizer: Optional[str] = None, loaded=None):
+        if device.startswith("cuda") and not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device; this engine has no CPU path")
+        torch_dtype = DTYPES[dtype] if isinstance(dtype, str) else dtype
+        self.model, self.model_config = loaded if loaded is not None else load_model(model, torch_dtype, device)
+        max_model_len = min(int(max_model_len), self.model.desc.max_positions)
+        block_size = min(int(block_size), max_model_len)
+        if max_num_batched_tokens is None:
+            max_num_batched_tokens = min(max_model_len, 256)
+        if num_kv_blocks <= 0:
+            num_kv_blocks = estimate_num_kv_blocks(self.model, block_size, torch_dtype,
+                                                   max_num_batched_tokens, gpu_memory_utilization, device)
+            cap = -(-max_model_len // block_size) * max_num_seqs
+            num_kv_blocks = min(num_kv_blocks, cap)
+            if num_kv_blocks <= 0:
+                raise RuntimeError("no memory left for the key/value cache")
+        self.cache = CacheManager(self.model.cache_needs(), block_size, num_kv_blocks, max_num_seqs,
+                                  max_model_len, torch_dtype, device)
+        self.runner = ModelRunner(self.model, self.cache, max_num_batched_tokens)
+        self.tokenizer = None
+        if tokenizer:
+            from tokenizers import Tokenizer     # optional; text is outside the engine proper
+            self.tokenizer = Tokenizer.from_file(tokenizer)
+        eos = getattr(self.model_config, "eos_token_ids", ())
+        cfg = EngineConfig(SchedulerConfig(max_num_seqs, max_num_batched_tokens, block_size, num_kv_blocks),
+                           max_model_len)
+        self.engine = LLMEngine(self.runner, cfg, eos,
+                                (lambda ids: self.tokenizer.decode(ids)) if self.tokenizer else None)
+
+    def encode(self, text: str) -> List[int]:
+        if self.tokenizer is None:
+            raise ValueError("text prompts need a tokenizer file")
+        return self.tokenizer.encode(text).ids
+
+    def generate(self, prompts, sampling_params=None) -> List[GenerationResult]:
+        """``prompts``: lists of token ids (or strings, with a tokenizer)."""
+        ids = [self.encode(p) if isinstance(p, str) else list(p) for p in prompts]
+        return self.engine.generate(ids, sampling_params)

@@ -1,0 +1,213 @@
+"""The scheduler: admits requests, cuts prompts into portions under a token budget,
+decodes, finishes and frees; and decides what happens when pages run out.
+
+Policy of the reference (engine/src/scheduler.cpp:40-160), kept:
+
+* two FIFO queues, ``waiting`` (new, partly computed and preempted requests) and
+  ``running`` (prompt fully computed);
+* pass 1, decode first: every running request gets one token, in queue order, while the
+  step has room; a request that cannot get the page for its next token is *preempted*:
+  it gives back everything it holds and goes to the front of ``waiting``; later its
+  prompt *and the tokens it had generated* are computed again (no swapping), and since
+  the key of a random draw depends only on the request and the token's index, sampling
+  goes on as if nothing had happened;
+* pass 2, portions of prompts into what is left of the token budget: a request that holds
+  nothing is admitted only if all pages of its present length are free (a prompt that
+  needs more pages than exist is an error; one that must wait goes to the back); it gets
+  ``min(uncomputed tokens, budget left)`` tokens; if that completes it, it moves to
+  ``running``, else to the back of ``waiting`` (one portion per request per step);
+* a step that schedules nothing while work remains is an error.
+
+Differences: pages are asked of the cache manager (several groups, windows) instead of
+a block manager of the scheduler's own; ``max_num_seqs`` bounds the requests that hold a
+slot at any time (the reference bounds the requests in one step); there is no prefix
+cache.
+"""
+from __future__ import annotations
+
+import enum
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Callable, Deque, Hashable, List, Optional, Sequence as Seq
+
+from ..sampling.params import SamplingParams
+
+
+class SchedulerError(RuntimeError):
+    pass
+
+
+class Status(enum.Enum):
+    WAITING = "waiting"
+    RUNNING = "running"
+    FINISHED = "finished"
+
+
+@dataclass
+class SchedulerConfig:
+    """Names and defaults of the reference (engine/include/scheduler.h:15-21)."""
+    max_num_seqs: int = 16
+    max_num_batched_tokens: int = 1024
+    block_size: int = 16
+    num_kv_blocks: int = 128
+
+    def validate(self) -> None:
+        for name in ("max_num_seqs", "max_num_batched_tokens", "block_size", "num_kv_blocks"):
+            if getattr(self, name) <= 0:
+                raise ValueError(f"{name} must be positive")
+
+
+class Sequence:
+    """A request: prompt and generated tokens, how many of them are in the cache
+    (reference: engine/include/sequence.h:19-54)."""
+
+    def __init__(self, request_id: int, prompt: Seq[int], sampling: SamplingParams):
+        self.id = request_id
+        self.tokens: List[int] = list(prompt)
+        self.prompt_len = len(self.tokens)
+        self.sampling = sampling
+        self.seed = sampling.seed if sampling.seed else request_id   # engine/src/sequence.cpp:14
+        self.status = Status.WAITING
+        self.num_cached_tokens = 0
+        self.num_scheduled_tokens = 0
+        self.preemptions = 0
+
+    def __len__(self) -> int:
+        return len(self.tokens)
+
+    @property
+    def completion(self) -> List[int]:
+        return self.tokens[self.prompt_len:]
+
+
+@dataclass
+class ScheduledSequence:
+    sequence: Sequence
+    token_start: int
+    token_count: int
+    is_prefill: bool
+    # a row is sampled for a decode token and for the portion that ends the sequence
+    # (engine/src/llm_engine.cpp:178-182); fixed when the plan is made
+    samples: bool = False
+
+
+@dataclass
+class BatchPlan:
+    sequences: List[ScheduledSequence] = field(default_factory=list)
+    num_tokens: int = 0
+    preempted: List[Sequence] = field(default_factory=list)
+
+    @property
+    def is_prefill(self) -> bool:
+        return bool(self.sequences) and all(s.is_prefill for s in self.sequences)
+
+
+class Scheduler:
+    def __init__(self, config: SchedulerConfig, cache):
+        """``cache`` is a ``CacheManager`` (only its host bookkeeping is used)."""
+        config.validate()
+        self.config, self.cache = config, cache
+        self.waiting: Deque[Sequence] = deque()
+        self.running: Deque[Sequence] = deque()
+        self.num_preemptions = 0
+
+    def add(self, sequence: Sequence) -> None:
+        if len(sequence) == 0:
+            raise ValueError("A scheduled request must contain at least one token.")
+        self.waiting.append(sequence)
+
+    def is_finished(self) -> bool:
+        return not self.waiting and not self.running
+
+    def _preempt(self, seq: Sequence, plan: BatchPlan) -> None:
+        self.cache.release(seq.id)
+        seq.status = Status.WAITING
+        seq.num_cached_tokens = 0
+        seq.num_scheduled_tokens = 0
+        seq.preemptions += 1
+        self.num_preemptions += 1
+        self.waiting.appendleft(seq)
+        plan.preempted.append(seq)
+
+    def schedule(self) -> BatchPlan:
+        plan = BatchPlan()
+        budget, max_seqs = self.config.max_num_batched_tokens, self.config.max_num_seqs
+        used = 0
+        # pass 1: one token for every running request
+        for _ in range(len(self.running)):
+            if len(plan.sequences) >= max_seqs or used >= budget:
+                break
+            seq = self.running.popleft()
+            if not self.cache.can_reserve(seq.id, len(seq)):
+                self._preempt(seq, plan)
+                continue
+            self.cache.reserve(seq.id, len(seq))
+            seq.num_scheduled_tokens = 1
+            plan.sequences.append(ScheduledSequence(seq, len(seq) - 1, 1, False, True))
+            self.running.append(seq)
+            used += 1
+        # pass 2: portions of waiting prompts into the rest of the budget
+        for _ in range(len(self.waiting)):
+            if len(plan.sequences) >= max_seqs or used >= budget:
+                break
+            seq = self.waiting.popleft()
+            if not self.cache.has(seq.id):
+                if not self._admit(seq):
+                    self.waiting.append(seq)
+                    continue
+            remaining = len(seq) - seq.num_cached_tokens
+            if remaining <= 0:
+                raise SchedulerError("A waiting prompt has no uncomputed tokens to schedule.")
+            count = min(remaining, budget - used)
+            seq.num_scheduled_tokens = count
+            plan.sequences.append(ScheduledSequence(seq, seq.num_cached_tokens, count, True,
+                                                    seq.num_cached_tokens + count == len(seq)))
+            used += count
+            if seq.num_cached_tokens + count == len(seq):
+                seq.status = Status.RUNNING
+                self.running.append(seq)
+            else:
+                self.waiting.append(seq)
+        plan.num_tokens = used
+        if not plan.sequences and not self.is_finished():
+            raise SchedulerError("The scheduler could not make progress with the available KV blocks.")
+        return plan
+
+    def _admit(self, seq: Sequence) -> bool:
+        """Slot and all pages of the present length, or nothing."""
+        pages = -(-len(seq) // self.cache.page_size)
+        for key, capacity in self.cache.capacity_pages().items():
+            if pages > capacity:
+                raise SchedulerError("The prompt requires more KV blocks than the engine owns.")
+        if self.cache.free_slots == 0:
+            return False
+        self.cache.admit(seq.id)
+        if not self.cache.can_reserve(seq.id, len(seq)):
+            self.cache.release(seq.id)
+            return False
+        self.cache.reserve(seq.id, len(seq))
+        return True
+
+    def postprocess(self, plan: BatchPlan, sampled: Seq[int], is_eos: Callable[[int], bool]) -> List[Sequence]:
+        """Book the step: ``sampled[i]`` is the token of ``plan.sequences[i]`` (-1 where it
+        sampled nothing).  Returns the requests that finished."""
+        if len(sampled) != len(plan.sequences):
+            raise SchedulerError("The model runner returned the wrong number of sampled tokens.")
+        finished = []
+        for item, token in zip(plan.sequences, sampled):
+            seq = item.sequence
+            seq.num_cached_tokens += seq.num_scheduled_tokens
+            seq.num_scheduled_tokens = 0
+            if item.is_prefill and seq.num_cached_tokens < len(seq):
+                continue
+            if token < 0:
+                raise SchedulerError("The model runner did not return a token for a completed step.")
+            seq.tokens.append(int(token))
+            stop = (not seq.sampling.ignore_eos and is_eos(int(token))) \
+                or len(seq.completion) >= seq.sampling.max_tokens
+            if stop:
+                seq.status = Status.FINISHED
+                self.cache.release(seq.id)
+                self.running.remove(seq)
+                finished.append(seq)
+        return finished

@@ -1,0 +1,64 @@
+"""Sampling of the next tokens on the device.
+
+One kernel draws a token per wanted row: argmax for greedy rows, the Gumbel-max rule
+for temperature rows, restricted to the nucleus when ``top_p`` < 1.  The reference keys
+its device sampler with a fresh 64-bit draw from a per-request ``mt19937_64`` at every
+step (engine/src/llm_engine.cpp:197-202) and samples top-p rows on the host (:110-145).
+Here the key of a draw is a hash of (request seed, index of the token among the
+request's outputs): it does not depend on which step or batch the token falls into, nor
+on a preemption in between.
+"""
+from __future__ import annotations
+
+from typing import List, Sequence, Tuple
+
+import torch
+
+from .. import ops
+
+_M = (1 << 64) - 1
+
+
+def _mix64(z: int) -> int:
+    z &= _M
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _M
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _M
+    return z ^ (z >> 31)
+
+
+def draw_key(request_seed: int, output_index: int) -> int:
+    """64-bit key of the draw for a request's ``output_index``-th generated token."""
+    return _mix64(_mix64(request_seed) + 0x9E3779B97F4A7C15 * (output_index + 1))
+
+
+def _signed(x: int) -> int:
+    return x - (1 << 64) if x >= (1 << 63) else x
+
+
+class Sampler:
+    def __init__(self, device, max_rows: int):
+        self.device = device
+        cuda = torch.device(device).type == "cuda"
+        self._params_host = torch.empty((max_rows, 2), dtype=torch.float32)
+        self._seeds_host = torch.empty(max_rows, dtype=torch.int64)
+        if cuda:
+            self._params_host = self._params_host.pin_memory()
+            self._seeds_host = self._seeds_host.pin_memory()
+        self._params = torch.empty((max_rows, 2), dtype=torch.float32, device=device)
+        self._seeds = torch.empty(max_rows, dtype=torch.int64, device=device)
+        self._out = torch.empty(max_rows, dtype=torch.int32, device=device)
+
+    def sample(self, logits: torch.Tensor, rows: Sequence[Tuple[float, float, int]]) -> List[int]:
+        """``rows[i]`` = (temperature, top_p, draw key) for ``logits[i]``; token ids on the host."""
+        n = len(rows)
+        assert logits.shape[0] == n
+        if n == 0:
+            return []
+        for i, (temp, top_p, key) in enumerate(rows):
+            self._params_host[i, 0] = temp
+            self._params_host[i, 1] = top_p
+            self._seeds_host[i] = _signed(key & _M)
+        self._params[:n].copy_(self._params_host[:n], non_blocking=True)
+        self._seeds[:n].copy_(self._seeds_host[:n], non_blocking=True)
+        ops.sample(logits, self._params[:n], self._seeds[:n], self._out[:n])
+        return self._out[:n].cpu().tolist()
