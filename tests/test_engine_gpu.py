@@ -131,7 +131,7 @@ def test_request_checks(folders):
                        (([1, 2], SamplingParams(max_tokens=32)), "completion exceeds"),
                        (([1], SamplingParams(top_p=0.0)), "top_p"),
                        (([1], SamplingParams(temperature=-1.0)), "temperature"),
-                       (([300], SamplingParams()), "outside")):
+                       (([300], SamplingParams(max_tokens=1)), "outside")):
         with pytest.raises(ValueError, match=match):
             eng.add_request(*bad)
     assert eng.is_finished()
