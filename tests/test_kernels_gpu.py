@@ -298,3 +298,105 @@ def test_refusals(ops):
     cache3 = torch.zeros((2, 2, 2, 16, 32), dtype=torch.bfloat16, device="cuda")
     with pytest.raises(ops.KernelError, match="heads"):
         ops.paged_attention(q3, cache3, z, z, table, 16, 3, 2, 32, None, 1.0, torch.empty_like(q3))
+
+
+# ----------------------------------------------------------------- tensor-core attention kernels
+def request_data(lens, nkv, hd, ps, seed, num_pages, max_pages):
+    table = scrambled_tables(len(lens), max_pages, num_pages, seed=seed)
+    cache = torch.zeros((num_pages, 2, nkv, ps, hd), dtype=torch.bfloat16, device="cuda").normal_()
+    K = [rnd(n, nkv, hd, seed=seed + 1 + i).to(torch.bfloat16).double() for i, n in enumerate(lens)]
+    V = [rnd(n, nkv, hd, seed=seed + 50 + i).to(torch.bfloat16).double() for i, n in enumerate(lens)]
+    for s in range(len(lens)):
+        fill_cache(cache, table, s, K[s], V[s], ps)
+    return table, cache, K, V
+
+
+@pytest.mark.parametrize("nh,nkv,hd,ps,window", [(32, 8, 128, 16, None), (4, 2, 64, 16, None), (16, 1, 128, 32, None),
+                                                 (6, 2, 64, 64, 100), (3, 3, 128, 16, 33), (14, 2, 64, 16, None)])
+@pytest.mark.parametrize("splits", [1, 3, 8])
+def test_decode_kernel_split_keys(ops, nh, nkv, hd, ps, window, splits):
+    """One-token rows of four requests (contexts 1 to 700), a padding row, a row list; for
+    each query one far key dominates: the first key the window admits or a page's last."""
+    lens = [700, 1, 130, 65]
+    max_pages = -(-700 // ps) + 1
+    table, cache, K, V = request_data(lens, nkv, hd, ps, 100, 4 * max_pages + 2, max_pages)
+    group = nh // nkv
+    T = 7
+    slot = torch.tensor([0, 1, -1, 2, 3, 0, 2], dtype=torch.int32)
+    pos = torch.tensor([699, 0, 0, 129, 64, 351, 17], dtype=torch.int32)
+    q = rnd(T, nh, hd, seed=101, scale=0.2).to(torch.bfloat16).double()
+    for t in range(T):
+        if slot[t] < 0:
+            continue
+        p = int(pos[t])
+        lo = max(0, p - window + 1) if window else 0
+        target = lo if t % 2 == 0 else max(lo, (p // ps) * ps - 1)
+        for h in range(nh):
+            q[t, h] += K[slot[t]][target, h // group] * 3.0
+    q = q.to(torch.bfloat16).double()
+    rows = torch.tensor([0, 1, 3, 4, 6, 5, 2], dtype=torch.int32)          # every row, in another order
+    out = torch.full((T, nh * hd), 3.0, dtype=torch.bfloat16, device="cuda")
+    ops.paged_attention_decode(dev(q.reshape(T, -1).to(torch.bfloat16)), cache, dev(pos), dev(slot), dev(rows), T,
+                               dev(table), ps, nh, nkv, hd, window, 1 / math.sqrt(hd), out, 700, splits=splits)
+    got = out.cpu().double().view(T, nh, hd)
+    assert (got[2] == 0).all()
+    for t in range(T):
+        if slot[t] < 0:
+            continue
+        s = int(slot[t])
+        want = plain_rows(q[t:t + 1], K[s][:pos[t] + 1], V[s][:pos[t] + 1], torch.tensor([int(pos[t])]), window)[0]
+        err = (got[t] - want).abs().max().item()
+        assert err < tol(torch.bfloat16, want.abs().max().item()), (t, err)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,ps,window", [(8, 2, 128, 16, None), (4, 4, 64, 32, None), (6, 1, 64, 16, 70),
+                                                 (2, 1, 128, 64, 9)])
+def test_prefill_kernel_segments(ops, nh, nkv, hd, ps, window):
+    """Segments that start inside a request (their earlier keys only in the cache), are
+    shorter and longer than a block of 64 rows, start and end off tile edges."""
+    lens = [300, 64, 131, 5]
+    max_pages = -(-300 // ps) + 1
+    table, cache, K, V = request_data(lens, nkv, hd, ps, 200, 4 * max_pages + 2, max_pages)
+    group = nh // nkv
+    segs = [(0, 93, 207), (1, 0, 64), (2, 128, 3), (3, 0, 5), (2, 1, 100)]      # slot, pos0, len (slot 2 twice is fine here)
+    seg_info, tiles, pos_rows, slot_rows, row = [], [], [], [], 0
+    for i, (s, p0, n) in enumerate(segs):
+        seg_info.append([s, row, n, p0])
+        tiles += [[i, off] for off in range(0, n, 64)]
+        pos_rows += list(range(p0, p0 + n))
+        slot_rows += [s] * n
+        row += n
+    T = row
+    q = rnd(T, nh, hd, seed=201, scale=0.2).to(torch.bfloat16).double()
+    for t in range(T):
+        p, s = pos_rows[t], slot_rows[t]
+        lo = max(0, p - window + 1) if window else 0
+        target = [lo, p, max(lo, (p // 64) * 64 - 1), max(lo, p - 1)][t % 4]
+        for h in range(nh):
+            q[t, h] += K[s][target, h // group] * 3.0
+    q = q.to(torch.bfloat16).double()
+    out = torch.zeros((T, nh * hd), dtype=torch.bfloat16, device="cuda")
+    tiles = tiles[::-1]
+    ops.paged_attention_prefill(dev(q.reshape(T, -1).to(torch.bfloat16)), cache,
+                                dev(torch.tensor(seg_info, dtype=torch.int32)),
+                                dev(torch.tensor(tiles, dtype=torch.int32)), len(tiles), dev(table), ps, nh, nkv,
+                                hd, window, 1 / math.sqrt(hd), out)
+    got = out.cpu().double().view(T, nh, hd)
+    for (s, r0, n, p0) in seg_info:
+        pos = torch.arange(p0, p0 + n)
+        want = plain_rows(q[r0:r0 + n], K[s][:p0 + n], V[s][:p0 + n], pos, window)
+        err = (got[r0:r0 + n] - want).abs().max().item()
+        assert err < tol(torch.bfloat16, want.abs().max().item()), (s, p0, n, err)
+
+
+def test_fast_attention_refuses_other_shapes(ops):
+    z = torch.zeros(1, dtype=torch.int32, device="cuda")
+    table = torch.zeros((1, 4), dtype=torch.int32, device="cuda")
+    for nh, nkv, hd, ps, match in ((2, 2, 48, 16, "head_dim"), (2, 2, 64, 8, "page size"), (34, 2, 64, 16, "group")):
+        q = torch.zeros((1, nh * hd), dtype=torch.bfloat16, device="cuda")
+        cache = torch.zeros((4, 2, nkv, ps, hd), dtype=torch.bfloat16, device="cuda")
+        assert not ops.fast_attention_ok(torch.bfloat16, ps, nh, nkv, hd)
+        with pytest.raises(ops.KernelError, match=match):
+            ops.paged_attention_decode(q, cache, z, z, None, 1, table, ps, nh, nkv, hd, None, 1.0,
+                                       torch.empty_like(q), 1, splits=1)
+    assert not ops.fast_attention_ok(torch.float32, 16, 4, 2, 64)

@@ -24,12 +24,12 @@ from tiny import TINIES, make_folder, requests_for, sharpen
 
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
-SHARPEN = {"A": 1.0, "B": 1.5, "C": 1.5}
-BF16_TOL = {"A": 0.012, "B": 0.15, "C": 0.3}
+SHARPEN = {"A": 1.0, "B": 1.5, "C": 1.5, "D": 1.5}
+BF16_TOL = {"A": 0.012, "B": 0.15, "C": 0.3, "D": 0.17}
 F32_TOL = 1e-4
 
 
-@pytest.fixture(scope="module", params=["A", "B", "C"])
+@pytest.fixture(scope="module", params=["A", "B", "C", "D"])
 def case(request, tmp_path_factory):
     name = request.param
     tiny = TINIES[name]

@@ -1,7 +1,8 @@
 """Tiny configurations for the tests.  A and B differ in every size and option: layers,
 width, heads and groups, head width, feed-forward width (200 is no multiple of 128),
 vocabulary, rope base, eps, tied or untied head, spread of the weights.  C adds sliding
-layers (window 24) between full ones, with sizes of its own."""
+layers (window 24) between full ones, with sizes of its own.  D has a head width (64) and
+a page size (16) that the tensor-core attention kernels take, one full and one sliding layer."""
 from __future__ import annotations
 
 import tempfile
@@ -30,7 +31,13 @@ TINY_C = dict(cfg=Qwen3Config(hidden_size=80, intermediate_size=176, num_hidden_
                               tie_word_embeddings=False, sliding_window=24,
                               layer_types=(SLIDING, FULL, SLIDING, SLIDING)),
               seed=2, std=0.08, norm_range=(0.6, 1.4), page_size=16)
-TINIES = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+TINY_D = dict(cfg=Qwen3Config(hidden_size=128, intermediate_size=344, num_hidden_layers=2,
+                              num_attention_heads=6, num_key_value_heads=2, head_dim=64, vocab_size=500,
+                              max_position_embeddings=512, rms_norm_eps=1e-6, rope_theta=1e5,
+                              tie_word_embeddings=True, sliding_window=80,
+                              layer_types=(FULL, SLIDING)),
+              seed=3, std=0.06, norm_range=(0.7, 1.3), page_size=16)
+TINIES = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 
 
 def make_folder(tiny, folder=None, dtype=torch.bfloat16, shards=1) -> Path:

@@ -80,10 +80,10 @@ class ModelRunner:
         strict_float32()
         n = self.max_batch_tokens
         # one packed int32 buffer per step: token ids | positions | slots | wanted rows | segments
-        self._host = torch.empty(8 * n, dtype=torch.int32)
+        self._host = torch.empty(12 * n + 64, dtype=torch.int32)
         if self.is_cuda:
             self._host = self._host.pin_memory()
-        self._dev = torch.empty(8 * n, dtype=torch.int32, device=self.device)
+        self._dev = torch.empty(12 * n + 64, dtype=torch.int32, device=self.device)
         self._uploaded: Optional[torch.cuda.Event] = None
 
     # ------------------------------------------------------------------ requests
@@ -112,7 +112,9 @@ class ModelRunner:
         host = self._host.numpy()
         o_ids, o_pos, o_slot, o_want = 0, total, 2 * total, 3 * total
         o_seg = o_want + wanted
-        used = o_seg + 4 * len(entries)
+        o_dec = o_seg + 4 * len(entries)
+        dec_rows: List[int] = []
+        tiles: List[Tuple[int, int, int]] = []      # (segment, offset, last position) per 64 query rows
         if self._uploaded is not None:
             self._uploaded.synchronize()
         segments: List[Segment] = []
@@ -139,10 +141,21 @@ class ModelRunner:
             s = len(segments)
             host[o_seg + 4 * s:o_seg + 4 * s + 4] = (slot, row, n, pos0)
             segments.append(Segment(e.request, slot, row, n, pos0))
+            if n == 1:
+                dec_rows.append(row)
+            else:
+                tiles += [(s, off, pos0 + min(off + 64, n)) for off in range(0, n, 64)]
             commits.append((e.request, pos0 + n))
             row += n
             max_ctx = max(max_ctx, pos0 + n)
             max_seg = max(max_seg, n)
+        n_dec, n_tiles = len(dec_rows), len(tiles)
+        o_tiles = o_dec + n_dec
+        used = o_tiles + 2 * n_tiles
+        host[o_dec:o_tiles] = dec_rows
+        tiles.sort(key=lambda t: -t[2])              # blocks with the most keys start first
+        for i, (s, off, _) in enumerate(tiles):
+            host[o_tiles + 2 * i], host[o_tiles + 2 * i + 1] = s, off
         self.cache.sync()
         if self.is_cuda:
             self._dev[:used].copy_(self._host[:used], non_blocking=True)
@@ -155,6 +168,8 @@ class ModelRunner:
             tokens=row, token_ids=d[o_ids:o_ids + row], positions=d[o_pos:o_pos + row],
             token_slot=d[o_slot:o_slot + row], want_rows=d[o_want:o_want + n_want],
             segments=segments, seg_info=d[o_seg:o_seg + 4 * len(segments)].view(-1, 4),
+            dec_rows=None if n_dec == row else d[o_dec:o_tiles], n_dec=n_dec,
+            pf_tiles=d[o_tiles:used].view(-1, 2), n_tiles=n_tiles,
             decode_only=(max_seg == 1), max_context=max_ctx, max_segment=max_seg)
         return ctx, commits
 

@@ -67,6 +67,9 @@ def _declare(h) -> None:
         "tllm_paged_attention_general": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32,
                                          i32, f32, vp, vp],
         "tllm_sample": [vp, i32, i32, i64, vp, vp, vp, vp],
+        "tllm_paged_attention_decode": [vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32,
+                                        i32, vp, vp, vp, vp],
+        "tllm_paged_attention_prefill": [vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32, vp, vp],
     }
     for name, args in sigs.items():
         fn = getattr(h, name)
@@ -166,15 +169,85 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_gain, k_gain, eps: float, inv_freq, 
         _dt(qkv), tokens, q_heads, kv_heads, head_dim, flags, _stream()), "qk_norm_rope_store")
 
 
+_workspaces = {}
+
+
+def workspace(device, floats: int) -> torch.Tensor:
+    """Float32 scratch that lives as long as the process (grown when a call needs more)."""
+    key = str(device)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < floats:
+        buf = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+SM_COUNT = 148
+
+
+def decode_splits(rows: int, kv_heads: int, max_context: int) -> int:
+    """How many blocks share the keys of one (row, key/value head): enough blocks for
+    about four per multiprocessor, each with at least 128 keys."""
+    want = -(-4 * SM_COUNT // max(rows * kv_heads, 1))
+    return max(1, min(want, -(-max_context // 128), 64))
+
+
+def fast_attention_ok(dtype, page_size: int, q_heads: int, kv_heads: int, head_dim: int) -> bool:
+    return (dtype == torch.bfloat16 and head_dim in (64, 128) and page_size % 16 == 0
+            and q_heads % kv_heads == 0 and q_heads // kv_heads <= 16)
+
+
+def paged_attention_decode(q, cache, positions, token_slot, rows, n_rows, block_table, page_size,
+                           q_heads, kv_heads, head_dim, window, scale, out, max_context, splits=None):
+    """Attention of one-token rows (``rows``: their indices, None for all), keys split over
+    ``splits`` blocks per (row, key/value head)."""
+    _cuda(q, cache, positions, token_slot, rows, block_table, out)
+    if splits is None:
+        splits = decode_splits(n_rows, kv_heads, max_context)
+    part_o = part_ml = None
+    if splits > 1:
+        n = n_rows * q_heads * splits
+        ws = workspace(q.device, n * (head_dim + 2))
+        part_o, part_ml = ws[:n * head_dim], ws[n * head_dim:n * (head_dim + 2)]
+    _check(lib().tllm_paged_attention_decode(
+        _p(q), _p(cache), _p(positions), _p(token_slot), _p(rows), n_rows, _p(block_table),
+        block_table.shape[1], page_size, q_heads, kv_heads, head_dim, int(window or 0), float(scale),
+        splits, _p(part_o), _p(part_ml), _p(out), _stream()), "paged_attention_decode")
+    return out
+
+
+def paged_attention_prefill(q, cache, seg_info, tiles, n_tiles, block_table, page_size, q_heads,
+                            kv_heads, head_dim, window, scale, out):
+    """Attention of the segments' query blocks listed in ``tiles`` ([n, 2] = segment, offset)."""
+    _cuda(q, cache, seg_info, tiles, block_table, out)
+    _check(lib().tllm_paged_attention_prefill(
+        _p(q), _p(cache), _p(seg_info), _p(tiles), n_tiles, _p(block_table), block_table.shape[1],
+        page_size, q_heads, kv_heads, head_dim, int(window or 0), float(scale), _p(out), _stream()),
+        "paged_attention_prefill")
+    return out
+
+
 def paged_attention(q: torch.Tensor, cache: torch.Tensor, positions, token_slot, block_table,
                     page_size: int, q_heads: int, kv_heads: int, head_dim: int,
                     window: Optional[int], scale: float, out: torch.Tensor, ctx=None) -> torch.Tensor:
     """Attention of every row of ``q`` over the keys of its own request in the paged cache:
-    positions max(0, pos - window + 1) .. pos.  ``ctx`` (the step's context) lets faster
-    kernels see how rows group into requests; the general kernel does not need it."""
+    positions max(0, pos - window + 1) .. pos.  With the step's context and a shape the
+    tensor-core kernels take (bfloat16, head width 64 or 128, pages of a multiple of 16),
+    one-token rows go to the split-key decode kernel and longer segments to the tiled
+    prefill kernel; everything else runs the general kernel."""
     _cuda(q, cache, positions, token_slot, block_table, out)
     tokens = q.shape[0]
     assert tuple(cache.shape[1:]) == (2, kv_heads, page_size, head_dim) and cache.dtype == q.dtype
+    if ctx is not None and ctx.pf_tiles is not None and ctx.tokens == tokens \
+            and fast_attention_ok(q.dtype, page_size, q_heads, kv_heads, head_dim):
+        if ctx.n_dec:
+            paged_attention_decode(q, cache, positions, token_slot, ctx.dec_rows, ctx.n_dec, block_table,
+                                   page_size, q_heads, kv_heads, head_dim, window, scale, out,
+                                   ctx.max_context)
+        if ctx.n_tiles:
+            paged_attention_prefill(q, cache, ctx.seg_info, ctx.pf_tiles, ctx.n_tiles, block_table,
+                                    page_size, q_heads, kv_heads, head_dim, window, scale, out)
+        return out
     _check(lib().tllm_paged_attention_general(
         _p(q), _p(cache), _p(positions), _p(token_slot), _p(block_table), block_table.shape[1],
         page_size, _dt(q), tokens, q_heads, kv_heads, head_dim, int(window or 0), float(scale),
