@@ -191,7 +191,7 @@ class LLM:
     def __init__(self, model: str, dtype: str = "bfloat16", max_model_len: int = 2048,
                  num_kv_blocks: int = 0, block_size: int = 16, max_num_batched_tokens: Optional[int] = None,
                  max_num_seqs: int = 16, gpu_memory_utilization: float = 0.9, device: str = "cuda:0",
-                 tokenizer: Optional[str] = None, loaded=None):
+                 tokenizer: Optional[str] = None, loaded=None, use_cuda_graphs: bool = True):
         if device.startswith("cuda") and not torch.cuda.is_available():
             raise RuntimeError("no CUDA device; this engine has no CPU path")
         torch_dtype = DTYPES[dtype] if isinstance(dtype, str) else dtype
@@ -209,7 +209,7 @@ class LLM:
                 raise RuntimeError("no memory left for the key/value cache")
         self.cache = CacheManager(self.model.cache_needs(), block_size, num_kv_blocks, max_num_seqs,
                                   max_model_len, torch_dtype, device)
-        self.runner = ModelRunner(self.model, self.cache, max_num_batched_tokens)
+        self.runner = ModelRunner(self.model, self.cache, max_num_batched_tokens, use_graphs=use_cuda_graphs)
         self.tokenizer = None
         if tokenizer:
             from tokenizers import Tokenizer     # optional; text is outside the engine proper

@@ -17,6 +17,7 @@ import numpy as np
 import torch
 
 from .. import models as _models  # noqa: F401  (registers the architectures)
+from .. import ops
 from ..cache.manager import CacheManager
 from ..config.base import ModelConfig, describe_model, load_config
 from ..models.model import Model, expected_tensors
@@ -71,8 +72,13 @@ def random_model(config: ModelConfig, seed: int, dtype: torch.dtype, device, std
 
 
 class ModelRunner:
-    def __init__(self, model: Model, cache: CacheManager, max_batch_tokens: int = 8192):
+    def __init__(self, model: Model, cache: CacheManager, max_batch_tokens: int = 8192,
+                 use_graphs: bool = True):
         self.model, self.cache = model, cache
+        self.use_graphs = use_graphs
+        self._graphs = {}
+        self._graph_pool = None
+        self._graph_logits: Optional[torch.Tensor] = None
         self.device = model.device
         self.vocab = model.desc.vocab_size
         self.max_batch_tokens = int(max_batch_tokens)
@@ -176,9 +182,108 @@ class ModelRunner:
     @torch.no_grad()
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Run one batch; logits [wanted, vocab] float32 on the device, in the order of
-        the entries and of their ``want`` lists."""
+        the entries and of their ``want`` lists.  The tensor may be reused by the next
+        step: read it (or sample from it) before stepping again."""
+        if self.use_graphs and self._graphable(entries):
+            return self._step_graph(entries)
         ctx, commits = self.build_context(entries)
         logits = self.model.forward(ctx, self.cache)
         for request, length in commits:
             self.cache.commit(request, length)
         return logits
+
+    # ------------------------------------------------------------------ decode steps as CUDA graphs
+    # A step of single tokens launches some three hundred small kernels; issued one by one
+    # from Python they cost more host time than the GPU needs to run them.  Such steps are
+    # therefore captured once per (rows rounded up to a power of two, context rounded up to
+    # a power of two) and replayed: every kernel reads the step's token ids, positions,
+    # slots and block tables from fixed device buffers, rows beyond the real ones carry
+    # slot -1 and are skipped, and the attention grid is sized for the context bucket.
+    # The same kernels run as in the step-by-step path.
+    GRAPH_MAX_ROWS = 256
+
+    def _graphable(self, entries: Sequence[StepEntry]) -> bool:
+        return (self.is_cuda and 0 < len(entries) <= self.GRAPH_MAX_ROWS
+                and len(entries) <= self.max_batch_tokens
+                and all(len(e.tokens) == 1 for e in entries)
+                and all(getattr(b.mixer, "graph_safe", False) for b in self.model.blocks))
+
+    def _step_graph(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        rows = len(entries)
+        bucket = 1
+        while bucket < rows:
+            bucket *= 2
+        bucket = min(bucket, self.max_batch_tokens)
+        seen = set()
+        host = self._host.numpy()
+        if self._uploaded is not None:
+            self._uploaded.synchronize()
+        host[0:bucket] = -1
+        host[bucket:2 * bucket] = 0
+        host[2 * bucket:3 * bucket] = -1
+        host[3 * bucket:4 * bucket] = np.arange(bucket)
+        commits, wanted, max_ctx = [], [], 0
+        for i, e in enumerate(entries):
+            if e.request in seen:
+                raise StepError(f"request {e.request!r} appears twice in one step")
+            seen.add(e.request)
+            tok = int(e.tokens[0])
+            if not 0 <= tok < self.vocab:
+                raise StepError(f"request {e.request!r}: token id outside [0, {self.vocab})")
+            if not self.cache.has(e.request):
+                self.cache.admit(e.request)
+            pos = self.cache.computed(e.request)
+            self.cache.reserve(e.request, pos + 1)
+            host[i], host[bucket + i], host[2 * bucket + i] = tok, pos, self.cache.slot_of(e.request)
+            for w in e.want:
+                if w != 0:
+                    raise StepError(f"request {e.request!r}: wanted place {w} outside its 1 token")
+                wanted.append(i)
+            commits.append((e.request, pos + 1))
+            max_ctx = max(max_ctx, pos + 1)
+        ctx_bucket = 256
+        while ctx_bucket < max_ctx:
+            ctx_bucket *= 2
+        self.cache.sync()
+        self._dev[:4 * bucket].copy_(self._host[:4 * bucket], non_blocking=True)
+        self._uploaded = torch.cuda.Event()
+        self._uploaded.record()
+        key = (bucket, ctx_bucket)
+        if key not in self._graphs:
+            self._capture(key)
+        graph, kernels = self._graphs[key]
+        graph.replay()
+        ops.launches += kernels                      # the replay launches what the capture recorded
+        logits = self._graph_logits
+        for request, length in commits:
+            self.cache.commit(request, length)
+        if wanted == list(range(rows)):
+            return logits[:rows]
+        if not wanted:
+            return logits[:0]
+        return logits[torch.tensor(wanted, device=self.device)]
+
+    def _capture(self, key) -> None:
+        bucket, ctx_bucket = key
+        d = self._dev
+        ctx = StepContext(
+            tokens=bucket, token_ids=d[0:bucket], positions=d[bucket:2 * bucket],
+            token_slot=d[2 * bucket:3 * bucket], want_rows=d[3 * bucket:4 * bucket], segments=[],
+            seg_info=None, dec_rows=None, n_dec=bucket, pf_tiles=d[0:0].view(-1, 2), n_tiles=0,
+            decode_only=True, max_context=ctx_bucket, max_segment=1)
+        self.model.forward(ctx, self.cache)          # warm-up: sizes workspaces, loads kernels
+        torch.cuda.current_stream().synchronize()
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        if self._graph_logits is None:
+            rows = min(self.GRAPH_MAX_ROWS, self.max_batch_tokens)
+            self._graph_logits = torch.empty((rows, self.vocab), dtype=torch.float32, device=self.device)
+        graph = torch.cuda.CUDAGraph()
+        before = ops.launches
+        with torch.cuda.graph(graph, pool=self._graph_pool):
+            # the result goes to a buffer of the runner's own, so that the graphs' private
+            # memory can be shared between them
+            self._graph_logits[:bucket].copy_(self.model.forward(ctx, self.cache))
+        kernels = ops.launches - before
+        ops.launches = before                        # capturing launches nothing
+        self._graphs[key] = (graph, kernels)

@@ -79,7 +79,12 @@ def _declare(h) -> None:
     h.tllm_uniform_of.restype = f32
 
 
-def _check(code: int, what: str) -> None:
+launches = 0      # kernels of csrc/ launched so far (graph replays are added by the runner)
+
+
+def _check(code: int, what: str, kernels: int = 1) -> None:
+    global launches
+    launches += kernels
     if code != 0:
         raise KernelError(f"{what}: {lib().tllm_last_error().decode(errors='replace')} (code {code})")
 
@@ -212,7 +217,8 @@ def paged_attention_decode(q, cache, positions, token_slot, rows, n_rows, block_
     _check(lib().tllm_paged_attention_decode(
         _p(q), _p(cache), _p(positions), _p(token_slot), _p(rows), n_rows, _p(block_table),
         block_table.shape[1], page_size, q_heads, kv_heads, head_dim, int(window or 0), float(scale),
-        splits, _p(part_o), _p(part_ml), _p(out), _stream()), "paged_attention_decode")
+        splits, _p(part_o), _p(part_ml), _p(out), _stream()), "paged_attention_decode",
+        kernels=2 if splits > 1 else 1)
     return out
 
 

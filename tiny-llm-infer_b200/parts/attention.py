@@ -25,6 +25,8 @@ from .spec import CacheSpec, ParamSpec, PartSpec, StateSpec
 
 @register("mixer", "gq_attention")
 class GroupedQueryAttention:
+    graph_safe = True      # every launch reads the step's data from device buffers: capturable
+
     def __init__(self, hidden_size: int, q_heads: int, kv_heads: int, head_dim: int,
                  dtype: torch.dtype, device, qk_norm_eps: Optional[float] = None,
                  position: Optional[PartSpec] = None, window: Optional[int] = None,
