@@ -297,3 +297,72 @@ extern "C" int tllm_paged_attention_decode(
     return launch_decode<128>(q, cache, positions, token_slot, rows, n_rows, block_table, max_pages, page_size,
                               q_heads, kv_heads, window, scale, splits, part_o, part_ml, out, stream);
 }
+
+// ---------------------------------------------------------------------------------------------
+// The same attention for callers that must not allocate device memory (see tllm_noalloc.h for
+// who they are and for the rules).  The partial results of the key splits go to the array
+// below, which is part of the library's device image.  In host code the name
+// `g_noalloc_scratch` is only a stand-in for the symbol, never a device address: handing it
+// to a kernel would make the kernel fault, or, where the GPU can reach host memory, use the
+// wrong memory without a word.  Its device address comes from cudaGetSymbolAddress, looked
+// up once per device by the first call made while that device is current.
+#include "tllm_noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_scratch[TLLM_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_scratch_addr[kMaxDevices] = {};
+
+// Device address of the scratch array on the current device, or nullptr (error text set).
+float* noalloc_scratch_address() {
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess || device < 0 || device >= kMaxDevices) {
+        set_error("paged_attention_decode_noalloc: cannot tell the current device (%s)",
+                  e != cudaSuccess ? cudaGetErrorString(e) : "index out of range");
+        return nullptr;
+    }
+    if (g_noalloc_scratch_addr[device] == nullptr) {
+        void* addr = nullptr;
+        e = cudaGetSymbolAddress(&addr, g_noalloc_scratch);
+        if (e != cudaSuccess || addr == nullptr) {
+            set_error("paged_attention_decode_noalloc: cudaGetSymbolAddress failed (%s)", cudaGetErrorString(e));
+            return nullptr;
+        }
+        g_noalloc_scratch_addr[device] = static_cast<float*>(addr);
+    }
+    return g_noalloc_scratch_addr[device];
+}
+}  // namespace
+
+extern "C" long long tllm_noalloc_scratch_needed(int n_rows, int q_heads, int head_dim, int splits) {
+    if (splits <= 1 || n_rows <= 0 || q_heads <= 0 || head_dim <= 0) return 0;
+    return (long long)n_rows * q_heads * splits * (head_dim + 2);
+}
+
+extern "C" int tllm_paged_attention_decode_noalloc(
+    const void* q, const void* cache, const int* positions, const int* token_slot, const int* rows,
+    int n_rows, const int* block_table, int max_pages, int page_size, int q_heads, int kv_heads,
+    int head_dim, int window, float scale, int splits, void* out, cudaStream_t stream) {
+    TLLM_REQUIRE(n_rows >= 0 && q_heads > 0 && head_dim > 0 && splits >= 1,
+                 "paged_attention_decode_noalloc: bad sizes");
+    const long long need = tllm_noalloc_scratch_needed(n_rows, q_heads, head_dim, splits);
+    TLLM_REQUIRE(need <= (long long)TLLM_NOALLOC_SCRATCH_FLOATS,
+                 "paged_attention_decode_noalloc: %d rows x %d heads x %d splits x (%d + 2) = %lld floats of "
+                 "scratch exceed the built-in %u; use fewer splits or rows, or the entry point that takes "
+                 "the caller's scratch", n_rows, q_heads, splits, head_dim, need,
+                 (unsigned)TLLM_NOALLOC_SCRATCH_FLOATS);
+    float* part_o = nullptr;
+    float* part_ml = nullptr;
+    if (splits > 1) {
+        float* base = noalloc_scratch_address();
+        if (base == nullptr) return -1;
+        const long long n = (long long)n_rows * q_heads * splits;
+        part_o = base;                       // [n][head_dim], each element written before it is read
+        part_ml = base + n * head_dim;       // [n][2]
+    }
+    return tllm_paged_attention_decode(q, cache, positions, token_slot, rows, n_rows, block_table, max_pages,
+                                       page_size, q_heads, kv_heads, head_dim, window, scale, splits, part_o,
+                                       part_ml, out, stream);
+}
