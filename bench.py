@@ -104,6 +104,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"],
                     help="fewer layers than the model has (named in the record) if memory or time needs it")
     ap.add_argument("--skip-points", action="store_true", help="leave out the batch 1 and 64 points")
+    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "e2e"],
+                    help="run one phase only (for profiling a small case); the record then lacks the others")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -166,17 +168,19 @@ def main() -> int:
         runner.release("prefill")
         return start.elapsed_time(end)
 
-    for _ in range(3):
-        prefill_once()
-    w0 = time.perf_counter()
-    prefill_ms = statistics.median(prefill_once() for _ in range(5))
-    windows.append((w0, time.perf_counter()))
-    prefill_flops = 2.0 * PREFILL_TOKENS * args.layers * layer_params \
-        + args.layers * 2.0 * PREFILL_TOKENS ** 2 * cfg.q_dim + 2.0 * vocab * cfg.hidden_size
-    prefill = {"value": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "tokens": PREFILL_TOKENS,
-               "ms": round(prefill_ms, 3),
-               "frac": round(prefill_flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
-    print(f"[bench] prefill {prefill}", file=sys.stderr, flush=True)
+    prefill = None
+    if args.only in ("all", "prefill"):
+        for _ in range(3):
+            prefill_once()
+        w0 = time.perf_counter()
+        prefill_ms = statistics.median(prefill_once() for _ in range(5))
+        windows.append((w0, time.perf_counter()))
+        prefill_flops = 2.0 * PREFILL_TOKENS * args.layers * layer_params \
+            + args.layers * 2.0 * PREFILL_TOKENS ** 2 * cfg.q_dim + 2.0 * vocab * cfg.hidden_size
+        prefill = {"value": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "tokens": PREFILL_TOKENS,
+                   "ms": round(prefill_ms, 3),
+                   "frac": round(prefill_flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+        print(f"[bench] prefill {prefill}", file=sys.stderr, flush=True)
 
     # ---------------------------------------------------------------- decode, timed on the device
     def decode_device(batch, steps, warmup):
@@ -217,13 +221,15 @@ def main() -> int:
         mean_ctx = start_len + warmup + (steps - 1) / 2.0 + 1
         return batch / (ms / 1e3), ms, launches, mean_ctx
 
-    value, ms_per_step, launches, mean_ctx = decode_device(args.batch, args.steps, args.warmup)
-    step_bytes = weight_bytes + args.batch * mean_ctx * kv_bytes_per_token
-    achieved = step_bytes / (ms_per_step / 1e3) / 1e9
-    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                "frac": round(achieved / pk["hbm_gbs"], 4)}
-    print(f"[bench] decode b{args.batch}: {value:.1f} tok/s, {ms_per_step:.3f} ms/step, {roofline}",
-          file=sys.stderr, flush=True)
+    value = ms_per_step = launches = mean_ctx = roofline = None
+    if args.only in ("all", "decode"):
+        value, ms_per_step, launches, mean_ctx = decode_device(args.batch, args.steps, args.warmup)
+        step_bytes = weight_bytes + args.batch * mean_ctx * kv_bytes_per_token
+        achieved = step_bytes / (ms_per_step / 1e3) / 1e9
+        roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                    "frac": round(achieved / pk["hbm_gbs"], 4)}
+        print(f"[bench] decode b{args.batch}: {value:.1f} tok/s, {ms_per_step:.3f} ms/step, {roofline}",
+              file=sys.stderr, flush=True)
 
     # ---------------------------------------------------------------- the same through the entry point
     def decode_e2e(batch, steps, warmup):
@@ -253,11 +259,14 @@ def main() -> int:
         h2d = 4 * bucket * 4 + batch * 8 + batch * 8         # rows' ids/positions/slots/wanted, sampling params, keys
         return batch * steps / elapsed, h2d, batch * 4
 
-    e2e_value, h2d, d2h = decode_e2e(args.batch, args.steps, args.warmup)
-    print(f"[bench] e2e b{args.batch}: {e2e_value:.1f} tok/s", file=sys.stderr, flush=True)
+    e2e = None
+    if args.only in ("all", "e2e"):
+        e2e_value, h2d, d2h = decode_e2e(args.batch, args.steps, args.warmup)
+        e2e = {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+        print(f"[bench] e2e b{args.batch}: {e2e_value:.1f} tok/s", file=sys.stderr, flush=True)
 
     points = {}
-    if not args.skip_points:
+    if not args.skip_points and args.only == "all":
         for b in (1, 64):
             v, ms_b, _, ctx_b = decode_device(b, min(args.steps, 32), args.warmup)
             points[f"decode_b{b}"] = round(v, 1)
@@ -266,17 +275,17 @@ def main() -> int:
 
     record = {
         "metric": "decode tok/s @ batch 8 (Qwen3-8B shape, context 4096, 1 B200)",
-        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "value": None if value is None else round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": None if ms_per_step is None else round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (random weights N(0,0.02), uniform random token ids)",
         "config": {"model": "Qwen3-8B shape", "global_batch": args.batch, "seq_len": CONTEXT,
                    "parallelism": "single GPU", "layers": args.layers, "layers_of_model": QWEN3_8B["num_hidden_layers"],
                    "hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size,
                    "q_heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
-                   "vocab_size": vocab, "page_size": PAGE, "decode_context": round(mean_ctx, 1),
+                   "vocab_size": vocab, "page_size": PAGE, "decode_context": None if mean_ctx is None else round(mean_ctx, 1),
                    "prefill_tokens": PREFILL_TOKENS, "l2": "inputs larger than L2 (16 GB of weights per step)",
                    "peaks": pk["source"]},
-        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "e2e": e2e,
         "gpu_launches": launches,
         "prefill": prefill, "roofline": roofline, "points": points,
         "clocks": clocks.stop(windows),
