@@ -116,7 +116,7 @@ def paged_attention(q, cache, positions, token_slot, block_table, page_size, q_h
     return out
 
 
-def sample(logits, params, seeds, out):
+def sample(logits, params, seeds, out, any_nucleus=None):
     from plain_qwen3 import gumbel_scores, nucleus
     import numpy as np
     for r in range(logits.shape[0]):

@@ -5,6 +5,10 @@
 // swiglu_kernel_cuda.cu:7-27) is fused here around one rule: the residual stream is
 // a float32 tensor that only this file's kernels write, so the residual sum and the
 // norm's mean are 32-bit in both storage modes.
+//
+// Every kernel has a vector form (16-byte loads and stores, eight elements per thread per
+// access, every load of a row issued before the first dependent instruction) for widths that
+// are multiples of eight, and a scalar form that takes any width.
 #include <cstdarg>
 #include <cstdio>
 
@@ -30,6 +34,38 @@ int finish_launch(const char* what) {
     return 0;
 }
 
+// ---------------------------------------------------------------- 8-element accesses
+template <typename T> struct Vec8;
+template <> struct Vec8<float> {
+    static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
+        const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[8]) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+};
+template <> struct Vec8<bf16> {
+    static __device__ __forceinline__ void load(const bf16* p, float (&v)[8]) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(h[i]);
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ void store(bf16* p, const float (&v)[8]) {
+        uint4 raw;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        *reinterpret_cast<uint4*>(p) = raw;
+    }
+};
+
 // ---------------------------------------------------------------- embedding
 // out[t, :] = table[ids[t], :] widened to float32.  Rows with ids[t] < 0 (padding of a
 // fixed-size batch) become zero.  Ids are range-checked on the host; the clamp below
@@ -47,6 +83,22 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const TW* __restri
     if (id >= vocab) id = vocab - 1;
     const TW* src = table + (size_t)id * hidden;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_f32<TW>(src[i]);
+}
+
+template <typename TW>
+__global__ void embedding_vec_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
+                                     float* __restrict__ out, int hidden, int vocab) {
+    const int t = blockIdx.x;
+    int id = ids[t];
+    float* dst = out + (size_t)t * hidden;
+    const bool pad = id < 0;
+    if (id >= vocab) id = vocab - 1;
+    const TW* src = table + (size_t)(pad ? 0 : id) * hidden;
+    for (int c = threadIdx.x; c < hidden / 8; c += blockDim.x) {
+        float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (!pad) Vec8<TW>::load(src + c * 8, v);
+        Vec8<float>::store(dst + c * 8, v);
+    }
 }
 
 // ---------------------------------------------------------------- add + RMSNorm
@@ -86,6 +138,62 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
     }
 }
 
+// Vector form: the row lives in registers between the sum and the scaling, CHUNKS groups of
+// eight elements per thread (width <= blockDim * 8 * CHUNKS, width a multiple of 8).
+template <typename TD, typename TG, typename TO, int CHUNKS>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restrict__ delta,
+                                       const TG* __restrict__ gain, float eps, TO* __restrict__ out,
+                                       const int* __restrict__ rows, int width) {
+    __shared__ float scratch[32];
+    const int o = blockIdx.x;
+    const int r = rows ? rows[o] : o;
+    TO* dst = out + (size_t)o * width;
+    const int n_chunks = width >> 3;
+    if (r < 0) {
+        const float zero[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int c = threadIdx.x; c < n_chunks; c += blockDim.x) Vec8<TO>::store(dst + c * 8, zero);
+        return;
+    }
+    float* hr = h + (size_t)r * width;
+    const TD* dr = delta ? delta + (size_t)r * width : nullptr;
+    const bool write_back = (rows == nullptr) && (dr != nullptr);
+    float v[CHUNKS][8], d[CHUNKS][8];
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        if (c < n_chunks) {
+            Vec8<float>::load(hr + c * 8, v[j]);
+            if (dr) Vec8<TD>::load(dr + c * 8, d[j]);
+        }
+    }
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        if (c < n_chunks) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                if (dr) v[j][e] += d[j][e];
+                sum += v[j][e] * v[j][e];
+            }
+            if (write_back) Vec8<float>::store(hr + c * 8, v[j]);
+        }
+    }
+    sum = block_sum(sum, scratch);
+    const float scale = 1.0f / sqrtf(sum / (float)width + eps);
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        if (c < n_chunks) {
+            float g[8];
+            Vec8<TG>::load(gain + c * 8, g);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) g[e] = g[e] * v[j][e] * scale;
+            Vec8<TO>::store(dst + c * 8, g);
+        }
+    }
+}
+
 // ---------------------------------------------------------------- SwiGLU
 // out[t, i] = silu(gu[t, i]) * gu[t, inter + i], silu(x) = x / (1 + exp(-x)), in float32.
 template <typename T>
@@ -98,6 +206,23 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
         const float g = to_f32<T>(gu[t * 2 * inter + i]);
         const float u = to_f32<T>(gu[t * 2 * inter + inter + i]);
         out[idx] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+    }
+}
+
+template <typename T>
+__global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter,
+                                  size_t total_chunks) {
+    const int per_row = inter >> 3;
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; idx < total_chunks; idx += stride) {
+        const size_t t = idx / per_row, c = idx - t * per_row;
+        float g[8], u[8];
+        Vec8<T>::load(gu + t * 2 * inter + c * 8, g);
+        Vec8<T>::load(gu + t * 2 * inter + inter + c * 8, u);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) g[e] = g[e] / (1.0f + expf(-g[e])) * u[e];
+        Vec8<T>::store(out + t * inter + c * 8, g);
     }
 }
 
@@ -114,18 +239,39 @@ static int grid_for(size_t total, int block) {
     return (int)(g < 1 ? 1 : (g > cap ? cap : g));
 }
 
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <typename TD, typename TG, typename TO>
+static int launch_add_rmsnorm_typed(float* h, const void* delta, const void* gain, float eps, void* out,
+                                    const int* rows, int n_out, int width, cudaStream_t stream) {
+    const bool vec = width % 8 == 0 && aligned16(h) && aligned16(delta) && aligned16(gain) && aligned16(out);
+    const int chunks = width / 8;
+    if (vec && chunks <= 1024 * 4) {
+        int block = 64;
+        while (block < 1024 && block < chunks) block *= 2;
+        const int per_thread = (chunks + block - 1) / block;
+#define VEC_LAUNCH(C)                                                                 \
+    add_rmsnorm_vec_kernel<TD, TG, TO, C><<<n_out, block, 0, stream>>>(               \
+        h, (const TD*)delta, (const TG*)gain, eps, (TO*)out, rows, width)
+        if (per_thread <= 1) VEC_LAUNCH(1);
+        else if (per_thread <= 2) VEC_LAUNCH(2);
+        else VEC_LAUNCH(4);
+#undef VEC_LAUNCH
+    } else {
+        const int block = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+        add_rmsnorm_kernel<TD, TG, TO><<<n_out, block, 0, stream>>>(
+            h, (const TD*)delta, (const TG*)gain, eps, (TO*)out, rows, width);
+    }
+    return finish_launch("add_rmsnorm");
+}
+
 template <typename TD, typename TO>
 static int launch_add_rmsnorm(float* h, const void* delta, const void* gain, int gain_dtype,
                               float eps, void* out, const int* rows, int n_out, int width,
                               cudaStream_t stream) {
-    const int block = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
     if (gain_dtype == kBF16)
-        add_rmsnorm_kernel<TD, bf16, TO><<<n_out, block, 0, stream>>>(
-            h, (const TD*)delta, (const bf16*)gain, eps, (TO*)out, rows, width);
-    else
-        add_rmsnorm_kernel<TD, float, TO><<<n_out, block, 0, stream>>>(
-            h, (const TD*)delta, (const float*)gain, eps, (TO*)out, rows, width);
-    return finish_launch("add_rmsnorm");
+        return launch_add_rmsnorm_typed<TD, bf16, TO>(h, delta, gain, eps, out, rows, n_out, width, stream);
+    return launch_add_rmsnorm_typed<TD, float, TO>(h, delta, gain, eps, out, rows, n_out, width, stream);
 }
 
 }  // namespace tllm
@@ -139,14 +285,17 @@ const char* tllm_last_error() { return g_error; }
 int tllm_embedding(const int* ids, const void* table, int table_dtype, float* out, int tokens,
                    int hidden, int vocab, cudaStream_t stream) {
     TLLM_REQUIRE(tokens >= 0 && hidden > 0 && vocab > 0, "embedding: bad sizes");
+    TLLM_REQUIRE(table_dtype == kBF16 || table_dtype == kF32, "embedding: unknown dtype %d", table_dtype);
     if (tokens == 0) return 0;
-    const int block = hidden >= 1024 ? 256 : 128;
-    if (table_dtype == kBF16)
-        embedding_kernel<bf16><<<tokens, block, 0, stream>>>(ids, (const bf16*)table, out, hidden, vocab);
-    else if (table_dtype == kF32)
-        embedding_kernel<float><<<tokens, block, 0, stream>>>(ids, (const float*)table, out, hidden, vocab);
-    else
-        TLLM_REQUIRE(false, "embedding: unknown dtype %d", table_dtype);
+    const bool vec = hidden % 8 == 0 && aligned16(table) && aligned16(out);
+    const int block = vec ? (hidden >= 2048 ? 256 : 128) : (hidden >= 1024 ? 256 : 128);
+    if (table_dtype == kBF16) {
+        if (vec) embedding_vec_kernel<bf16><<<tokens, block, 0, stream>>>(ids, (const bf16*)table, out, hidden, vocab);
+        else embedding_kernel<bf16><<<tokens, block, 0, stream>>>(ids, (const bf16*)table, out, hidden, vocab);
+    } else {
+        if (vec) embedding_vec_kernel<float><<<tokens, block, 0, stream>>>(ids, (const float*)table, out, hidden, vocab);
+        else embedding_kernel<float><<<tokens, block, 0, stream>>>(ids, (const float*)table, out, hidden, vocab);
+    }
     return finish_launch("embedding");
 }
 
@@ -168,15 +317,24 @@ int tllm_add_rmsnorm(float* h, const void* delta, const void* gain, int gain_dty
 int tllm_swiglu(const void* gate_up, void* out, int dtype, int tokens, int inter,
                 cudaStream_t stream) {
     TLLM_REQUIRE(tokens >= 0 && inter > 0, "swiglu: bad sizes");
+    TLLM_REQUIRE(dtype == kBF16 || dtype == kF32, "swiglu: unknown dtype %d", dtype);
     const size_t total = (size_t)tokens * inter;
     if (total == 0) return 0;
-    const int block = 256, grid = grid_for(total, block);
-    if (dtype == kBF16)
-        swiglu_kernel<bf16><<<grid, block, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter, total);
-    else if (dtype == kF32)
-        swiglu_kernel<float><<<grid, block, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
-    else
-        TLLM_REQUIRE(false, "swiglu: unknown dtype %d", dtype);
+    const int block = 256;
+    if (inter % 8 == 0 && aligned16(gate_up) && aligned16(out)) {
+        const size_t chunks = total / 8;
+        const int grid = grid_for(chunks, block);
+        if (dtype == kBF16)
+            swiglu_vec_kernel<bf16><<<grid, block, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter, chunks);
+        else
+            swiglu_vec_kernel<float><<<grid, block, 0, stream>>>((const float*)gate_up, (float*)out, inter, chunks);
+    } else {
+        const int grid = grid_for(total, block);
+        if (dtype == kBF16)
+            swiglu_kernel<bf16><<<grid, block, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter, total);
+        else
+            swiglu_kernel<float><<<grid, block, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
+    }
     return finish_launch("swiglu");
 }
 

@@ -90,6 +90,129 @@ __global__ void qk_norm_rope_store_kernel(
     }
 }
 
+// Vector form for head widths 64, 128 and 256 with the whole head rotated: one block per
+// token.  The block first writes the token's cosines and sines to shared memory (once, not
+// once per head), then its warps take the heads in turn.  A lane holds VEC = head_dim / 32
+// neighbouring elements (one 4-, 8- or 16-byte access); the rotation partner of an element
+// is VEC * 16 elements away, that is, in lane ^ 16.
+template <typename T, int VEC> struct VecIO;
+template <int VEC> struct VecIO<bf16, VEC> {
+    static __device__ __forceinline__ void load(const bf16* p, float (&v)[VEC]) {
+        if constexpr (VEC == 2) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+            v[0] = f.x; v[1] = f.y;
+        } else if constexpr (VEC == 4) {
+            const uint2 raw = *reinterpret_cast<const uint2*>(p);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+            const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+            v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+        } else {
+            const uint4 raw = *reinterpret_cast<const uint4*>(p);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(h[i]);
+                v[2 * i] = f.x; v[2 * i + 1] = f.y;
+            }
+        }
+    }
+    static __device__ __forceinline__ void store(bf16* p, const float (&v)[VEC]) {
+        if constexpr (VEC == 2) {
+            *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v[0], v[1]);
+        } else if constexpr (VEC == 4) {
+            uint2 raw;
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+            h[0] = __floats2bfloat162_rn(v[0], v[1]);
+            h[1] = __floats2bfloat162_rn(v[2], v[3]);
+            *reinterpret_cast<uint2*>(p) = raw;
+        } else {
+            uint4 raw;
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            *reinterpret_cast<uint4*>(p) = raw;
+        }
+    }
+};
+template <int VEC> struct VecIO<float, VEC> {
+    static __device__ __forceinline__ void load(const float* p, float (&v)[VEC]) {
+#pragma unroll
+        for (int i = 0; i < VEC; i += 2) {
+            const float2 f = *reinterpret_cast<const float2*>(p + i);
+            v[i] = f.x; v[i + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[VEC]) {
+#pragma unroll
+        for (int i = 0; i < VEC; i += 2) *reinterpret_cast<float2*>(p + i) = make_float2(v[i], v[i + 1]);
+    }
+};
+
+template <typename T, typename TG, int VEC>
+__global__ void qk_norm_rope_store_vec_kernel(
+    T* __restrict__ qkv, const TG* __restrict__ q_gain, const TG* __restrict__ k_gain, float eps,
+    const float* __restrict__ inv_freq, const int* __restrict__ positions,
+    const int* __restrict__ token_slot, const int* __restrict__ block_table, int max_pages,
+    T* __restrict__ cache, int page_size, T* __restrict__ q_out, int q_heads, int kv_heads, int flags) {
+    constexpr int HD = VEC * 32, HALF = HD / 2;
+    __shared__ float cs[HALF], sn[HALF];
+    const int t = blockIdx.x;
+    const int slot = token_slot[t];
+    if (slot < 0) return;
+    const int pos = positions[t];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const bool rope = (flags & kFlagRope) != 0;
+    if (rope)
+        for (int i = threadIdx.x; i < HALF; i += blockDim.x) sincosf((float)pos * inv_freq[i], &sn[i], &cs[i]);
+    const int heads_total = q_heads + 2 * kv_heads;
+    const int e0 = lane * VEC;
+    float gq[VEC], gk[VEC];
+    if (flags & kFlagNorm) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) { gq[i] = to_f32<TG>(q_gain[e0 + i]); gk[i] = to_f32<TG>(k_gain[e0 + i]); }
+    }
+    int page = -1;
+    if (flags & kFlagStore) page = block_table[(size_t)slot * max_pages + pos / page_size];
+    __syncthreads();
+    T* row = qkv + (size_t)t * heads_total * HD;
+    for (int head = warp; head < heads_total; head += warps) {
+        const bool is_q = head < q_heads, is_k = !is_q && head < q_heads + kv_heads;
+        T* src = row + (size_t)head * HD + e0;
+        float x[VEC];
+        VecIO<T, VEC>::load(src, x);
+        if ((is_q || is_k) && (flags & kFlagNorm)) {
+            float ss = 0.0f;
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) ss += x[i] * x[i];
+            ss = warp_sum(ss);
+            const float scale = 1.0f / sqrtf(ss / (float)HD + eps);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) x[i] = (is_q ? gq[i] : gk[i]) * x[i] * scale;
+        }
+        if ((is_q || is_k) && rope) {
+            const bool low = lane < 16;
+            const int f0 = low ? e0 : e0 - HALF;
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) {
+                const float other = __shfl_xor_sync(0xffffffffu, x[i], 16);
+                const float c = cs[f0 + i], s = sn[f0 + i];
+                x[i] = low ? x[i] * c - other * s : other * s + x[i] * c;
+            }
+        }
+        if (is_q) {
+            if (flags & kFlagQOut) VecIO<T, VEC>::store(q_out + ((size_t)t * q_heads + head) * HD + e0, x);
+        } else {
+            if ((flags & kFlagStore) && page >= 0) {
+                const int kvh = is_k ? head - q_heads : head - q_heads - kv_heads;
+                T* dst = cache + ((((size_t)page * 2 + (is_k ? 0 : 1)) * kv_heads + kvh) * page_size +
+                                  (pos % page_size)) * HD + e0;
+                VecIO<T, VEC>::store(dst, x);
+            }
+            if (flags & kFlagKvOut) VecIO<T, VEC>::store(src, x);
+        }
+    }
+}
+
 }  // namespace tllm
 
 using namespace tllm;
@@ -112,6 +235,32 @@ extern "C" int tllm_qk_norm_rope_store(
     TLLM_REQUIRE(!(flags & kFlagQOut) || q_out, "qk_norm_rope_store: no query output");
     TLLM_REQUIRE(gain_dtype == kBF16 || gain_dtype == kF32, "qk_norm_rope_store: unknown gain dtype");
     if (tokens == 0) return 0;
+    const bool whole_rotation = !(flags & kFlagRope) || rotary_dim == head_dim;
+    const auto al = [](const void* p, int bytes) { return (reinterpret_cast<uintptr_t>(p) & (bytes - 1)) == 0; };
+    if (whole_rotation && (head_dim == 64 || head_dim == 128 || head_dim == 256)) {
+        const int need = dtype == kBF16 ? (head_dim / 32) * 2 : 8;     // widest access of the vector form
+        if (al(qkv, need) && al(cache, need) && al(q_out, need) && (dtype == kBF16 || dtype == kF32)) {
+            const int vblock = 256;
+#define VLAUNCH(T, TG, VEC)                                                                         \
+    qk_norm_rope_store_vec_kernel<T, TG, VEC><<<tokens, vblock, 0, stream>>>(                       \
+        (T*)qkv, (const TG*)q_gain, (const TG*)k_gain, eps, inv_freq, positions, token_slot,        \
+        block_table, max_pages, (T*)cache, page_size, (T*)q_out, q_heads, kv_heads, flags)
+#define VDISPATCH(T, TG)                                              \
+    do {                                                              \
+        if (head_dim == 64) VLAUNCH(T, TG, 2);                        \
+        else if (head_dim == 128) VLAUNCH(T, TG, 4);                  \
+        else VLAUNCH(T, TG, 8);                                       \
+    } while (0)
+            if (dtype == kBF16) {
+                if (gain_dtype == kBF16) VDISPATCH(bf16, bf16); else VDISPATCH(bf16, float);
+            } else {
+                if (gain_dtype == kBF16) VDISPATCH(float, bf16); else VDISPATCH(float, float);
+            }
+#undef VDISPATCH
+#undef VLAUNCH
+            return finish_launch("qk_norm_rope_store");
+        }
+    }
     const int warps = 4, block = warps * 32;
     const long long units = (long long)tokens * (q_heads + 2 * kv_heads);
     const int grid = (int)((units + warps - 1) / warps);

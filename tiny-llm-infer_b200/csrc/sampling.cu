@@ -56,10 +56,56 @@ __device__ __forceinline__ Best block_best(Best v, Best* scratch) {
     return r;
 }
 
+// Two-stage form for greedy and temperature rows: `blocks_per_row` blocks share a row's
+// vocabulary, each leaves its best candidate in `partial`, and a second small kernel picks
+// among them (same comparison rule, so the result is that of the one-block form).  Rows
+// with top_p < 1 are left to the one-block kernel below.
+__global__ void sample_partial_kernel(const float* __restrict__ logits, int vocab, long long row_stride,
+                                      const float* __restrict__ params,
+                                      const unsigned long long* __restrict__ seeds,
+                                      Best* __restrict__ partial, int blocks_per_row) {
+    __shared__ Best best_scratch[32];
+    const int row = blockIdx.y, b = blockIdx.x;
+    const float temperature = params[2 * row], top_p = params[2 * row + 1];
+    const bool greedy = !(temperature > 1.0e-6f);
+    if (!greedy && top_p < 1.0f) return;
+    const float* lg = logits + (size_t)row * row_stride;
+    const uint64_t seed = seeds[row];
+    const int chunk = (vocab + blocks_per_row - 1) / blocks_per_row;
+    const int v0 = b * chunk, v1 = min(vocab, v0 + chunk);
+    Best local{-FLT_MAX, INT32_MAX};
+    if (greedy) {
+        for (int v = v0 + threadIdx.x; v < v1; v += blockDim.x) local = better(local, Best{lg[v], v});
+    } else {
+        for (int v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
+            const float g = -logf(-logf(uniform_of(seed, v)));
+            local = better(local, Best{lg[v] + temperature * g, v});
+        }
+    }
+    local = block_best(local, best_scratch);
+    if (threadIdx.x == 0) partial[(size_t)row * blocks_per_row + b] = local;
+}
+
+__global__ void sample_final_kernel(const Best* __restrict__ partial, int blocks_per_row,
+                                    const float* __restrict__ params, int* __restrict__ out) {
+    __shared__ Best best_scratch[32];
+    const int row = blockIdx.x;
+    const float temperature = params[2 * row], top_p = params[2 * row + 1];
+    if (temperature > 1.0e-6f && top_p < 1.0f) return;
+    Best local{-FLT_MAX, INT32_MAX};
+    for (int b = threadIdx.x; b < blocks_per_row; b += blockDim.x)
+        local = better(local, partial[(size_t)row * blocks_per_row + b]);
+    local = block_best(local, best_scratch);
+    if (threadIdx.x == 0) out[row] = local.token;
+}
+
 // One block per row.  params[row] = {temperature, top_p}; seeds[row] is the 64-bit key.
+// With `only_nucleus` rows that are greedy or have top_p == 1 are skipped (the two-stage
+// kernels above have done them).
 __global__ void sample_kernel(const float* __restrict__ logits, int vocab, long long row_stride,
                               const float* __restrict__ params,
-                              const unsigned long long* __restrict__ seeds, int* __restrict__ out) {
+                              const unsigned long long* __restrict__ seeds, int* __restrict__ out,
+                              int only_nucleus) {
     __shared__ Best best_scratch[32];
     __shared__ float sum_scratch[32];
     const int row = blockIdx.x;
@@ -67,6 +113,7 @@ __global__ void sample_kernel(const float* __restrict__ logits, int vocab, long 
     const float temperature = params[2 * row], top_p = params[2 * row + 1];
     const uint64_t seed = seeds[row];
     const bool greedy = !(temperature > 1.0e-6f);
+    if (only_nucleus && (greedy || !(top_p < 1.0f))) return;
 
     Best local{-FLT_MAX, INT32_MAX};
     if (greedy) {
@@ -127,7 +174,28 @@ extern "C" int tllm_sample(const float* logits, int rows, int vocab, long long r
     TLLM_REQUIRE(rows >= 0 && vocab > 0 && row_stride >= vocab, "sample: bad sizes");
     if (rows == 0) return 0;
     const int block = vocab >= 8192 ? 1024 : 256;
-    sample_kernel<<<rows, block, 0, stream>>>(logits, vocab, row_stride, params, seeds, out);
+    sample_kernel<<<rows, block, 0, stream>>>(logits, vocab, row_stride, params, seeds, out, 0);
+    return finish_launch("sample");
+}
+
+// The same result with the vocabulary of a row shared by `blocks_per_row` blocks.
+// `partial` is scratch of rows * blocks_per_row * 8 bytes.  `any_nucleus` tells whether some
+// row has temperature > 1e-6 and top_p < 1 (those rows need the one-block kernel).
+extern "C" int tllm_sample_split(const float* logits, int rows, int vocab, long long row_stride,
+                                 const float* params, const unsigned long long* seeds, int* out,
+                                 void* partial, int blocks_per_row, int any_nucleus, cudaStream_t stream) {
+    TLLM_REQUIRE(rows >= 0 && vocab > 0 && row_stride >= vocab, "sample: bad sizes");
+    TLLM_REQUIRE(partial != nullptr && blocks_per_row >= 1 && blocks_per_row <= 1024 && rows <= 65535,
+                 "sample: bad split");
+    if (rows == 0) return 0;
+    sample_partial_kernel<<<dim3(blocks_per_row, rows), 256, 0, stream>>>(
+        logits, vocab, row_stride, params, seeds, (Best*)partial, blocks_per_row);
+    int rc = finish_launch("sample_partial");
+    if (rc) return rc;
+    sample_final_kernel<<<rows, 64, 0, stream>>>((const Best*)partial, blocks_per_row, params, out);
+    rc = finish_launch("sample_final");
+    if (rc || !any_nucleus) return rc;
+    sample_kernel<<<rows, vocab >= 8192 ? 1024 : 256, 0, stream>>>(logits, vocab, row_stride, params, seeds, out, 1);
     return finish_launch("sample");
 }
 

@@ -67,6 +67,7 @@ def _declare(h) -> None:
         "tllm_paged_attention_general": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32,
                                          i32, f32, vp, vp],
         "tllm_sample": [vp, i32, i32, i64, vp, vp, vp, vp],
+        "tllm_sample_split": [vp, i32, i32, i64, vp, vp, vp, vp, i32, i32, vp],
         "tllm_paged_attention_decode": [vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32,
                                         i32, vp, vp, vp, vp],
         "tllm_paged_attention_prefill": [vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32, vp, vp],
@@ -177,12 +178,19 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_gain, k_gain, eps: float, inv_freq, 
 _workspaces = {}
 
 
+WORKSPACE_FLOATS = 16 << 20
+
+
 def workspace(device, floats: int) -> torch.Tensor:
-    """Float32 scratch that lives as long as the process (grown when a call needs more)."""
+    """Float32 scratch for one call.  Up to WORKSPACE_FLOATS it is one buffer per device
+    that lives as long as the process and never moves (captured CUDA graphs keep its
+    address); a larger request gets a tensor of its own."""
+    if floats > WORKSPACE_FLOATS:
+        return torch.empty(floats, dtype=torch.float32, device=device)
     key = str(device)
     buf = _workspaces.get(key)
-    if buf is None or buf.numel() < floats:
-        buf = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
+    if buf is None:
+        buf = torch.empty(WORKSPACE_FLOATS, dtype=torch.float32, device=device)
         _workspaces[key] = buf
     return buf
 
@@ -262,13 +270,23 @@ def paged_attention(q: torch.Tensor, cache: torch.Tensor, positions, token_slot,
 
 
 def sample(logits: torch.Tensor, params: torch.Tensor, seeds: torch.Tensor,
-           out: torch.Tensor) -> torch.Tensor:
+           out: torch.Tensor, any_nucleus: Optional[bool] = None) -> torch.Tensor:
     """Token per row of float32 ``logits`` [S, V]: params[s] = (temperature, top_p), seeds[s]
-    an int64 key.  temperature <= 1e-6 is argmax (lowest id on ties)."""
+    an int64 key.  temperature <= 1e-6 is argmax (lowest id on ties).  ``any_nucleus`` says
+    whether some row samples with top_p < 1 (None: not known, assume so)."""
     _cuda(logits, params, seeds, out)
     assert logits.dtype == torch.float32 and params.dtype == torch.float32
     assert seeds.dtype == torch.int64 and out.dtype == torch.int32
     rows, vocab = logits.shape
+    if vocab >= 4096 and rows > 0:
+        # a row's vocabulary shared by several blocks; rows with top-p take the one-block kernel
+        blocks = min(64, -(-vocab // 2048))
+        partial = torch.empty((rows, blocks, 2), dtype=torch.float32, device=logits.device)
+        nucleus = 1 if any_nucleus is None else int(any_nucleus)
+        _check(lib().tllm_sample_split(_p(logits), rows, vocab, logits.stride(0), _p(params), _p(seeds),
+                                       _p(out), _p(partial), blocks, nucleus, _stream()), "sample",
+               kernels=2 + nucleus)
+        return out
     _check(lib().tllm_sample(_p(logits), rows, vocab, logits.stride(0), _p(params), _p(seeds),
                              _p(out), _stream()), "sample")
     return out

@@ -60,5 +60,6 @@ class Sampler:
             self._seeds_host[i] = _signed(key & _M)
         self._params[:n].copy_(self._params_host[:n], non_blocking=True)
         self._seeds[:n].copy_(self._seeds_host[:n], non_blocking=True)
-        ops.sample(logits, self._params[:n], self._seeds[:n], self._out[:n])
+        nucleus = any(temp > 1e-6 and top_p < 1.0 for temp, top_p, _ in rows)
+        ops.sample(logits, self._params[:n], self._seeds[:n], self._out[:n], any_nucleus=nucleus)
         return self._out[:n].cpu().tolist()
