@@ -400,3 +400,25 @@ def test_fast_attention_refuses_other_shapes(ops):
             ops.paged_attention_decode(q, cache, z, z, None, 1, table, ps, nh, nkv, hd, None, 1.0,
                                        torch.empty_like(q), 1, splits=1)
     assert not ops.fast_attention_ok(torch.float32, 16, 4, 2, 64)
+
+
+@pytest.mark.parametrize("M", [1, 2, 7, 8, 9, 16, 17, 32])
+@pytest.mark.parametrize("N,K", [(200, 96), (1000, 1000), (77, 4104), (4096, 264)])
+def test_gemm_skinny(ops, M, N, K):
+    """The weight-streaming product for few rows: widths that are no multiple of the 16-row
+    tile or of the 32-wide k-block, one weight row much larger than the rest (a wrong row or
+    a dropped k-block would show)."""
+    x = rnd(M, K, seed=300 + M).to(torch.bfloat16)
+    w = rnd(N, K, seed=301, scale=0.1).to(torch.bfloat16)
+    w[N - 1] *= 30
+    w[5, K - 3:] = 4.0
+    want = x.double() @ w.double().T
+    for out_dtype, bound in ((torch.float32, 2e-3), (torch.bfloat16, 1.6e-2)):
+        y = ops.gemm_skinny(dev(x), dev(w), out_dtype)
+        assert y.dtype == out_dtype and y.shape == (M, N)
+        assert (y.cpu().double() - want).abs().max() < bound * want.abs().max()
+    # linear() takes this path for bfloat16 and agrees with the library path on more rows
+    y16 = ops.linear(dev(x), dev(w), out_dtype=torch.float32)
+    assert (y16.cpu().double() - want).abs().max() < 2e-3 * want.abs().max()
+    with pytest.raises(ops.KernelError, match="multiple of 8"):
+        ops.gemm_skinny(dev(x[:, :K - 4].contiguous()), dev(w[:, :K - 4].contiguous()), torch.float32)

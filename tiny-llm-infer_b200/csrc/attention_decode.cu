@@ -33,6 +33,7 @@ paged_attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict
                               float scale_log2e, int splits, float* __restrict__ part_o,
                               float* __restrict__ part_ml, bf16* __restrict__ out) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
+    TLLM_PDL_ENTER();
     constexpr int kChunks = HD / 8;                 // 16-byte chunks per row
     constexpr int kTileBytes = kTileKeys * HD * 2;  // one K or V tile
     const int split = blockIdx.x, g = blockIdx.y, ridx = blockIdx.z;
@@ -230,6 +231,7 @@ __global__ void paged_attention_combine_kernel(const float* __restrict__ part_o,
                                                const int* __restrict__ token_slot,
                                                const int* __restrict__ rows, int q_heads, int splits,
                                                bf16* __restrict__ out) {
+    TLLM_PDL_ENTER();
     const int ridx = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
     const int r = rows ? rows[ridx] : ridx;
     bf16* dst = out + ((size_t)r * q_heads + head) * HD;
@@ -261,13 +263,13 @@ static int launch_decode(const void* q, const void* cache, const int* positions,
         configured = true;
     }
     const dim3 grid(splits, kv_heads, n_rows);
-    paged_attention_decode_kernel<HD><<<grid, kDecWarps * 32, smem, stream>>>(
+    launch_pdl(paged_attention_decode_kernel<HD>, grid, dim3(kDecWarps * 32), smem, stream,
         (const bf16*)q, (const bf16*)cache, positions, token_slot, rows, block_table, max_pages, page_size,
         q_heads, kv_heads, window, scale * 1.4426950408889634f, splits, part_o, part_ml, (bf16*)out);
     int rc = finish_launch("paged_attention_decode");
     if (rc != 0 || splits == 1) return rc;
-    paged_attention_combine_kernel<HD><<<dim3(n_rows, q_heads), HD, 0, stream>>>(
-        part_o, part_ml, token_slot, rows, q_heads, splits, (bf16*)out);
+    launch_pdl(paged_attention_combine_kernel<HD>, dim3(n_rows, q_heads), dim3(HD), 0, stream,
+        (const float*)part_o, (const float*) part_ml, token_slot, rows, q_heads, splits, (bf16*)out);
     return finish_launch("paged_attention_combine");
 }
 

@@ -31,6 +31,7 @@ paged_attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restric
                                int q_heads, int kv_heads, int window, float scale_log2e,
                                bf16* __restrict__ out) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
+    TLLM_PDL_ENTER();
     constexpr int kChunks = HD / 8;
     constexpr int kTileBytes = kBN * HD * 2;
     const int seg = tiles[2 * blockIdx.x], q_off = tiles[2 * blockIdx.x + 1];
@@ -200,7 +201,7 @@ static int launch_prefill(const void* q, const void* cache, const int* seg_info,
         if (e != cudaSuccess) { set_error("paged_attention_prefill: %s", cudaGetErrorString(e)); return (int)e; }
         configured = true;
     }
-    paged_attention_prefill_kernel<HD><<<dim3(n_tiles, q_heads), kPfWarps * 32, smem, stream>>>(
+    launch_pdl(paged_attention_prefill_kernel<HD>, dim3(n_tiles, q_heads), dim3(kPfWarps * 32), smem, stream,
         (const bf16*)q, (const bf16*)cache, seg_info, tiles, block_table, max_pages, page_size, q_heads,
         kv_heads, window, scale * 1.4426950408889634f, (bf16*)out);
     return finish_launch("paged_attention_prefill");

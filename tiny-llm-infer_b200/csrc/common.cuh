@@ -46,6 +46,36 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     return warp_sum(r);
 }
 
+// Programmatic dependent launch.  A kernel launched with `launch_pdl` may be scheduled while
+// the kernel before it in the stream is still running; it must execute TLLM_PDL_ENTER()
+// (or TLLM_PDL_WAIT() after a prologue that touches nothing an earlier kernel writes or
+// reads) before its first access to memory that earlier kernels produce or still read.
+// Kernels that are a few microseconds long, as in a decode step, then no longer pay their
+// launch and ramp-up one after the other.
+#define TLLM_PDL_TRIGGER() asm volatile("griddepcontrol.launch_dependents;\n" ::)
+#define TLLM_PDL_WAIT() asm volatile("griddepcontrol.wait;\n" ::: "memory")
+#define TLLM_PDL_ENTER() \
+    do {                 \
+        TLLM_PDL_TRIGGER(); \
+        TLLM_PDL_WAIT();    \
+    } while (0)
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Host side: the last error text of this thread's most recent failing entry point.
 void set_error(const char* fmt, ...);
 

@@ -73,6 +73,7 @@ template <> struct Vec8<bf16> {
 template <typename TW>
 __global__ void embedding_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
                                  float* __restrict__ out, int hidden, int vocab) {
+    TLLM_PDL_ENTER();
     const int t = blockIdx.x;
     int id = ids[t];
     float* dst = out + (size_t)t * hidden;
@@ -88,6 +89,7 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const TW* __restri
 template <typename TW>
 __global__ void embedding_vec_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
                                      float* __restrict__ out, int hidden, int vocab) {
+    TLLM_PDL_ENTER();
     const int t = blockIdx.x;
     int id = ids[t];
     float* dst = out + (size_t)t * hidden;
@@ -112,6 +114,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
                                    TO* __restrict__ out, const int* __restrict__ rows,
                                    int width) {
     __shared__ float scratch[32];
+    TLLM_PDL_ENTER();
     const int o = blockIdx.x;
     const int r = rows ? rows[o] : o;
     TO* dst = out + (size_t)o * width;
@@ -145,6 +148,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restri
                                        const TG* __restrict__ gain, float eps, TO* __restrict__ out,
                                        const int* __restrict__ rows, int width) {
     __shared__ float scratch[32];
+    TLLM_PDL_ENTER();
     const int o = blockIdx.x;
     const int r = rows ? rows[o] : o;
     TO* dst = out + (size_t)o * width;
@@ -199,6 +203,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restri
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter,
                               size_t total) {
+    TLLM_PDL_ENTER();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; idx < total; idx += stride) {
@@ -212,6 +217,7 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
 template <typename T>
 __global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter,
                                   size_t total_chunks) {
+    TLLM_PDL_ENTER();
     const int per_row = inter >> 3;
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -251,16 +257,16 @@ static int launch_add_rmsnorm_typed(float* h, const void* delta, const void* gai
         while (block < 1024 && block < chunks) block *= 2;
         const int per_thread = (chunks + block - 1) / block;
 #define VEC_LAUNCH(C)                                                                 \
-    add_rmsnorm_vec_kernel<TD, TG, TO, C><<<n_out, block, 0, stream>>>(               \
-        h, (const TD*)delta, (const TG*)gain, eps, (TO*)out, rows, width)
+    launch_pdl(add_rmsnorm_vec_kernel<TD, TG, TO, C>, dim3(n_out), dim3(block), 0, stream, \
+               h, (const TD*)delta, (const TG*)gain, eps, (TO*)out, rows, width)
         if (per_thread <= 1) VEC_LAUNCH(1);
         else if (per_thread <= 2) VEC_LAUNCH(2);
         else VEC_LAUNCH(4);
 #undef VEC_LAUNCH
     } else {
         const int block = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
-        add_rmsnorm_kernel<TD, TG, TO><<<n_out, block, 0, stream>>>(
-            h, (const TD*)delta, (const TG*)gain, eps, (TO*)out, rows, width);
+        launch_pdl(add_rmsnorm_kernel<TD, TG, TO>, dim3(n_out), dim3(block), 0, stream,
+                   h, (const TD*)delta, (const TG*)gain, eps, (TO*)out, rows, width);
     }
     return finish_launch("add_rmsnorm");
 }
@@ -290,11 +296,11 @@ int tllm_embedding(const int* ids, const void* table, int table_dtype, float* ou
     const bool vec = hidden % 8 == 0 && aligned16(table) && aligned16(out);
     const int block = vec ? (hidden >= 2048 ? 256 : 128) : (hidden >= 1024 ? 256 : 128);
     if (table_dtype == kBF16) {
-        if (vec) embedding_vec_kernel<bf16><<<tokens, block, 0, stream>>>(ids, (const bf16*)table, out, hidden, vocab);
-        else embedding_kernel<bf16><<<tokens, block, 0, stream>>>(ids, (const bf16*)table, out, hidden, vocab);
+        if (vec) launch_pdl(embedding_vec_kernel<bf16>, dim3(tokens), dim3(block), 0, stream, ids, (const bf16*)table, out, hidden, vocab);
+        else launch_pdl(embedding_kernel<bf16>, dim3(tokens), dim3(block), 0, stream, ids, (const bf16*)table, out, hidden, vocab);
     } else {
-        if (vec) embedding_vec_kernel<float><<<tokens, block, 0, stream>>>(ids, (const float*)table, out, hidden, vocab);
-        else embedding_kernel<float><<<tokens, block, 0, stream>>>(ids, (const float*)table, out, hidden, vocab);
+        if (vec) launch_pdl(embedding_vec_kernel<float>, dim3(tokens), dim3(block), 0, stream, ids, (const float*)table, out, hidden, vocab);
+        else launch_pdl(embedding_kernel<float>, dim3(tokens), dim3(block), 0, stream, ids, (const float*)table, out, hidden, vocab);
     }
     return finish_launch("embedding");
 }
@@ -325,15 +331,15 @@ int tllm_swiglu(const void* gate_up, void* out, int dtype, int tokens, int inter
         const size_t chunks = total / 8;
         const int grid = grid_for(chunks, block);
         if (dtype == kBF16)
-            swiglu_vec_kernel<bf16><<<grid, block, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter, chunks);
+            launch_pdl(swiglu_vec_kernel<bf16>, dim3(grid), dim3(block), 0, stream, (const bf16*)gate_up, (bf16*)out, inter, chunks);
         else
-            swiglu_vec_kernel<float><<<grid, block, 0, stream>>>((const float*)gate_up, (float*)out, inter, chunks);
+            launch_pdl(swiglu_vec_kernel<float>, dim3(grid), dim3(block), 0, stream, (const float*)gate_up, (float*)out, inter, chunks);
     } else {
         const int grid = grid_for(total, block);
         if (dtype == kBF16)
-            swiglu_kernel<bf16><<<grid, block, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter, total);
+            launch_pdl(swiglu_kernel<bf16>, dim3(grid), dim3(block), 0, stream, (const bf16*)gate_up, (bf16*)out, inter, total);
         else
-            swiglu_kernel<float><<<grid, block, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
+            launch_pdl(swiglu_kernel<float>, dim3(grid), dim3(block), 0, stream, (const float*)gate_up, (float*)out, inter, total);
     }
     return finish_launch("swiglu");
 }

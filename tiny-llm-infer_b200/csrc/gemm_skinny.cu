@@ -1,0 +1,183 @@
+// y[M, N] = x[M, K] . W[N, K]^T for a handful of rows (M <= 32), bfloat16 in, float32
+// accumulation: the product of a decode step, where every weight is read once and the time
+// is the time HBM needs to deliver the weights.
+//
+// The reference has a one-row kernel for this (matmul_fp16_gemv_kernel,
+// kernels/src/matmul_kernel_cuda.cu:17-32: one block per output, scalar half loads) and
+// falls back to the library for two rows and more.  Here a block owns 16 rows of W and its
+// eight warps split K.  A lane reads 16 contiguous bytes of a weight row at a time with a
+// streaming load and feeds them to mma.sync m16n8k16 with W as the A operand (16 weight
+// rows) and the activations as the B operand (8 tokens per tile): because a sum does not
+// care about the order of its terms, the eight neighbouring k's of a lane can stand for the
+// k-columns the fragment layout assigns to it, in two mma steps, provided the activations
+// are permuted the same way, which a 16-byte load of x does by itself.  No shared memory,
+// no shuffles on the way in; loads of the next k-blocks are in flight while the current
+// ones are multiplied; the warps' partial sums meet in shared memory at the end and are
+// added in warp order.
+//
+// The kernel is launched with programmatic dependent launch: it may start while the kernel
+// before it in the stream is still draining, fetches its first weights (which depend on
+// nothing), and only then waits for that kernel's results (griddepcontrol.wait) before it
+// touches the activations or writes anything.
+#include "common.cuh"
+#include "mma_tiles.cuh"
+
+namespace tllm {
+
+constexpr int kSkinnyWarps = 8;
+constexpr int kSkinnyUnroll = 2;      // k-blocks of 32 per pipeline stage
+
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.cs.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+template <int NT>
+struct SkinnyStage {
+    uint4 a_lo[kSkinnyUnroll], a_hi[kSkinnyUnroll], b[kSkinnyUnroll][NT];
+};
+
+template <int NT, typename TOut>
+__global__ void __launch_bounds__(kSkinnyWarps * 32)
+skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __restrict__ y, int M,
+                   int N, int K) {
+    __shared__ float red[kSkinnyWarps][16][NT * 8 + 1];
+    asm volatile("griddepcontrol.launch_dependents;\n" ::);
+    const int r0 = blockIdx.x * 16;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, c = lane & 3, rq = lane >> 2;
+    const bf16* w_lo = w + (size_t)min(r0 + rq, N - 1) * K;
+    const bf16* w_hi = w + (size_t)min(r0 + rq + 8, N - 1) * K;
+    const bf16* xr[NT];
+    bool xv[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        const int tok = nt * 8 + rq;
+        xv[nt] = tok < M;
+        xr[nt] = x + (size_t)(xv[nt] ? tok : 0) * K;
+    }
+    float acc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
+
+    const int kblocks = (K + 31) >> 5;                       // 32 k per block: 8 per lane of a quad
+    const int per_warp = (kblocks + kSkinnyWarps - 1) / kSkinnyWarps;
+    const int kb0 = warp * per_warp, kb1 = min(kblocks, kb0 + per_warp);
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+
+    auto load_w = [&](SkinnyStage<NT>& s, int kb) {
+#pragma unroll
+        for (int u = 0; u < kSkinnyUnroll; ++u) {
+            const int k = (kb + u) * 32 + c * 8;
+            const bool ok = kb + u < kb1 && k < K;
+            s.a_lo[u] = ok ? ld_stream(w_lo + k) : zero;
+            s.a_hi[u] = ok ? ld_stream(w_hi + k) : zero;
+        }
+    };
+    auto load_x = [&](SkinnyStage<NT>& s, int kb) {
+#pragma unroll
+        for (int u = 0; u < kSkinnyUnroll; ++u) {
+            const int k = (kb + u) * 32 + c * 8;
+            const bool ok = kb + u < kb1 && k < K;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+                s.b[u][nt] = (ok && xv[nt]) ? __ldg(reinterpret_cast<const uint4*>(xr[nt] + k)) : zero;
+        }
+    };
+    auto multiply = [&](const SkinnyStage<NT>& s) {
+#pragma unroll
+        for (int u = 0; u < kSkinnyUnroll; ++u) {
+            const uint32_t a1[4] = {s.a_lo[u].x, s.a_hi[u].x, s.a_lo[u].y, s.a_hi[u].y};
+            const uint32_t a2[4] = {s.a_lo[u].z, s.a_hi[u].z, s.a_lo[u].w, s.a_hi[u].w};
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const uint32_t b1[2] = {s.b[u][nt].x, s.b[u][nt].y}, b2[2] = {s.b[u][nt].z, s.b[u][nt].w};
+                mma_bf16_16816(acc[nt], a1, b1);
+                mma_bf16_16816(acc[nt], a2, b2);
+            }
+        }
+    };
+
+    SkinnyStage<NT> s0, s1, s2;
+    load_w(s0, kb0);                                         // weights depend on no earlier kernel
+    load_w(s1, kb0 + kSkinnyUnroll);
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");     // from here on x may be read, y written
+    load_x(s0, kb0);
+    load_x(s1, kb0 + kSkinnyUnroll);
+    for (int kb = kb0; kb < kb1; kb += 3 * kSkinnyUnroll) {
+        load_w(s2, kb + 2 * kSkinnyUnroll);
+        load_x(s2, kb + 2 * kSkinnyUnroll);
+        multiply(s0);
+        load_w(s0, kb + 3 * kSkinnyUnroll);
+        load_x(s0, kb + 3 * kSkinnyUnroll);
+        multiply(s1);
+        load_w(s1, kb + 4 * kSkinnyUnroll);
+        load_x(s1, kb + 4 * kSkinnyUnroll);
+        multiply(s2);
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        red[warp][rq][nt * 8 + c * 2] = acc[nt][0];
+        red[warp][rq][nt * 8 + c * 2 + 1] = acc[nt][1];
+        red[warp][rq + 8][nt * 8 + c * 2] = acc[nt][2];
+        red[warp][rq + 8][nt * 8 + c * 2 + 1] = acc[nt][3];
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < 16 * NT * 8; idx += blockDim.x) {
+        const int row = idx & 15, tok = idx >> 4;
+        if (tok < M && r0 + row < N) {
+            float s = 0.0f;
+#pragma unroll
+            for (int ww = 0; ww < kSkinnyWarps; ++ww) s += red[ww][row][tok];
+            y[(size_t)tok * N + r0 + row] = from_f32<TOut>(s);
+        }
+    }
+}
+
+template <int NT, typename TOut>
+static int launch_skinny(const void* x, const void* w, void* y, int M, int N, int K, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((N + 15) / 16);
+    cfg.blockDim = dim3(kSkinnyWarps * 32);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<NT, TOut>, (const bf16*)x, (const bf16*)w,
+                                       (TOut*)y, M, N, K);
+    if (e != cudaSuccess) {
+        set_error("gemm_skinny: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    return finish_launch("gemm_skinny");
+}
+
+}  // namespace tllm
+
+using namespace tllm;
+
+// out_dtype: storage type of y (bfloat16 or float32).  K must be a multiple of 8 and x, w
+// 16-byte aligned; M at most 32.
+extern "C" int tllm_gemm_skinny(const void* x, const void* w, void* y, int out_dtype, int M, int N, int K,
+                                cudaStream_t stream) {
+    TLLM_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_skinny: bad sizes");
+    TLLM_REQUIRE(M <= 32, "gemm_skinny: %d rows exceed 32", M);
+    TLLM_REQUIRE(K % 8 == 0, "gemm_skinny: K = %d is no multiple of 8", K);
+    TLLM_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15u) == 0,
+                 "gemm_skinny: operands must be 16-byte aligned");
+    TLLM_REQUIRE(out_dtype == kBF16 || out_dtype == kF32, "gemm_skinny: unknown output dtype");
+    if (M == 0) return 0;
+    if (out_dtype == kBF16) {
+        if (M <= 8) return launch_skinny<1, bf16>(x, w, y, M, N, K, stream);
+        if (M <= 16) return launch_skinny<2, bf16>(x, w, y, M, N, K, stream);
+        return launch_skinny<4, bf16>(x, w, y, M, N, K, stream);
+    }
+    if (M <= 8) return launch_skinny<1, float>(x, w, y, M, N, K, stream);
+    if (M <= 16) return launch_skinny<2, float>(x, w, y, M, N, K, stream);
+    return launch_skinny<4, float>(x, w, y, M, N, K, stream);
+}

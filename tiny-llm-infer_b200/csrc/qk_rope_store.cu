@@ -30,6 +30,7 @@ __global__ void qk_norm_rope_store_kernel(
     T* __restrict__ cache, int page_size, T* __restrict__ q_out, int tokens, int q_heads,
     int kv_heads, int head_dim, int flags) {
     extern __shared__ float smem[];  // one head vector per warp
+    TLLM_PDL_ENTER();
     const int warps_per_block = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads_total = q_heads + 2 * kv_heads;
@@ -156,6 +157,7 @@ __global__ void qk_norm_rope_store_vec_kernel(
     T* __restrict__ cache, int page_size, T* __restrict__ q_out, int q_heads, int kv_heads, int flags) {
     constexpr int HD = VEC * 32, HALF = HD / 2;
     __shared__ float cs[HALF], sn[HALF];
+    TLLM_PDL_ENTER();
     const int t = blockIdx.x;
     const int slot = token_slot[t];
     if (slot < 0) return;
@@ -242,7 +244,7 @@ extern "C" int tllm_qk_norm_rope_store(
         if (al(qkv, need) && al(cache, need) && al(q_out, need) && (dtype == kBF16 || dtype == kF32)) {
             const int vblock = 256;
 #define VLAUNCH(T, TG, VEC)                                                                         \
-    qk_norm_rope_store_vec_kernel<T, TG, VEC><<<tokens, vblock, 0, stream>>>(                       \
+    launch_pdl(qk_norm_rope_store_vec_kernel<T, TG, VEC>, dim3(tokens), dim3(vblock), 0, stream,   \
         (T*)qkv, (const TG*)q_gain, (const TG*)k_gain, eps, inv_freq, positions, token_slot,        \
         block_table, max_pages, (T*)cache, page_size, (T*)q_out, q_heads, kv_heads, flags)
 #define VDISPATCH(T, TG)                                              \
@@ -266,7 +268,7 @@ extern "C" int tllm_qk_norm_rope_store(
     const int grid = (int)((units + warps - 1) / warps);
     const size_t smem = (size_t)warps * head_dim * sizeof(float);
 #define LAUNCH(T, TG)                                                                            \
-    qk_norm_rope_store_kernel<T, TG><<<grid, block, smem, stream>>>(                             \
+    launch_pdl(qk_norm_rope_store_kernel<T, TG>, dim3(grid), dim3(block), smem, stream,          \
         (T*)qkv, (const TG*)q_gain, (const TG*)k_gain, eps, inv_freq, rotary_dim, positions,     \
         token_slot, block_table, max_pages, (T*)cache, page_size, (T*)q_out, tokens, q_heads,    \
         kv_heads, head_dim, flags)

@@ -65,6 +65,7 @@ __global__ void sample_partial_kernel(const float* __restrict__ logits, int voca
                                       const unsigned long long* __restrict__ seeds,
                                       Best* __restrict__ partial, int blocks_per_row) {
     __shared__ Best best_scratch[32];
+    TLLM_PDL_ENTER();
     const int row = blockIdx.y, b = blockIdx.x;
     const float temperature = params[2 * row], top_p = params[2 * row + 1];
     const bool greedy = !(temperature > 1.0e-6f);
@@ -89,6 +90,7 @@ __global__ void sample_partial_kernel(const float* __restrict__ logits, int voca
 __global__ void sample_final_kernel(const Best* __restrict__ partial, int blocks_per_row,
                                     const float* __restrict__ params, int* __restrict__ out) {
     __shared__ Best best_scratch[32];
+    TLLM_PDL_ENTER();
     const int row = blockIdx.x;
     const float temperature = params[2 * row], top_p = params[2 * row + 1];
     if (temperature > 1.0e-6f && top_p < 1.0f) return;
@@ -188,11 +190,11 @@ extern "C" int tllm_sample_split(const float* logits, int rows, int vocab, long 
     TLLM_REQUIRE(partial != nullptr && blocks_per_row >= 1 && blocks_per_row <= 1024 && rows <= 65535,
                  "sample: bad split");
     if (rows == 0) return 0;
-    sample_partial_kernel<<<dim3(blocks_per_row, rows), 256, 0, stream>>>(
+    launch_pdl(sample_partial_kernel, dim3(blocks_per_row, rows), dim3(256), 0, stream,
         logits, vocab, row_stride, params, seeds, (Best*)partial, blocks_per_row);
     int rc = finish_launch("sample_partial");
     if (rc) return rc;
-    sample_final_kernel<<<rows, 64, 0, stream>>>((const Best*)partial, blocks_per_row, params, out);
+    launch_pdl(sample_final_kernel, dim3(rows), dim3(64), 0, stream, (const Best*)partial, blocks_per_row, params, out);
     rc = finish_launch("sample_final");
     if (rc || !any_nucleus) return rc;
     sample_kernel<<<rows, vocab >= 8192 ? 1024 : 256, 0, stream>>>(logits, vocab, row_stride, params, seeds, out, 1);

@@ -68,6 +68,7 @@ def _declare(h) -> None:
                                          i32, f32, vp, vp],
         "tllm_sample": [vp, i32, i32, i64, vp, vp, vp, vp],
         "tllm_sample_split": [vp, i32, i32, i64, vp, vp, vp, vp, i32, i32, vp],
+        "tllm_gemm_skinny": [vp, vp, vp, i32, i32, i32, i32, vp],
         "tllm_paged_attention_decode": [vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32,
                                         i32, vp, vp, vp, vp],
         "tllm_paged_attention_prefill": [vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32, vp, vp],
@@ -297,6 +298,22 @@ def uniform_of(seed: int, token: int) -> float:
     return float(lib().tllm_uniform_of(seed & 0xFFFFFFFFFFFFFFFF, token))
 
 
+SKINNY_MAX_ROWS = 8       # up to this many rows the weight-streaming product beats the library
+
+
+def gemm_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """y = x . weight^T for at most 32 bfloat16 rows: every weight is read once, straight from
+    HBM into tensor-core fragments (csrc/gemm_skinny.cu)."""
+    _cuda(x, weight)
+    rows, k = x.shape
+    n = weight.shape[0]
+    assert weight.shape[1] == k and x.dtype == weight.dtype == torch.bfloat16
+    y = torch.empty((rows, n), dtype=out_dtype, device=x.device)
+    _check(lib().tllm_gemm_skinny(_p(x), _p(weight), _p(y), _DT[out_dtype], rows, n, k, _stream()),
+           "gemm_skinny")
+    return y
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """y[T, N] = x[T, K] . weight[N, K]^T with float32 accumulation.  A weight kept in
     float32 is multiplied in float32 whatever the activations are stored in."""
@@ -310,6 +327,10 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
         return y if want == torch.float32 else cast(y, want)
     if x.dtype != weight.dtype:
         x = cast(x, weight.dtype)
+    rows, k = x.shape
+    if weight.dtype == torch.bfloat16 and 0 < rows <= SKINNY_MAX_ROWS and k % 8 == 0 \
+            and x.is_contiguous() and weight.is_contiguous() and want in _DT:
+        return gemm_skinny(x, weight, want)
     if want == weight.dtype:
         return torch.mm(x, weight.t())
     return torch.mm(x, weight.t(), out_dtype=want)
