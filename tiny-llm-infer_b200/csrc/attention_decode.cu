@@ -26,7 +26,7 @@ constexpr int kTileKeys = 16;
 
 template <int HD>
 __global__ void __launch_bounds__(kDecWarps * 32)
-paged_attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache,
+paged_attention_decode_kernel(const bf16* q, const bf16* cache,
                               const int* __restrict__ positions, const int* __restrict__ token_slot,
                               const int* __restrict__ rows, const int* __restrict__ block_table,
                               int max_pages, int page_size, int q_heads, int kv_heads, int window,
@@ -226,8 +226,7 @@ paged_attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict
 
 // out[row, head, :] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), splits in index order.
 template <int HD>
-__global__ void paged_attention_combine_kernel(const float* __restrict__ part_o,
-                                               const float* __restrict__ part_ml,
+__global__ void paged_attention_combine_kernel(const float* part_o, const float* part_ml,
                                                const int* __restrict__ token_slot,
                                                const int* __restrict__ rows, int q_heads, int splits,
                                                bf16* __restrict__ out) {

@@ -20,7 +20,7 @@ constexpr int kWarps = 4;
 
 template <typename T, int CHUNKS>
 __global__ void paged_attention_general_kernel(
-    const T* __restrict__ q, const T* __restrict__ cache, const int* __restrict__ positions,
+    const T* q, const T* cache, const int* __restrict__ positions,
     const int* __restrict__ token_slot, const int* __restrict__ block_table, int max_pages,
     int page_size, int q_heads, int kv_heads, int head_dim, int window, float scale,
     T* __restrict__ out) {

@@ -25,7 +25,7 @@ constexpr int kBN = 64;   // keys per tile
 
 template <int HD>
 __global__ void __launch_bounds__(kPfWarps * 32)
-paged_attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache,
+paged_attention_prefill_kernel(const bf16* q, const bf16* cache,
                                const int* __restrict__ seg_info, const int* __restrict__ tiles,
                                const int* __restrict__ block_table, int max_pages, int page_size,
                                int q_heads, int kv_heads, int window, float scale_log2e,

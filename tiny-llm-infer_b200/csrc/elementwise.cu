@@ -6,6 +6,10 @@
 // a float32 tensor that only this file's kernels write, so the residual sum and the
 // norm's mean are 32-bit in both storage modes.
 //
+// Pointers to what an earlier kernel of the step has written carry no __restrict__: with
+// programmatic dependent launch this kernel may start before that kernel ends, and the
+// read-only load path the compiler would otherwise choose may then return stale data.
+//
 // Every kernel has a vector form (16-byte loads and stores, eight elements per thread per
 // access, every load of a row issued before the first dependent instruction) for widths that
 // are multiples of eight, and a scalar form that takes any width.
@@ -109,7 +113,7 @@ __global__ void embedding_vec_kernel(const int* __restrict__ ids, const TW* __re
 // With `rows`: r = rows[o], h is left as it is (used for the last norm, on the rows
 // whose logits are wanted).  gain is read as float32 or bfloat16.
 template <typename TD, typename TG, typename TO>
-__global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ delta,
+__global__ void add_rmsnorm_kernel(float* h, const TD* delta,
                                    const TG* __restrict__ gain, float eps,
                                    TO* __restrict__ out, const int* __restrict__ rows,
                                    int width) {
@@ -144,7 +148,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
 // Vector form: the row lives in registers between the sum and the scaling, CHUNKS groups of
 // eight elements per thread (width <= blockDim * 8 * CHUNKS, width a multiple of 8).
 template <typename TD, typename TG, typename TO, int CHUNKS>
-__global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restrict__ delta,
+__global__ void add_rmsnorm_vec_kernel(float* h, const TD* delta,
                                        const TG* __restrict__ gain, float eps, TO* __restrict__ out,
                                        const int* __restrict__ rows, int width) {
     __shared__ float scratch[32];
@@ -201,7 +205,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restri
 // ---------------------------------------------------------------- SwiGLU
 // out[t, i] = silu(gu[t, i]) * gu[t, inter + i], silu(x) = x / (1 + exp(-x)), in float32.
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter,
+__global__ void swiglu_kernel(const T* gu, T* out, int inter,
                               size_t total) {
     TLLM_PDL_ENTER();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -215,7 +219,7 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
 }
 
 template <typename T>
-__global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter,
+__global__ void swiglu_vec_kernel(const T* gu, T* out, int inter,
                                   size_t total_chunks) {
     TLLM_PDL_ENTER();
     const int per_row = inter >> 3;

@@ -35,6 +35,18 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {
     return v;
 }
 
+// The activations were written by the kernel this one may have started beside: they are
+// read with an ordinary (coherent) load after the wait, never through the read-only path,
+// whose contract (data constant for the kernel's lifetime) an early start would break.
+__device__ __forceinline__ uint4 ld_coherent(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p)
+                 : "memory");
+    return v;
+}
+
 template <int NT>
 struct SkinnyStage {
     uint4 a_lo[kSkinnyUnroll], a_hi[kSkinnyUnroll], b[kSkinnyUnroll][NT];
@@ -83,7 +95,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut*
             const bool ok = kb + u < kb1 && k < K;
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt)
-                s.b[u][nt] = (ok && xv[nt]) ? __ldg(reinterpret_cast<const uint4*>(xr[nt] + k)) : zero;
+                s.b[u][nt] = (ok && xv[nt]) ? ld_coherent(xr[nt] + k) : zero;
         }
     };
     auto multiply = [&](const SkinnyStage<NT>& s) {

@@ -24,7 +24,7 @@ constexpr int kMaxHeadDim = 512;
 
 template <typename T, typename TG>
 __global__ void qk_norm_rope_store_kernel(
-    T* __restrict__ qkv, const TG* __restrict__ q_gain, const TG* __restrict__ k_gain, float eps,
+    T* qkv, const TG* __restrict__ q_gain, const TG* __restrict__ k_gain, float eps,
     const float* __restrict__ inv_freq, int rotary_dim, const int* __restrict__ positions,
     const int* __restrict__ token_slot, const int* __restrict__ block_table, int max_pages,
     T* __restrict__ cache, int page_size, T* __restrict__ q_out, int tokens, int q_heads,
@@ -151,7 +151,7 @@ template <int VEC> struct VecIO<float, VEC> {
 
 template <typename T, typename TG, int VEC>
 __global__ void qk_norm_rope_store_vec_kernel(
-    T* __restrict__ qkv, const TG* __restrict__ q_gain, const TG* __restrict__ k_gain, float eps,
+    T* qkv, const TG* __restrict__ q_gain, const TG* __restrict__ k_gain, float eps,
     const float* __restrict__ inv_freq, const int* __restrict__ positions,
     const int* __restrict__ token_slot, const int* __restrict__ block_table, int max_pages,
     T* __restrict__ cache, int page_size, T* __restrict__ q_out, int q_heads, int kv_heads, int flags) {

@@ -60,7 +60,7 @@ __device__ __forceinline__ Best block_best(Best v, Best* scratch) {
 // vocabulary, each leaves its best candidate in `partial`, and a second small kernel picks
 // among them (same comparison rule, so the result is that of the one-block form).  Rows
 // with top_p < 1 are left to the one-block kernel below.
-__global__ void sample_partial_kernel(const float* __restrict__ logits, int vocab, long long row_stride,
+__global__ void sample_partial_kernel(const float* logits, int vocab, long long row_stride,
                                       const float* __restrict__ params,
                                       const unsigned long long* __restrict__ seeds,
                                       Best* __restrict__ partial, int blocks_per_row) {
@@ -87,7 +87,7 @@ __global__ void sample_partial_kernel(const float* __restrict__ logits, int voca
     if (threadIdx.x == 0) partial[(size_t)row * blocks_per_row + b] = local;
 }
 
-__global__ void sample_final_kernel(const Best* __restrict__ partial, int blocks_per_row,
+__global__ void sample_final_kernel(const Best* partial, int blocks_per_row,
                                     const float* __restrict__ params, int* __restrict__ out) {
     __shared__ Best best_scratch[32];
     TLLM_PDL_ENTER();
