@@ -33,7 +33,7 @@ paged_attention_decode_kernel(const bf16* q, const bf16* cache,
                               float scale_log2e, int splits, float* __restrict__ part_o,
                               float* __restrict__ part_ml, bf16* __restrict__ out) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    TLLM_PDL_ENTER();
+    TLLM_PDL_TRIGGER();
     constexpr int kChunks = HD / 8;                 // 16-byte chunks per row
     constexpr int kTileBytes = kTileKeys * HD * 2;  // one K or V tile
     const int split = blockIdx.x, g = blockIdx.y, ridx = blockIdx.z;
@@ -42,6 +42,7 @@ paged_attention_decode_kernel(const bf16* q, const bf16* cache,
     const int group = q_heads / kv_heads;
     const int slot = token_slot[r];
     if (slot < 0) {
+        TLLM_PDL_WAIT();
         if (splits == 1)
             for (int i = threadIdx.x; i < group * HD; i += blockDim.x)
                 out[((size_t)r * q_heads + g * group) * HD + i] = __float2bfloat16_rn(0.0f);
@@ -57,18 +58,9 @@ paged_attention_decode_kernel(const bf16* q, const bf16* cache,
     const int k1 = min(pos + 1, k0 + per);
     const int lower = max(lo, k0), upper = k1 - 1;          // keys [lower, upper] count
 
-    // ---- query fragments: rows = query heads of the group
+    TLLM_PDL_WAIT();
+
     const int row_lo = lane >> 2, row_hi = row_lo + 8;
-    const bf16* qrow = q + ((size_t)r * q_heads + (size_t)g * group) * HD;
-    uint32_t qa[HD / 16][4];
-#pragma unroll
-    for (int ks = 0; ks < HD / 16; ++ks) {
-        const int c0 = ks * 16 + (lane & 3) * 2;
-        qa[ks][0] = row_lo < group ? *reinterpret_cast<const uint32_t*>(qrow + row_lo * HD + c0) : 0u;
-        qa[ks][1] = row_hi < group ? *reinterpret_cast<const uint32_t*>(qrow + row_hi * HD + c0) : 0u;
-        qa[ks][2] = row_lo < group ? *reinterpret_cast<const uint32_t*>(qrow + row_lo * HD + c0 + 8) : 0u;
-        qa[ks][3] = row_hi < group ? *reinterpret_cast<const uint32_t*>(qrow + row_hi * HD + c0 + 8) : 0u;
-    }
 
     float o[HD / 8][4];
 #pragma unroll
@@ -100,6 +92,19 @@ paged_attention_decode_kernel(const bf16* q, const bf16* cache,
 
     int tile = first_tile + warp;
     if (tile <= last_tile) issue(tile, 0);
+
+    // ---- query fragments (rows = query heads of the group), read while the first tile is on its way
+    const bf16* qrow = q + ((size_t)r * q_heads + (size_t)g * group) * HD;
+    uint32_t qa[HD / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+        const int c0 = ks * 16 + (lane & 3) * 2;
+        qa[ks][0] = row_lo < group ? *reinterpret_cast<const uint32_t*>(qrow + row_lo * HD + c0) : 0u;
+        qa[ks][1] = row_hi < group ? *reinterpret_cast<const uint32_t*>(qrow + row_hi * HD + c0) : 0u;
+        qa[ks][2] = row_lo < group ? *reinterpret_cast<const uint32_t*>(qrow + row_lo * HD + c0 + 8) : 0u;
+        qa[ks][3] = row_hi < group ? *reinterpret_cast<const uint32_t*>(qrow + row_hi * HD + c0 + 8) : 0u;
+    }
+
     for (int it = 0; tile <= last_tile; tile += kDecWarps, ++it) {
         const int stage = it & 1;
         if (tile + kDecWarps <= last_tile) {

@@ -5,6 +5,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 namespace tllm {
 
@@ -60,6 +61,16 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
         TLLM_PDL_WAIT();    \
     } while (0)
 
+// Whether `launch_pdl` really asks for the early start.  Measured on a decode step of a
+// Qwen3-8B-sized model: early starts pay for the kernels that have something to fetch before
+// they wait (the weight-streaming product); for the short element-wise kernels between them
+// an ordinary launch is faster as long as they still let their successor start early.  The
+// default is therefore off for the callers of this function; TLLM_PDL=1 switches it on.
+inline bool pdl_enabled() {
+    static const bool on = [] { const char* v = getenv("TLLM_PDL"); return v != nullptr && v[0] == '1'; }();
+    return on;
+}
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
                               cudaStream_t stream, Args... args) {
@@ -72,7 +83,7 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

@@ -202,8 +202,9 @@ SM_COUNT = 148
 def decode_splits(rows: int, kv_heads: int, max_context: int) -> int:
     """How many blocks share the keys of one (row, key/value head): enough blocks for
     about four per multiprocessor, each with at least 128 keys."""
-    want = -(-4 * SM_COUNT // max(rows * kv_heads, 1))
-    return max(1, min(want, -(-max_context // 128), 64))
+    by_length = -(-max_context // 1024)                       # about a thousand keys per block
+    by_count = -(-128 // max(rows * kv_heads, 1))             # but at least 128 blocks in all
+    return max(1, min(max(by_length, by_count), -(-max_context // 128), 64))
 
 
 def fast_attention_ok(dtype, page_size: int, q_heads: int, kv_heads: int, head_dim: int) -> bool:
