@@ -14,7 +14,7 @@ import torch
 from tiny_llm_infer_b200 import ops
 
 NAMES = ["embedding", "add_rmsnorm", "swiglu", "cast", "qk_norm_rope_store", "paged_attention",
-         "sample", "linear"]
+         "sample", "linear", "linear_swiglu"]
 
 
 def install(monkeypatch):
@@ -54,6 +54,12 @@ def cast(src, dtype):
 def linear(x, weight, out_dtype=None):
     want = out_dtype or x.dtype
     return (x.float() @ weight.float().t()).to(want)
+
+
+def linear_swiglu(x, w_gate_up, out_dtype):
+    gate_up = linear(x, w_gate_up, out_dtype)
+    out = torch.empty((x.shape[0], w_gate_up.shape[0] // 2), dtype=out_dtype)
+    return swiglu(gate_up, out)
 
 
 def qk_norm_rope_store(qkv, q_gain, k_gain, eps, inv_freq, rotary_dim, positions, token_slot,

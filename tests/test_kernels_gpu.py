@@ -422,3 +422,41 @@ def test_gemm_skinny(ops, M, N, K):
     assert (y16.cpu().double() - want).abs().max() < 2e-3 * want.abs().max()
     with pytest.raises(ops.KernelError, match="multiple of 8"):
         ops.gemm_skinny(dev(x[:, :K - 4].contiguous()), dev(w[:, :K - 4].contiguous()), torch.float32)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (200, 304, 328), (300, 1000, 136), (1000, 512, 4104),
+                                   (2048, 1536, 1024)])
+@pytest.mark.parametrize("swiglu", [False, True])
+@pytest.mark.parametrize("short_tiles", [False, True])
+def test_gemm_tcgen05(ops, M, N, K, swiglu, short_tiles):
+    """The TMA + tcgen05 product: row and column counts that end inside a tile, K that ends
+    inside a 64-wide block, several tiles per block (both accumulators in turn), fused SwiGLU.
+    One weight row and one k-column are made much larger than the rest."""
+    x = rnd(M, K, seed=400, scale=0.5).to(torch.bfloat16)
+    w = rnd(N, K, seed=401, scale=0.5).to(torch.bfloat16)
+    w[N - 1] *= 8
+    w[:, K - 1] *= 6
+    ref = x.double() @ w.double().T
+    if swiglu:
+        ref = plain.silu(ref[:, :N // 2]) * ref[:, N // 2:]
+    y = ops.gemm_tcgen05(dev(x), dev(w), swiglu, short_tiles)
+    ops.check_error_word("cuda:0")
+    assert y.shape == ref.shape and y.dtype == torch.bfloat16
+    assert (y.cpu().double() - ref).abs().max() < 1.6e-2 * ref.abs().max()
+
+
+def test_linear_takes_the_tcgen05_path_for_many_rows(ops):
+    assert ops.tcgen05_pays(2048, 4096, 4096, torch.bfloat16) and not ops.tcgen05_pays(2048, 6144, 4096, torch.bfloat16)
+    assert not ops.tcgen05_pays(64, 4096, 4096, torch.bfloat16) and not ops.tcgen05_pays(2048, 4096, 4096, torch.float32)
+    x = rnd(600, 136, seed=410).to(torch.bfloat16)
+    w = rnd(2 * 5376, 136, seed=411, scale=0.3).to(torch.bfloat16)
+    before = ops.tcgen05_calls
+    act = ops.linear_swiglu(dev(x), dev(w), torch.bfloat16)
+    assert ops.tcgen05_calls == before + 1
+    ref = x.double() @ w.double().T
+    ref = plain.silu(ref[:, :5376]) * ref[:, 5376:]
+    ops.check_error_word("cuda:0")
+    assert (act.cpu().double() - ref).abs().max() < 1.6e-2 * ref.abs().max()
+    small = ops.linear_swiglu(dev(x[:9]), dev(w), torch.bfloat16)           # few rows: two kernels, same values
+    assert ops.tcgen05_calls == before + 1
+    assert (small.cpu().double() - ref[:9]).abs().max() < 1.6e-2 * ref.abs().max()

@@ -112,6 +112,7 @@ class LLMEngine:
                 row_of.append(len(entries) - 1)
         logits = self.runner.step(entries)
         tokens = self.sampler.sample(logits, rows)
+        self.runner.check_kernels()
         sampled = [-1] * len(plan.sequences)
         for idx, tok in zip(row_of, tokens):
             sampled[idx] = tok

@@ -79,6 +79,7 @@ class ModelRunner:
         self._graphs = {}
         self._graph_pool = None
         self._graph_logits: Optional[torch.Tensor] = None
+        self._checked_calls = 0
         self.device = model.device
         self.vocab = model.desc.vocab_size
         self.max_batch_tokens = int(max_batch_tokens)
@@ -91,6 +92,13 @@ class ModelRunner:
             self._host = self._host.pin_memory()
         self._dev = torch.empty(12 * n + 64, dtype=torch.int32, device=self.device)
         self._uploaded: Optional[torch.cuda.Event] = None
+
+    def check_kernels(self) -> None:
+        """Raise if a kernel with bounded waits gave up since the last check (reads a device
+        word: call it where the host waits for the step anyway)."""
+        if self.is_cuda and ops.tcgen05_calls != self._checked_calls:
+            self._checked_calls = ops.tcgen05_calls
+            ops.check_error_word(self.device)
 
     # ------------------------------------------------------------------ requests
     def release(self, request: Hashable) -> None:

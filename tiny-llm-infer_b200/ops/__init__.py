@@ -69,6 +69,7 @@ def _declare(h) -> None:
         "tllm_sample": [vp, i32, i32, i64, vp, vp, vp, vp],
         "tllm_sample_split": [vp, i32, i32, i64, vp, vp, vp, vp, i32, i32, vp],
         "tllm_gemm_skinny": [vp, vp, vp, i32, i32, i32, i32, vp],
+        "tllm_gemm_tcgen05": [vp, vp, vp, i32, i32, i32, i32, vp, vp],
         "tllm_paged_attention_decode": [vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32,
                                         i32, vp, vp, vp, vp],
         "tllm_paged_attention_prefill": [vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32, vp, vp],
@@ -315,6 +316,58 @@ def gemm_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -
     return y
 
 
+_error_words = {}
+
+
+def error_word(device) -> torch.Tensor:
+    """Device int32 that kernels with bounded waits (the tcgen05 product) set to a non-zero
+    code when a wait ran out.  ``check_error_word`` reads it (a synchronisation)."""
+    key = str(device)
+    if key not in _error_words:
+        _error_words[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _error_words[key]
+
+
+def check_error_word(device) -> None:
+    code = int(error_word(device).item())
+    if code:
+        error_word(device).zero_()
+        raise KernelError(f"a bounded wait ran out inside a kernel (code {code}); its result is invalid")
+
+
+tcgen05_calls = 0          # products issued on the tcgen05 path (their bounded waits report to error_word)
+
+
+def tcgen05_pays(rows: int, out_cols: int, k: int, dtype, col_tile: int = 256) -> bool:
+    """Whether the hand-written tcgen05 product is used instead of the library's: bfloat16, at
+    least 256 rows, and a tile count that fills the SMs' last round to 85% (blocks of 256 rows;
+    with fewer tiles per round the library's 2-CTA kernels are faster)."""
+    if dtype != torch.bfloat16 or rows < 256 or k % 8 or out_cols % 8:
+        return False
+    tiles = -(-rows // 256) * -(-out_cols // col_tile)
+    rounds = -(-tiles // SM_COUNT)
+    return tiles / (rounds * SM_COUNT) >= 0.85
+
+
+def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, swiglu: bool = False, short_tiles: bool = False) -> torch.Tensor:
+    """y = x . weight^T on tcgen05 tensor cores fed by TMA (csrc/gemm_tcgen05.cu), bfloat16 in
+    and out, float32 accumulation in tensor memory.  With ``swiglu`` the weight is [gate; up]
+    and the result is silu(x . gate^T) * (x . up^T), [rows, weight rows / 2].  ``short_tiles``
+    keeps blocks of 128 rows even when there are more (for measurements)."""
+    _cuda(x, weight)
+    rows, k = x.shape
+    n = weight.shape[0]
+    assert weight.shape[1] == k and x.dtype == weight.dtype == torch.bfloat16
+    y = torch.empty((rows, n // 2 if swiglu else n), dtype=torch.bfloat16, device=x.device)
+    if rows == 0:
+        return y
+    global tcgen05_calls
+    tcgen05_calls += 1
+    _check(lib().tllm_gemm_tcgen05(_p(x), _p(weight), _p(y), rows, n, k, int(swiglu) | (2 if short_tiles else 0),
+                                   _p(error_word(x.device)), _stream()), "gemm_tcgen05")
+    return y
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """y[T, N] = x[T, K] . weight[N, K]^T with float32 accumulation.  A weight kept in
     float32 is multiplied in float32 whatever the activations are stored in."""
@@ -332,6 +385,23 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     if weight.dtype == torch.bfloat16 and 0 < rows <= SKINNY_MAX_ROWS and k % 8 == 0 \
             and x.is_contiguous() and weight.is_contiguous() and want in _DT:
         return gemm_skinny(x, weight, want)
+    if want == torch.bfloat16 and tcgen05_pays(rows, weight.shape[0], k, weight.dtype) \
+            and x.is_contiguous() and weight.is_contiguous():
+        return gemm_tcgen05(x, weight)
     if want == weight.dtype:
         return torch.mm(x, weight.t())
     return torch.mm(x, weight.t(), out_dtype=want)
+
+
+def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """silu(x . Wg^T) * (x . Wu^T) for w_gate_up = [Wg; Wu].  With enough bfloat16 rows the
+    product and the activation are one tcgen05 kernel; otherwise the product is followed by the
+    SwiGLU kernel."""
+    rows, k = x.shape
+    inter = w_gate_up.shape[0] // 2
+    if x.dtype == w_gate_up.dtype == out_dtype == torch.bfloat16 and x.is_contiguous() \
+            and w_gate_up.is_contiguous() and tcgen05_pays(rows, inter, k, w_gate_up.dtype, col_tile=128):
+        return gemm_tcgen05(x, w_gate_up, swiglu=True)
+    gate_up = linear(x, w_gate_up, out_dtype=out_dtype)
+    act = torch.empty((rows, inter), dtype=out_dtype, device=x.device)
+    return swiglu(gate_up, act)

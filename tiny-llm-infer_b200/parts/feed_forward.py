@@ -35,7 +35,5 @@ class SwiGLUFeedForward:
         self.w_down = t["down_proj.weight"].contiguous()
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
-        gate_up = ops.linear(x, self.w_gate_up, out_dtype=self.dtype)
-        act = torch.empty((x.shape[0], self.inter), dtype=self.dtype, device=x.device)
-        ops.swiglu(gate_up, act)
+        act = ops.linear_swiglu(x, self.w_gate_up, out_dtype=self.dtype)
         return ops.linear(act, self.w_down, out_dtype=self.dtype)
