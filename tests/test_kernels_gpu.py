@@ -460,3 +460,19 @@ def test_linear_takes_the_tcgen05_path_for_many_rows(ops):
     small = ops.linear_swiglu(dev(x[:9]), dev(w), torch.bfloat16)           # few rows: two kernels, same values
     assert ops.tcgen05_calls == before + 1
     assert (small.cpu().double() - ref[:9]).abs().max() < 1.6e-2 * ref.abs().max()
+
+
+@pytest.mark.parametrize("M", [1, 5, 8])
+@pytest.mark.parametrize("inter,K", [(200, 96), (1000, 1000), (77, 4104)])
+def test_linear_swiglu_few_rows(ops, M, inter, K):
+    """Gate/up product and SwiGLU for few rows, as the engine runs them and as one
+    weight-streaming kernel, against the plain formulas."""
+    x = rnd(M, K, seed=500 + M, scale=0.5).to(torch.bfloat16)
+    w = rnd(2 * inter, K, seed=501, scale=0.2).to(torch.bfloat16)
+    w[inter - 1] *= 10
+    w[2 * inter - 1] *= 10
+    ref = x.double() @ w.double().T
+    ref = plain.silu(ref[:, :inter]) * ref[:, inter:]
+    for act in (ops.linear_swiglu(dev(x), dev(w), torch.bfloat16), ops.gemm_skinny_swiglu(dev(x), dev(w))):
+        assert act.shape == (M, inter)
+        assert (act.cpu().double() - ref).abs().max() < 1.6e-2 * ref.abs().max()

@@ -47,21 +47,26 @@ __device__ __forceinline__ uint4 ld_coherent(const void* p) {
     return v;
 }
 
-template <int NT>
+template <int NT, bool SWIGLU>
 struct SkinnyStage {
     uint4 a_lo[kSkinnyUnroll], a_hi[kSkinnyUnroll], b[kSkinnyUnroll][NT];
+    uint4 u_lo[SWIGLU ? kSkinnyUnroll : 1], u_hi[SWIGLU ? kSkinnyUnroll : 1];     // the "up" rows of a SwiGLU pair
 };
 
-template <int NT, typename TOut>
+// SWIGLU: w is [gate rows; up rows] with N rows each; the block owns gate rows r0..r0+15 and the
+// up rows that belong to them, and writes silu(gate) * up: y is [M, N].
+template <int NT, typename TOut, bool SWIGLU>
 __global__ void __launch_bounds__(kSkinnyWarps * 32)
-skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __restrict__ y, int M,
-                   int N, int K) {
+skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, TOut* y, int M, int N, int K) {
     __shared__ float red[kSkinnyWarps][16][NT * 8 + 1];
+    __shared__ float red_up[SWIGLU ? kSkinnyWarps : 1][16][NT * 8 + 1];
     asm volatile("griddepcontrol.launch_dependents;\n" ::);
     const int r0 = blockIdx.x * 16;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, c = lane & 3, rq = lane >> 2;
     const bf16* w_lo = w + (size_t)min(r0 + rq, N - 1) * K;
     const bf16* w_hi = w + (size_t)min(r0 + rq + 8, N - 1) * K;
+    const bf16* u_lo = w_lo + (size_t)N * K;
+    const bf16* u_hi = w_hi + (size_t)N * K;
     const bf16* xr[NT];
     bool xv[NT];
 #pragma unroll
@@ -70,25 +75,32 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut*
         xv[nt] = tok < M;
         xr[nt] = x + (size_t)(xv[nt] ? tok : 0) * K;
     }
-    float acc[NT][4];
+    float acc[NT][4], acc_up[NT][4];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
+    for (int nt = 0; nt < NT; ++nt) {
+        acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
+        acc_up[nt][0] = acc_up[nt][1] = acc_up[nt][2] = acc_up[nt][3] = 0.0f;
+    }
 
     const int kblocks = (K + 31) >> 5;                       // 32 k per block: 8 per lane of a quad
     const int per_warp = (kblocks + kSkinnyWarps - 1) / kSkinnyWarps;
     const int kb0 = warp * per_warp, kb1 = min(kblocks, kb0 + per_warp);
     const uint4 zero = make_uint4(0, 0, 0, 0);
 
-    auto load_w = [&](SkinnyStage<NT>& s, int kb) {
+    auto load_w = [&](SkinnyStage<NT, SWIGLU>& s, int kb) {
 #pragma unroll
         for (int u = 0; u < kSkinnyUnroll; ++u) {
             const int k = (kb + u) * 32 + c * 8;
             const bool ok = kb + u < kb1 && k < K;
             s.a_lo[u] = ok ? ld_stream(w_lo + k) : zero;
             s.a_hi[u] = ok ? ld_stream(w_hi + k) : zero;
+            if (SWIGLU) {
+                s.u_lo[u] = ok ? ld_stream(u_lo + k) : zero;
+                s.u_hi[u] = ok ? ld_stream(u_hi + k) : zero;
+            }
         }
     };
-    auto load_x = [&](SkinnyStage<NT>& s, int kb) {
+    auto load_x = [&](SkinnyStage<NT, SWIGLU>& s, int kb) {
 #pragma unroll
         for (int u = 0; u < kSkinnyUnroll; ++u) {
             const int k = (kb + u) * 32 + c * 8;
@@ -98,7 +110,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut*
                 s.b[u][nt] = (ok && xv[nt]) ? ld_coherent(xr[nt] + k) : zero;
         }
     };
-    auto multiply = [&](const SkinnyStage<NT>& s) {
+    auto multiply = [&](const SkinnyStage<NT, SWIGLU>& s) {
 #pragma unroll
         for (int u = 0; u < kSkinnyUnroll; ++u) {
             const uint32_t a1[4] = {s.a_lo[u].x, s.a_hi[u].x, s.a_lo[u].y, s.a_hi[u].y};
@@ -108,11 +120,17 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut*
                 const uint32_t b1[2] = {s.b[u][nt].x, s.b[u][nt].y}, b2[2] = {s.b[u][nt].z, s.b[u][nt].w};
                 mma_bf16_16816(acc[nt], a1, b1);
                 mma_bf16_16816(acc[nt], a2, b2);
+                if (SWIGLU) {
+                    const uint32_t u1[4] = {s.u_lo[u].x, s.u_hi[u].x, s.u_lo[u].y, s.u_hi[u].y};
+                    const uint32_t u2[4] = {s.u_lo[u].z, s.u_hi[u].z, s.u_lo[u].w, s.u_hi[u].w};
+                    mma_bf16_16816(acc_up[nt], u1, b1);
+                    mma_bf16_16816(acc_up[nt], u2, b2);
+                }
             }
         }
     };
 
-    SkinnyStage<NT> s0, s1, s2;
+    SkinnyStage<NT, SWIGLU> s0, s1, s2;
     load_w(s0, kb0);                                         // weights depend on no earlier kernel
     load_w(s1, kb0 + kSkinnyUnroll);
     asm volatile("griddepcontrol.wait;\n" ::: "memory");     // from here on x may be read, y written
@@ -135,6 +153,12 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut*
         red[warp][rq][nt * 8 + c * 2 + 1] = acc[nt][1];
         red[warp][rq + 8][nt * 8 + c * 2] = acc[nt][2];
         red[warp][rq + 8][nt * 8 + c * 2 + 1] = acc[nt][3];
+        if (SWIGLU) {
+            red_up[warp][rq][nt * 8 + c * 2] = acc_up[nt][0];
+            red_up[warp][rq][nt * 8 + c * 2 + 1] = acc_up[nt][1];
+            red_up[warp][rq + 8][nt * 8 + c * 2] = acc_up[nt][2];
+            red_up[warp][rq + 8][nt * 8 + c * 2 + 1] = acc_up[nt][3];
+        }
     }
     __syncthreads();
     for (int idx = threadIdx.x; idx < 16 * NT * 8; idx += blockDim.x) {
@@ -143,12 +167,18 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut*
             float s = 0.0f;
 #pragma unroll
             for (int ww = 0; ww < kSkinnyWarps; ++ww) s += red[ww][row][tok];
+            if (SWIGLU) {
+                float up = 0.0f;
+#pragma unroll
+                for (int ww = 0; ww < kSkinnyWarps; ++ww) up += red_up[ww][row][tok];
+                s = s / (1.0f + expf(-s)) * up;
+            }
             y[(size_t)tok * N + r0 + row] = from_f32<TOut>(s);
         }
     }
 }
 
-template <int NT, typename TOut>
+template <int NT, typename TOut, bool SWIGLU>
 static int launch_skinny(const void* x, const void* w, void* y, int M, int N, int K, cudaStream_t stream) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((N + 15) / 16);
@@ -160,7 +190,7 @@ static int launch_skinny(const void* x, const void* w, void* y, int M, int N, in
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<NT, TOut>, (const bf16*)x, (const bf16*)w,
+    cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<NT, TOut, SWIGLU>, (const bf16*)x, (const bf16*)w,
                                        (TOut*)y, M, N, K);
     if (e != cudaSuccess) {
         set_error("gemm_skinny: %s", cudaGetErrorString(e));
@@ -185,11 +215,24 @@ extern "C" int tllm_gemm_skinny(const void* x, const void* w, void* y, int out_d
     TLLM_REQUIRE(out_dtype == kBF16 || out_dtype == kF32, "gemm_skinny: unknown output dtype");
     if (M == 0) return 0;
     if (out_dtype == kBF16) {
-        if (M <= 8) return launch_skinny<1, bf16>(x, w, y, M, N, K, stream);
-        if (M <= 16) return launch_skinny<2, bf16>(x, w, y, M, N, K, stream);
-        return launch_skinny<4, bf16>(x, w, y, M, N, K, stream);
+        if (M <= 8) return launch_skinny<1, bf16, false>(x, w, y, M, N, K, stream);
+        if (M <= 16) return launch_skinny<2, bf16, false>(x, w, y, M, N, K, stream);
+        return launch_skinny<4, bf16, false>(x, w, y, M, N, K, stream);
     }
-    if (M <= 8) return launch_skinny<1, float>(x, w, y, M, N, K, stream);
-    if (M <= 16) return launch_skinny<2, float>(x, w, y, M, N, K, stream);
-    return launch_skinny<4, float>(x, w, y, M, N, K, stream);
+    if (M <= 8) return launch_skinny<1, float, false>(x, w, y, M, N, K, stream);
+    if (M <= 16) return launch_skinny<2, float, false>(x, w, y, M, N, K, stream);
+    return launch_skinny<4, float, false>(x, w, y, M, N, K, stream);
+}
+
+// y[M, N] = silu(x . w[:N]^T) * (x . w[N:]^T) for w = [gate; up] of 2 N rows, bfloat16 out, M <= 16.
+extern "C" int tllm_gemm_skinny_swiglu(const void* x, const void* w, void* y, int M, int N, int K,
+                                       cudaStream_t stream) {
+    TLLM_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_skinny_swiglu: bad sizes");
+    TLLM_REQUIRE(M <= 16, "gemm_skinny_swiglu: %d rows exceed 16", M);
+    TLLM_REQUIRE(K % 8 == 0, "gemm_skinny_swiglu: K = %d is no multiple of 8", K);
+    TLLM_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15u) == 0,
+                 "gemm_skinny_swiglu: operands must be 16-byte aligned");
+    if (M == 0) return 0;
+    if (M <= 8) return launch_skinny<1, bf16, true>(x, w, y, M, N, K, stream);
+    return launch_skinny<2, bf16, true>(x, w, y, M, N, K, stream);
 }

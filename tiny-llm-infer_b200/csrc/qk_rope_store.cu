@@ -177,7 +177,8 @@ __global__ void qk_norm_rope_store_vec_kernel(
     if (flags & kFlagStore) page = block_table[(size_t)slot * max_pages + pos / page_size];
     __syncthreads();
     T* row = qkv + (size_t)t * heads_total * HD;
-    for (int head = warp; head < heads_total; head += warps) {
+    // with few tokens the heads of a token are spread over gridDim.y blocks (one round per warp)
+    for (int head = blockIdx.y * warps + warp; head < heads_total; head += warps * gridDim.y) {
         const bool is_q = head < q_heads, is_k = !is_q && head < q_heads + kv_heads;
         T* src = row + (size_t)head * HD + e0;
         float x[VEC];
@@ -243,8 +244,9 @@ extern "C" int tllm_qk_norm_rope_store(
         const int need = dtype == kBF16 ? (head_dim / 32) * 2 : 8;     // widest access of the vector form
         if (al(qkv, need) && al(cache, need) && al(q_out, need) && (dtype == kBF16 || dtype == kF32)) {
             const int vblock = 256;
+            const int vgroups = tokens <= 64 ? (q_heads + 2 * kv_heads + 7) / 8 : 1;
 #define VLAUNCH(T, TG, VEC)                                                                         \
-    launch_pdl(qk_norm_rope_store_vec_kernel<T, TG, VEC>, dim3(tokens), dim3(vblock), 0, stream,   \
+    launch_pdl(qk_norm_rope_store_vec_kernel<T, TG, VEC>, dim3(tokens, vgroups), dim3(vblock), 0, stream, \
         (T*)qkv, (const TG*)q_gain, (const TG*)k_gain, eps, inv_freq, positions, token_slot,        \
         block_table, max_pages, (T*)cache, page_size, (T*)q_out, q_heads, kv_heads, flags)
 #define VDISPATCH(T, TG)                                              \
