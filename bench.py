@@ -207,7 +207,7 @@ def main() -> int:
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             start.record()
             logits = runner.step([StepEntry(n, t, [0]) for n, t in zip(names, nxt)])
-            ops.sample(logits, params, seeds, out)
+            ops.sample(logits, params, seeds, out, any_nucleus=False)
             end.record()
             nxt = [[t] for t in out.cpu().tolist()]          # the next step feeds what was sampled
             if it >= warmup:
