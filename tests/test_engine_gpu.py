@@ -19,7 +19,7 @@ pytestmark = pytest.mark.gpu
 @pytest.fixture(scope="module")
 def folders(tmp_path_factory):
     out = {}
-    for name in ("A", "B", "C"):
+    for name in ("A", "B", "C", "E"):
         out[name] = make_folder(TINIES[name], tmp_path_factory.mktemp(f"m{name}"))
     return out
 
@@ -79,6 +79,24 @@ def test_long_decoding(folders, name):
         assert len(out.token_ids) == 300
         ok, info = teacher_forced_ok(cfg, w, p, out.token_ids, margin)
         assert ok, (dtype, info)
+
+
+@pytest.mark.parametrize("budget", [1024, 160])
+def test_long_prompts_head_width_128(folders, budget):
+    """Prompts longer than the 128-row blocks of the tcgen05 prompt kernel (whole, and cut by
+    a budget that is no multiple of the block), then decoding, in bfloat16 against the plain
+    implementation on the same prefix."""
+    from tiny_llm_infer_b200 import LLM, SamplingParams
+    tiny = TINIES["E"]
+    cfg, w = plain.read_model(folders["E"])
+    prompts = [prompt(20 + i, n, cfg["vocab_size"]) for i, n in enumerate((300, 129, 257))]
+    llm = LLM(str(folders["E"]), dtype="bfloat16", max_model_len=400, num_kv_blocks=40,
+              block_size=tiny["page_size"], max_num_batched_tokens=budget, max_num_seqs=3)
+    outs = llm.generate(prompts, SamplingParams(max_tokens=24, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        assert len(o.token_ids) == 24
+        ok, info = teacher_forced_ok(cfg, w, p, o.token_ids, 0.08)
+        assert ok, info
 
 
 def test_eos_stops_and_is_ignored_on_request(folders, tmp_path):

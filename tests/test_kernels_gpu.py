@@ -389,6 +389,61 @@ def test_prefill_kernel_segments(ops, nh, nkv, hd, ps, window):
         assert err < tol(torch.bfloat16, want.abs().max().item()), (s, p0, n, err)
 
 
+@pytest.mark.parametrize("nh,nkv,ps,window", [(8, 2, 16, None), (3, 3, 32, None), (6, 1, 16, 70), (2, 1, 64, 9),
+                                              (4, 2, 48, 200)])
+def test_prefill_tcgen05_kernel_segments(ops, nh, nkv, ps, window):
+    """The tcgen05 kernel (head width 128, blocks of 128 rows) on segments that start inside a
+    request, are shorter and longer than a block, start and end off the edges of key tiles
+    and pages; each row's query points at one key (the window's first, the row's own, the
+    last of the tile before, the one before its own), so that a key that is missed, masked
+    wrongly or read from the wrong page changes the result."""
+    hd = 128
+    lens = [600, 128, 259, 5]
+    max_pages = -(-600 // ps) + 1
+    table, cache, K, V = request_data(lens, nkv, hd, ps, 210, 4 * max_pages + 2, max_pages)
+    group = nh // nkv
+    segs = [(0, 93, 507), (1, 0, 128), (2, 256, 3), (3, 0, 5), (2, 1, 200)]
+    seg_info, tiles, pos_rows, slot_rows, row = [], [], [], [], 0
+    for i, (s, p0, n) in enumerate(segs):
+        seg_info.append([s, row, n, p0])
+        tiles += [[i, off] for off in range(0, n, 128)]
+        pos_rows += list(range(p0, p0 + n))
+        slot_rows += [s] * n
+        row += n
+    T = row
+    q = rnd(T, nh, hd, seed=211, scale=0.2).to(torch.bfloat16).double()
+    for t in range(T):
+        p, s = pos_rows[t], slot_rows[t]
+        lo = max(0, p - window + 1) if window else 0
+        target = [lo, p, max(lo, (p // 64) * 64 - 1), max(lo, p - 1)][t % 4]
+        for h in range(nh):
+            q[t, h] += K[s][target, h // group] * 3.0
+    q = q.to(torch.bfloat16).double()
+    out = torch.zeros((T, nh * hd), dtype=torch.bfloat16, device="cuda")
+    tiles = tiles[::-1]
+    ops.paged_attention_prefill_tcgen05(dev(q.reshape(T, -1).to(torch.bfloat16)), cache,
+                                        dev(torch.tensor(seg_info, dtype=torch.int32)),
+                                        dev(torch.tensor(tiles, dtype=torch.int32)), len(tiles), dev(table), ps,
+                                        nh, nkv, hd, window, 1 / math.sqrt(hd), out)
+    ops.check_error_word(torch.device("cuda"))
+    got = out.cpu().double().view(T, nh, hd)
+    for (s, r0, n, p0) in seg_info:
+        pos = torch.arange(p0, p0 + n)
+        want = plain_rows(q[r0:r0 + n], K[s][:p0 + n], V[s][:p0 + n], pos, window)
+        err = (got[r0:r0 + n] - want).abs().max().item()
+        assert err < tol(torch.bfloat16, want.abs().max().item()), (s, p0, n, err)
+
+
+def test_prefill_tcgen05_refuses_other_shapes(ops):
+    z = torch.zeros((1, 4), dtype=torch.int32, device="cuda")
+    for nh, nkv, hd, ps, match in ((2, 2, 64, 16, "head_dim"), (2, 2, 128, 8, "page size"), (3, 2, 128, 16, "heads")):
+        q = torch.zeros((4, nh * hd), dtype=torch.bfloat16, device="cuda")
+        cache = torch.zeros((4, 2, nkv, ps, hd), dtype=torch.bfloat16, device="cuda")
+        with pytest.raises(ops.KernelError, match=match):
+            ops.paged_attention_prefill_tcgen05(q, cache, z, z[:, :2], 1, z, ps, nh, nkv, hd, None, 1.0,
+                                                torch.empty_like(q))
+
+
 def test_fast_attention_refuses_other_shapes(ops):
     z = torch.zeros(1, dtype=torch.int32, device="cuda")
     table = torch.zeros((1, 4), dtype=torch.int32, device="cuda")

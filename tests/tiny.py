@@ -37,7 +37,14 @@ TINY_D = dict(cfg=Qwen3Config(hidden_size=128, intermediate_size=344, num_hidden
                               tie_word_embeddings=True, sliding_window=80,
                               layer_types=(FULL, SLIDING)),
               seed=3, std=0.06, norm_range=(0.7, 1.3), page_size=16)
-TINIES = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+# head width 128: the width of the tcgen05 prompt kernel, with requests longer than its blocks
+TINY_E = dict(cfg=Qwen3Config(hidden_size=192, intermediate_size=328, num_hidden_layers=2,
+                              num_attention_heads=3, num_key_value_heads=1, head_dim=128, vocab_size=640,
+                              max_position_embeddings=512, rms_norm_eps=3e-6, rope_theta=2e5,
+                              tie_word_embeddings=False, sliding_window=150,
+                              layer_types=(SLIDING, FULL)),
+              seed=4, std=0.05, norm_range=(0.7, 1.3), page_size=32, lengths=(70, 300, 130, 41, 200, 35))
+TINIES = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
 
 
 def make_folder(tiny, folder=None, dtype=torch.bfloat16, shards=1) -> Path:
@@ -67,6 +74,7 @@ def sharpen(folder, factor: float) -> None:
     save_file(tensors, path)
 
 
-def requests_for(tiny, lengths=(70, 97, 130, 41, 66, 35)):
+def requests_for(tiny, lengths=None):
+    lengths = lengths or tiny.get("lengths", (70, 97, 130, 41, 66, 35))
     vocab = tiny["cfg"].vocab_size
     return {str(i): prompt(i, n, vocab) for i, n in enumerate(lengths)}

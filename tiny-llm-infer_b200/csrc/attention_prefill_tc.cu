@@ -1,0 +1,422 @@
+// Attention of prompt portions over the paged cache on the fifth-generation tensor cores:
+// TMA brings queries, keys and values into shared memory, tcgen05.mma computes S = Q K^T and
+// P V with accumulators in tensor memory, and the softmax runs on what tcgen05.ld reads back.
+// Head width 128, bfloat16, pages of a multiple of 16 tokens.
+//
+// (The reference treats each prompt token as a decode query of its own,
+// kernels/src/paged_attention_cuda.cu:70-120; the mma.sync version of this kernel is
+// attention_prefill.cu, which stays for head width 64 and as the comparison in the tests.)
+//
+// A block owns 128 consecutive query rows of one portion and one query head, and walks the
+// request's keys in tiles of 64.  It has two warpgroups.
+//   warp 0   producer: one thread looks the tile's pages up in the block table and issues TMA
+//            loads (128-byte swizzle) of 16 keys x 64 columns each, keys and values, into a
+//            two-stage ring; the 128 x 128 query tile is loaded once.
+//   warp 1   issues the MMAs (one thread): S[128 x 64] = Q K^T (8 x tcgen05.mma 128x64x16, both
+//            operands K-major), then, once the softmax has put P in shared memory,
+//            O_tile[128 x 128] = P V (4 x tcgen05.mma 128x128x16, V used as it lies in the
+//            cache: an MN-major operand).  tcgen05.commit tells the softmax warps and frees
+//            the stage.
+//   warps 4-7 softmax, one query row per thread (TMEM lane = row): read S, scale, mask by the
+//            row's position (and window), online softmax in base 2 in float32, write P as
+//            bfloat16 into the swizzled operand layout, then read O_tile and fold it into the
+//            row's float32 accumulator in registers with the correction factor.
+// The producer warpgroup gives registers away (setmaxnreg) and the softmax warpgroup takes
+// them, so that two blocks fit on an SM and one block's MMAs run under the other's softmax.
+// Every mbarrier wait is bounded; on a timeout the block sets the caller's error word, stops,
+// waits (bounded) for copies in flight, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace tllm {
+namespace pftc {
+
+constexpr int kHD = 128, kBM = 128, kBN = 64;
+constexpr int kQBytes = kBM * kHD * 2;            // 32 KB: two column halves of [128 rows x 128 B]
+constexpr int kKBytes = kBN * kHD * 2;            // 16 KB: two column halves of [64 keys x 128 B]
+constexpr int kVBytes = kKBytes;
+constexpr int kPBytes = kBM * kBN * 2;            // 16 KB: [128 rows x 128 B]
+constexpr int kStages = 2;
+constexpr int kTilesBytes = kQBytes + kStages * (kKBytes + kVBytes) + kPBytes;   // 112 KB
+constexpr int kSmemBytes = kTilesBytes + 256;     // + barriers and the TMEM slot
+constexpr int kThreads = 256;
+constexpr uint32_t kTmemCols = 256;               // S: columns 0..63, O_tile: columns 128..255
+constexpr int kSpinLimit = 1 << 20;
+
+__device__ __forceinline__ uint32_t sa(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(sa(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(sa(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(sa(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = sa(bar);
+    for (int spin = 0; spin < kSpinLimit; ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}\n"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::"r"(
+            smem_dst),
+        "l"(map), "r"(sa(bar)), "r"(c0), "r"(c1)
+        : "memory");
+}
+// K-major operand, 128-byte swizzle: rows of 128 bytes, eight-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// MN-major operand, 128-byte swizzle: a row of 128 bytes holds 64 consecutive MN elements of one
+// k; eight k's form a 1024-byte group (stride byte offset), the next 64 MN elements lie
+// `mn_block_bytes` further (leading byte offset).
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr, uint32_t mn_block_bytes) {
+    return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)(mn_block_bytes >> 4) << 16) |
+           ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// kind::f16 instruction descriptor: float32 accumulator, bfloat16 operands, A K-major, B K-major
+// (b_mn_major = 0) or MN-major (1), N / 8 in bits 17-22, M / 16 in bits 24-28.
+__host__ __device__ constexpr uint32_t idesc(int m, int n, int b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t id, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(id), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(sa(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,"
+        "%28,%29,%30,%31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct Barriers {
+    uint64_t q_full, kv_full[kStages], kv_empty[kStages], s_full, p_full, o_full;
+    uint32_t tmem_slot;
+    int abort_flag;
+};
+
+__global__ void __launch_bounds__(kThreads, 2)
+paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+                                  const int* __restrict__ seg_info, const int* __restrict__ tiles,
+                                  const int* __restrict__ block_table, int max_pages, int page_size, int q_heads,
+                                  int kv_heads, long long kv_rows, int window, float scale_log2e,
+                                  bf16* __restrict__ out, int* __restrict__ error_word) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    Barriers* bars = reinterpret_cast<Barriers*>(smem + kTilesBytes);
+    volatile int* aborted = &bars->abort_flag;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t q_s = sa(smem), kv_s = q_s + kQBytes, p_s = kv_s + kStages * (kKBytes + kVBytes);
+
+    const int seg = tiles[2 * blockIdx.x], q_off = tiles[2 * blockIdx.x + 1];
+    const int head = blockIdx.y;
+    const int slot = seg_info[4 * seg], start = seg_info[4 * seg + 1];
+    const int len = seg_info[4 * seg + 2], pos0 = seg_info[4 * seg + 3];
+    const int g = head / (q_heads / kv_heads);
+    const int rows_here = min(kBM, len - q_off);
+    const int first_pos = pos0 + q_off, last_pos = first_pos + rows_here - 1;
+    const int lo_all = (window > 0 && first_pos - window + 1 > 0) ? first_pos - window + 1 : 0;
+    const int kt_first = lo_all / kBN, kt_last = last_pos / kBN;
+    const int n_tiles = kt_last - kt_first + 1;
+
+    if (threadIdx.x == 0) {
+        if (q_s & 1023) atomicExch(error_word, 9);         // operand tiles need a 1024-byte aligned window
+        mbar_init(&bars->q_full, 1);
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&bars->kv_full[s], 1);
+            mbar_init(&bars->kv_empty[s], 1);
+        }
+        mbar_init(&bars->s_full, 1);
+        mbar_init(&bars->p_full, 4);                        // one arrival per softmax warp
+        mbar_init(&bars->o_full, 1);
+        bars->abort_flag = (q_s & 1023) ? 1 : 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(sa(&bars->tmem_slot)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem_s = bars->tmem_slot, tmem_o = tmem_s + 128;
+
+    if (warp < 4) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;\n" ::);
+        if (warp == 0 && lane == 0) {
+            // ---------------------------------------------------------------- producer
+            const int* table = block_table + (size_t)slot * max_pages;
+            if (!*aborted) {
+                mbar_expect_tx(&bars->q_full, kQBytes);
+                tma_load_2d(q_s, &map_q, head * kHD, start + q_off, &bars->q_full);
+                tma_load_2d(q_s + kQBytes / 2, &map_q, head * kHD + 64, start + q_off, &bars->q_full);
+            }
+            int issued = 0;
+            for (int j = 0; j < n_tiles && !*aborted; ++j) {
+                const int s = j % kStages;
+                if (j >= kStages && !mbar_wait(&bars->kv_empty[s], ((j / kStages) - 1) & 1)) {
+                    atomicExch(error_word, 1);
+                    *aborted = 1;
+                    break;
+                }
+                const uint32_t k_dst = kv_s + s * (kKBytes + kVBytes), v_dst = k_dst + kKBytes;
+                mbar_expect_tx(&bars->kv_full[s], kKBytes + kVBytes);
+                for (int grp = 0; grp < kBN / 16; ++grp) {
+                    const int key0 = (kt_first + j) * kBN + grp * 16;
+                    int page = key0 <= last_pos ? table[key0 / page_size] : -1;
+                    // rows outside the tensor read as zeros: used for pages that are not held
+                    const long long row_k = page >= 0
+                        ? ((long long)page * 2 * kv_heads + g) * page_size + (key0 % page_size) : kv_rows;
+                    const long long row_v = page >= 0 ? row_k + (long long)kv_heads * page_size : kv_rows;
+                    const uint32_t off = grp * 16 * 128;
+                    tma_load_2d(k_dst + off, &map_kv, 0, (int)row_k, &bars->kv_full[s]);
+                    tma_load_2d(k_dst + kKBytes / 2 + off, &map_kv, 64, (int)row_k, &bars->kv_full[s]);
+                    tma_load_2d(v_dst + off, &map_kv, 0, (int)row_v, &bars->kv_full[s]);
+                    tma_load_2d(v_dst + kVBytes / 2 + off, &map_kv, 64, (int)row_v, &bars->kv_full[s]);
+                }
+                issued = j + 1;
+            }
+            if (*aborted) {      // do not leave while copies into this block's shared memory are in flight
+                mbar_wait(&bars->q_full, 0);
+                const int first = issued > kStages ? issued - kStages : 0;
+                for (int j = first; j < issued; ++j) mbar_wait(&bars->kv_full[j % kStages], (j / kStages) & 1);
+            }
+        } else if (warp == 1 && lane == 0) {
+            // ---------------------------------------------------------------- MMA issuer
+            constexpr uint32_t id_s = idesc(kBM, kBN, 0), id_o = idesc(kBM, kHD, 1);
+            bool ok = mbar_wait(&bars->q_full, 0);
+            if (!ok) { atomicExch(error_word, 2); *aborted = 1; }
+            for (int j = 0; j < n_tiles && !*aborted; ++j) {
+                const int s = j % kStages;
+                if (!mbar_wait(&bars->kv_full[s], (j / kStages) & 1)) { atomicExch(error_word, 3); *aborted = 1; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t k_addr = kv_s + s * (kKBytes + kVBytes), v_addr = k_addr + kKBytes;
+#pragma unroll
+                for (int k = 0; k < kHD / 16; ++k) {        // S = Q K^T over the head width
+                    const uint32_t half = k >> 2, kk = k & 3;
+                    umma(tmem_s, desc_k_major(q_s + half * (kQBytes / 2) + kk * 32),
+                         desc_k_major(k_addr + half * (kKBytes / 2) + kk * 32), id_s, k > 0 ? 1u : 0u);
+                }
+                umma_commit(&bars->s_full);
+                if (!mbar_wait(&bars->p_full, j & 1)) { atomicExch(error_word, 4); *aborted = 1; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll
+                for (int k = 0; k < kBN / 16; ++k) {        // O_tile = P V over the tile's keys
+                    umma(tmem_o, desc_k_major(p_s + k * 32), desc_mn_major(v_addr + k * 2048, kVBytes / 2), id_o,
+                         k > 0 ? 1u : 0u);
+                }
+                umma_commit(&bars->o_full);
+                umma_commit(&bars->kv_empty[s]);
+            }
+        }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;\n" ::);
+        // -------------------------------------------------------------------- softmax, one row per thread
+        const int quad = warp & 3, r = quad * 32 + lane;
+        const int pos = first_pos + r;
+        const int min_key = window > 0 ? pos - window + 1 : 0;
+        const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
+        float acc[kHD];
+#pragma unroll
+        for (int i = 0; i < kHD; ++i) acc[i] = 0.0f;
+        float m_run = -INFINITY, l_run = 0.0f;
+        for (int j = 0; j < n_tiles; ++j) {
+            if (!mbar_wait(&bars->s_full, j & 1)) {
+                if (lane == 0) atomicExch(error_word, 5);
+                *aborted = 1;
+            }
+            if (*aborted) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            uint32_t s0[32], s1[32];
+            tmem_ld32(tmem_s + lane_sel, s0);
+            tmem_ld32(tmem_s + lane_sel + 32, s1);
+            tmem_ld_wait();
+            const int key0 = (kt_first + j) * kBN;
+            float sv[kBN];
+            float tile_max = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < kBN; ++i) {
+                const int key = key0 + i;
+                const float raw = __uint_as_float(i < 32 ? s0[i] : s1[i - 32]);
+                sv[i] = (key <= pos && key >= min_key) ? raw * scale_log2e : -INFINITY;
+                tile_max = fmaxf(tile_max, sv[i]);
+            }
+            const float m_new = fmaxf(m_run, tile_max);
+            const float m_safe = m_new == -INFINITY ? 0.0f : m_new;
+            const float corr = exp2f(m_run - m_safe);
+            m_run = m_new;
+            float sum = 0.0f;
+            // P as bfloat16 into the K-major swizzled operand layout: row r, 16-byte chunk c at c ^ (r & 7)
+            const uint32_t p_row = p_s + r * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                uint32_t w[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float a = exp2f(sv[c * 8 + 2 * e] - m_safe), b = exp2f(sv[c * 8 + 2 * e + 1] - m_safe);
+                    sum += a + b;
+                    w[e] = pack2(a, b);
+                }
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(p_row + ((c ^ (r & 7)) << 4)), "r"(w[0]),
+                             "r"(w[1]), "r"(w[2]), "r"(w[3])
+                             : "memory");
+            }
+            l_run = l_run * corr + sum;
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");     // P visible to the tensor core
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");  // S has been read
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->p_full);
+            if (!mbar_wait(&bars->o_full, j & 1)) {
+                if (lane == 0) atomicExch(error_word, 6);
+                *aborted = 1;
+            }
+            if (*aborted) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll
+            for (int c = 0; c < kHD; c += 32) {
+                uint32_t o[32];
+                tmem_ld32(tmem_o + lane_sel + c, o);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[c + i] = acc[c + i] * corr + __uint_as_float(o[i]);
+            }
+        }
+        // ---- result: through shared memory (the query tile is no longer needed) for whole-line stores
+        const bool finished = !*aborted;
+        asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+        asm volatile("bar.sync 1, 128;\n" ::: "memory");       // all softmax warps are done with Q and P
+        if (finished) {
+            const float inv = 1.0f / l_run;
+            const uint32_t stage_row = q_s + r * 256;
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                uint32_t w[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) w[e] = pack2(acc[c * 8 + 2 * e] * inv, acc[c * 8 + 2 * e + 1] * inv);
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(stage_row + ((c ^ (r & 15)) << 4)),
+                             "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                             : "memory");
+            }
+            __syncwarp();
+            // a warp stores its 32 rows, two rows (2 x 256 bytes) per instruction
+#pragma unroll 1
+            for (int i = 0; i < 16; ++i) {
+                const int rr = quad * 32 + i * 2 + (lane >> 4), c = lane & 15;
+                if (rr < rows_here) {
+                    uint4 val;
+                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                                 : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w)
+                                 : "r"(q_s + rr * 256 + ((c ^ (rr & 15)) << 4)));
+                    *reinterpret_cast<uint4*>(out + ((size_t)(start + q_off + rr) * q_heads + head) * kHD + c * 8) = val;
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_s), "r"(kTmemCols) : "memory");
+    }
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// [rows, cols] bfloat16 row-major, boxes of box_rows x 64 columns, 128-byte swizzle.
+static bool make_map(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace pftc
+}  // namespace tllm
+
+using namespace tllm;
+
+// tiles: int[n_tiles][2] = segment, offset of the block's first query row (blocks of 128 rows).
+// q [tokens, q_heads * 128], cache [num_pages, 2, kv_heads, page_size, 128], both bfloat16.
+extern "C" int tllm_paged_attention_prefill_tc(
+    const void* q, int tokens, const void* cache, int num_pages, const int* seg_info, const int* tiles, int n_tiles,
+    const int* block_table, int max_pages, int page_size, int q_heads, int kv_heads, int head_dim, int window,
+    float scale, void* out, int* error_word, cudaStream_t stream) {
+    TLLM_REQUIRE(head_dim == 128, "paged_attention_prefill_tc: head_dim %d is not 128", head_dim);
+    TLLM_REQUIRE(q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0 && q_heads <= 65535,
+                 "paged_attention_prefill_tc: %d query heads over %d key/value heads", q_heads, kv_heads);
+    TLLM_REQUIRE(page_size > 0 && page_size % 16 == 0, "paged_attention_prefill_tc: page size %d is no multiple of 16",
+                 page_size);
+    TLLM_REQUIRE(error_word != nullptr && n_tiles >= 0 && tokens > 0, "paged_attention_prefill_tc: bad arguments");
+    const long long kv_rows = (long long)num_pages * 2 * kv_heads * page_size;
+    TLLM_REQUIRE(kv_rows < (1ll << 31), "paged_attention_prefill_tc: cache of %lld rows exceeds the copy engine's coordinates",
+                 kv_rows);
+    if (n_tiles == 0) return 0;
+    CUtensorMap mq, mkv;
+    TLLM_REQUIRE(pftc::make_map(&mq, q, tokens, (long long)q_heads * 128, 128) && pftc::make_map(&mkv, cache, kv_rows, 128, 16),
+                 "paged_attention_prefill_tc: cuTensorMapEncodeTiled failed or is not available");
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(pftc::paged_attention_prefill_tc_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, pftc::kSmemBytes);
+        if (e != cudaSuccess) { set_error("paged_attention_prefill_tc: %s", cudaGetErrorString(e)); return (int)e; }
+        configured = true;
+    }
+    pftc::paged_attention_prefill_tc_kernel<<<dim3(n_tiles, q_heads), pftc::kThreads, pftc::kSmemBytes, stream>>>(
+        mq, mkv, seg_info, tiles, block_table, max_pages, page_size, q_heads, kv_heads, kv_rows, window,
+        scale * 1.4426950408889634f, (bf16*)out, error_word);
+    return finish_launch("paged_attention_prefill_tc");
+}

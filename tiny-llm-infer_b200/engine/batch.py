@@ -44,11 +44,13 @@ class StepContext:
     segments: List[Segment]
     seg_info: Optional[torch.Tensor] = None   # [segments, 4] = slot, start, length, pos0
     # rows of one-token segments (None: every row is one) and, for the longer segments,
-    # blocks of 64 query rows as (segment, offset) pairs; faster attention kernels use them
+    # blocks of 64 query rows as (segment, offset) pairs, the first n_tiles128 of which start at
+    # multiples of 128 rows (the list of 128-row blocks); faster attention kernels use them
     dec_rows: Optional[torch.Tensor] = None
     n_dec: int = 0
     pf_tiles: Optional[torch.Tensor] = None
     n_tiles: int = 0
+    n_tiles128: int = 0
     decode_only: bool = False
     max_context: int = 0          # largest position + 1 among the rows
     max_segment: int = 0          # longest segment

@@ -74,6 +74,8 @@ def _declare(h) -> None:
         "tllm_paged_attention_decode": [vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32,
                                         i32, vp, vp, vp, vp],
         "tllm_paged_attention_prefill": [vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32, vp, vp],
+        "tllm_paged_attention_prefill_tc": [vp, i32, vp, i32, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32,
+                                            vp, vp, vp],
     }
     for name, args in sigs.items():
         fn = getattr(h, name)
@@ -245,6 +247,26 @@ def paged_attention_prefill(q, cache, seg_info, tiles, n_tiles, block_table, pag
     return out
 
 
+PREFILL_TCGEN05 = True     # head width 128 takes the tcgen05 kernel; False keeps the mma.sync one
+
+
+def paged_attention_prefill_tcgen05(q, cache, seg_info, tiles, n_tiles, block_table, page_size, q_heads,
+                                    kv_heads, head_dim, window, scale, out):
+    """As ``paged_attention_prefill`` with blocks of 128 query rows, on tcgen05 tensor cores with
+    TMA loads: bfloat16, head width 128.  The kernel's waits are bounded; what they report is
+    read by ``check_error_word``."""
+    _cuda(q, cache, seg_info, tiles, block_table, out)
+    assert q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    assert q.shape[1] == q_heads * head_dim and tuple(out.shape) == tuple(q.shape)
+    global tcgen05_calls
+    tcgen05_calls += 1
+    _check(lib().tllm_paged_attention_prefill_tc(
+        _p(q), q.shape[0], _p(cache), cache.shape[0], _p(seg_info), _p(tiles), n_tiles, _p(block_table),
+        block_table.shape[1], page_size, q_heads, kv_heads, head_dim, int(window or 0), float(scale),
+        _p(out), _p(error_word(q.device)), _stream()), "paged_attention_prefill_tc")
+    return out
+
+
 def paged_attention(q: torch.Tensor, cache: torch.Tensor, positions, token_slot, block_table,
                     page_size: int, q_heads: int, kv_heads: int, head_dim: int,
                     window: Optional[int], scale: float, out: torch.Tensor, ctx=None) -> torch.Tensor:
@@ -263,8 +285,13 @@ def paged_attention(q: torch.Tensor, cache: torch.Tensor, positions, token_slot,
                                    page_size, q_heads, kv_heads, head_dim, window, scale, out,
                                    ctx.max_context)
         if ctx.n_tiles:
-            paged_attention_prefill(q, cache, ctx.seg_info, ctx.pf_tiles, ctx.n_tiles, block_table,
-                                    page_size, q_heads, kv_heads, head_dim, window, scale, out)
+            if PREFILL_TCGEN05 and head_dim == 128 and getattr(ctx, "n_tiles128", 0):
+                paged_attention_prefill_tcgen05(q, cache, ctx.seg_info, ctx.pf_tiles, ctx.n_tiles128,
+                                                block_table, page_size, q_heads, kv_heads, head_dim,
+                                                window, scale, out)
+            else:
+                paged_attention_prefill(q, cache, ctx.seg_info, ctx.pf_tiles, ctx.n_tiles, block_table,
+                                        page_size, q_heads, kv_heads, head_dim, window, scale, out)
         return out
     _check(lib().tllm_paged_attention_general(
         _p(q), _p(cache), _p(positions), _p(token_slot), _p(block_table), block_table.shape[1],
