@@ -1,6 +1,6 @@
 // Attention of prompt portions over the paged cache on the fifth-generation tensor cores:
 // TMA brings queries, keys and values into shared memory, tcgen05.mma computes S = Q K^T and
-// P V with accumulators in tensor memory, and the softmax runs on what tcgen05.ld reads back.
+// O += P V with S, P and O in tensor memory, and the softmax runs on what tcgen05.ld reads back.
 // Head width 128, bfloat16, pages of a multiple of 16 tokens.
 //
 // (The reference treats each prompt token as a decode query of its own,
@@ -8,23 +8,26 @@
 // attention_prefill.cu, which stays for head width 64 and as the comparison in the tests.)
 //
 // A block owns 128 consecutive query rows of one portion and one query head, and walks the
-// request's keys in tiles of 64.  It has two warpgroups.
-//   warp 0   producer: one thread looks the tile's pages up in the block table and issues TMA
-//            loads (128-byte swizzle) of 16 keys x 64 columns each, keys and values, into a
-//            two-stage ring; the 128 x 128 query tile is loaded once.
-//   warp 1   issues the MMAs (one thread): S[128 x 64] = Q K^T (8 x tcgen05.mma 128x64x16, both
-//            operands K-major), then, once the softmax has put P in shared memory,
-//            O_tile[128 x 128] = P V (4 x tcgen05.mma 128x128x16, V used as it lies in the
-//            cache: an MN-major operand).  tcgen05.commit tells the softmax warps and frees
-//            the stage.
-//   warps 4-7 softmax, one query row per thread (TMEM lane = row): read S, scale, mask by the
-//            row's position (and window), online softmax in base 2 in float32, write P as
-//            bfloat16 into the swizzled operand layout, then read O_tile and fold it into the
-//            row's float32 accumulator in registers with the correction factor.
-// The producer warpgroup gives registers away (setmaxnreg) and the softmax warpgroup takes
-// them, so that two blocks fit on an SM and one block's MMAs run under the other's softmax.
-// Every mbarrier wait is bounded; on a timeout the block sets the caller's error word, stops,
-// waits (bounded) for copies in flight, frees its tensor memory and returns.
+// request's keys in tiles of 64.
+//   warp 0   producer: eight lanes each look one group of 16 keys up in the block table and issue
+//            one TMA load (128-byte swizzle) of 16 keys x 64 columns into a ring of three key
+//            tiles and a ring of two value tiles; the 128 x 128 query tile is loaded once.
+//   warp 1   issues the MMAs (one thread).  S[128 x 64] = Q K^T (8 x tcgen05.mma 128x64x16, both
+//            operands K-major in shared memory) goes into one of two S buffers, one tile ahead
+//            of the softmax (and only after the P V product that read that buffer has completed).  Once the softmax has put P into tensor memory (over the S it
+//            read), O[128 x 128] += P V (4 x tcgen05.mma 128x128x16 with A from tensor memory and
+//            V as it lies in the cache: an MN-major operand).  tcgen05.commit frees the stages
+//            and tells the softmax warps.
+//   warps 4-7 softmax, one query row per thread (TMEM lane = row): read S, mask by the row's
+//            position and window where the tile needs it, softmax in base 2 in float32 against
+//            a reference maximum that is only raised when a tile exceeds it by more than 2^8
+//            (then O, which stays in tensor memory, and the row sum are scaled down: rare after
+//            the first tiles), write P as bfloat16 back into tensor memory.  At the end O / sum
+//            goes through shared memory to whole-line stores.
+// Two blocks fit on an SM (112 KB of shared memory, 256 TMEM columns each), so that one
+// block's MMAs run under the other's softmax.  Every mbarrier wait is bounded; on a timeout
+// the block sets the caller's error word, stops, waits (bounded) for copies in flight, frees
+// its tensor memory and returns.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -36,12 +39,12 @@ constexpr int kHD = 128, kBM = 128, kBN = 64;
 constexpr int kQBytes = kBM * kHD * 2;            // 32 KB: two column halves of [128 rows x 128 B]
 constexpr int kKBytes = kBN * kHD * 2;            // 16 KB: two column halves of [64 keys x 128 B]
 constexpr int kVBytes = kKBytes;
-constexpr int kPBytes = kBM * kBN * 2;            // 16 KB: [128 rows x 128 B]
-constexpr int kStages = 2;
-constexpr int kTilesBytes = kQBytes + kStages * (kKBytes + kVBytes) + kPBytes;   // 112 KB
+constexpr int kKStages = 3, kVStages = 2;
+constexpr int kTilesBytes = kQBytes + kKStages * kKBytes + kVStages * kVBytes;   // 112 KB
 constexpr int kSmemBytes = kTilesBytes + 256;     // + barriers and the TMEM slot
 constexpr int kThreads = 256;
-constexpr uint32_t kTmemCols = 256;               // S: columns 0..63, O_tile: columns 128..255
+constexpr uint32_t kTmemCols = 256;               // S (and P over it): columns 0..63 and 64..127, O: 128..255
+constexpr float kRaise = 8.0f;                    // the reference maximum follows only beyond 2^8
 constexpr int kSpinLimit = 1 << 20;
 
 __device__ __forceinline__ uint32_t sa(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -102,6 +105,15 @@ __device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t 
         "l"(a_desc), "l"(b_desc), "r"(id), "r"(acc)
         : "memory");
 }
+// A from tensor memory (lane = row, two bfloat16 per 32-bit column), B from shared memory.
+__device__ __forceinline__ void umma_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t id, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(id), "r"(acc)
+        : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(sa(bar))
                  : "memory");
@@ -118,6 +130,23 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+        "%29,%30,%31,%32};\n" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+        "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+        "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -125,10 +154,22 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 }
 
 struct Barriers {
-    uint64_t q_full, kv_full[kStages], kv_empty[kStages], s_full, p_full, o_full;
+    uint64_t q_full, k_full[kKStages], k_empty[kKStages], v_full[kVStages], v_empty[kVStages];
+    uint64_t s_full[2], p_full[2], o_full, drain;
     uint32_t tmem_slot;
     int abort_flag;
 };
+
+// The 16 keys from key0 on, for K (kv = 0) or V (kv = 1): the row of the cache seen as
+// [pages * 2 * kv_heads * page_size, 128], or `kv_rows` (outside: reads as zeros) if the
+// request holds no such key.
+__device__ __forceinline__ int cache_row(const int* table, int key0, int last_pos, int page_size, int kv_heads, int g,
+                                         int kv, long long kv_rows) {
+    if (key0 > last_pos) return (int)kv_rows;
+    const int page = table[key0 / page_size];
+    if (page < 0) return (int)kv_rows;
+    return (int)((((long long)page * 2 + kv) * kv_heads + g) * page_size + (key0 % page_size));
+}
 
 __global__ void __launch_bounds__(kThreads, 2)
 paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
@@ -140,7 +181,7 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
     Barriers* bars = reinterpret_cast<Barriers*>(smem + kTilesBytes);
     volatile int* aborted = &bars->abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t q_s = sa(smem), kv_s = q_s + kQBytes, p_s = kv_s + kStages * (kKBytes + kVBytes);
+    const uint32_t q_s = sa(smem), k_s = q_s + kQBytes, v_s = k_s + kKStages * kKBytes;
 
     const int seg = tiles[2 * blockIdx.x], q_off = tiles[2 * blockIdx.x + 1];
     const int head = blockIdx.y;
@@ -156,13 +197,14 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
     if (threadIdx.x == 0) {
         if (q_s & 1023) atomicExch(error_word, 9);         // operand tiles need a 1024-byte aligned window
         mbar_init(&bars->q_full, 1);
-        for (int s = 0; s < kStages; ++s) {
-            mbar_init(&bars->kv_full[s], 1);
-            mbar_init(&bars->kv_empty[s], 1);
+        for (int s = 0; s < kKStages; ++s) { mbar_init(&bars->k_full[s], 1); mbar_init(&bars->k_empty[s], 1); }
+        for (int s = 0; s < kVStages; ++s) { mbar_init(&bars->v_full[s], 1); mbar_init(&bars->v_empty[s], 1); }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&bars->s_full[b], 1);
+            mbar_init(&bars->p_full[b], 4);                 // one arrival per softmax warp
         }
-        mbar_init(&bars->s_full, 1);
-        mbar_init(&bars->p_full, 4);                        // one arrival per softmax warp
         mbar_init(&bars->o_full, 1);
+        mbar_init(&bars->drain, 1);
         bars->abort_flag = (q_s & 1023) ? 1 : 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
@@ -177,161 +219,222 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const uint32_t tmem_s = bars->tmem_slot, tmem_o = tmem_s + 128;
 
-    if (warp < 4) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;\n" ::);
-        if (warp == 0 && lane == 0) {
-            // ---------------------------------------------------------------- producer
-            const int* table = block_table + (size_t)slot * max_pages;
-            if (!*aborted) {
-                mbar_expect_tx(&bars->q_full, kQBytes);
-                tma_load_2d(q_s, &map_q, head * kHD, start + q_off, &bars->q_full);
-                tma_load_2d(q_s + kQBytes / 2, &map_q, head * kHD + 64, start + q_off, &bars->q_full);
+    if (warp == 0) {
+        // -------------------------------------------------------------------- producer (the whole warp)
+        // A tile is 8 boxes (4 groups of 16 keys x 2 column halves): lanes 0-7 each look one
+        // group's page up and issue one box, so that a tile costs one lookup's latency, not eight.
+        const int* table = block_table + (size_t)slot * max_pages;
+        bool stop = __any_sync(0xffffffffu, *aborted != 0);
+        const bool q_issued = !stop;
+        if (!stop && lane == 0) {
+            mbar_expect_tx(&bars->q_full, kQBytes);
+            tma_load_2d(q_s, &map_q, head * kHD, start + q_off, &bars->q_full);
+            tma_load_2d(q_s + kQBytes / 2, &map_q, head * kHD + 64, start + q_off, &bars->q_full);
+        }
+        const int grp = lane >> 1, half = lane & 1;
+        int k_issued = 0, v_issued = 0;
+        // keys run one tile ahead of values, as the MMAs use them: K0, then K(j+1), V(j)
+        for (int step = 0; step <= n_tiles && !stop; ++step) {
+            const int jk = step, jv = step - 1;
+            if (jk < n_tiles) {
+                const int s = jk % kKStages;
+                bool ok = true;
+                if (jk >= kKStages && lane == 0) ok = mbar_wait(&bars->k_empty[s], ((jk / kKStages) - 1) & 1);
+                if (!ok) { atomicExch(error_word, 1); *aborted = 1; }
+                if (__any_sync(0xffffffffu, !ok || *aborted != 0)) { stop = true; break; }
+                if (lane == 0) mbar_expect_tx(&bars->k_full[s], kKBytes);
+                __syncwarp();
+                if (lane < 8) {
+                    const int row = cache_row(table, (kt_first + jk) * kBN + grp * 16, last_pos, page_size, kv_heads,
+                                              g, 0, kv_rows);
+                    tma_load_2d(k_s + s * kKBytes + half * (kKBytes / 2) + grp * 2048, &map_kv, half * 64, row,
+                                &bars->k_full[s]);
+                }
+                k_issued = jk + 1;
             }
-            int issued = 0;
-            for (int j = 0; j < n_tiles && !*aborted; ++j) {
-                const int s = j % kStages;
-                if (j >= kStages && !mbar_wait(&bars->kv_empty[s], ((j / kStages) - 1) & 1)) {
-                    atomicExch(error_word, 1);
-                    *aborted = 1;
-                    break;
+            if (jv >= 0) {
+                const int s = jv % kVStages;
+                bool ok = true;
+                if (jv >= kVStages && lane == 0) ok = mbar_wait(&bars->v_empty[s], ((jv / kVStages) - 1) & 1);
+                if (!ok) { atomicExch(error_word, 2); *aborted = 1; }
+                if (__any_sync(0xffffffffu, !ok || *aborted != 0)) { stop = true; break; }
+                if (lane == 0) mbar_expect_tx(&bars->v_full[s], kVBytes);
+                __syncwarp();
+                if (lane < 8) {
+                    const int row = cache_row(table, (kt_first + jv) * kBN + grp * 16, last_pos, page_size, kv_heads,
+                                              g, 1, kv_rows);
+                    tma_load_2d(v_s + s * kVBytes + half * (kVBytes / 2) + grp * 2048, &map_kv, half * 64, row,
+                                &bars->v_full[s]);
                 }
-                const uint32_t k_dst = kv_s + s * (kKBytes + kVBytes), v_dst = k_dst + kKBytes;
-                mbar_expect_tx(&bars->kv_full[s], kKBytes + kVBytes);
-                for (int grp = 0; grp < kBN / 16; ++grp) {
-                    const int key0 = (kt_first + j) * kBN + grp * 16;
-                    int page = key0 <= last_pos ? table[key0 / page_size] : -1;
-                    // rows outside the tensor read as zeros: used for pages that are not held
-                    const long long row_k = page >= 0
-                        ? ((long long)page * 2 * kv_heads + g) * page_size + (key0 % page_size) : kv_rows;
-                    const long long row_v = page >= 0 ? row_k + (long long)kv_heads * page_size : kv_rows;
-                    const uint32_t off = grp * 16 * 128;
-                    tma_load_2d(k_dst + off, &map_kv, 0, (int)row_k, &bars->kv_full[s]);
-                    tma_load_2d(k_dst + kKBytes / 2 + off, &map_kv, 64, (int)row_k, &bars->kv_full[s]);
-                    tma_load_2d(v_dst + off, &map_kv, 0, (int)row_v, &bars->kv_full[s]);
-                    tma_load_2d(v_dst + kVBytes / 2 + off, &map_kv, 64, (int)row_v, &bars->kv_full[s]);
-                }
-                issued = j + 1;
-            }
-            if (*aborted) {      // do not leave while copies into this block's shared memory are in flight
-                mbar_wait(&bars->q_full, 0);
-                const int first = issued > kStages ? issued - kStages : 0;
-                for (int j = first; j < issued; ++j) mbar_wait(&bars->kv_full[j % kStages], (j / kStages) & 1);
-            }
-        } else if (warp == 1 && lane == 0) {
-            // ---------------------------------------------------------------- MMA issuer
-            constexpr uint32_t id_s = idesc(kBM, kBN, 0), id_o = idesc(kBM, kHD, 1);
-            bool ok = mbar_wait(&bars->q_full, 0);
-            if (!ok) { atomicExch(error_word, 2); *aborted = 1; }
-            for (int j = 0; j < n_tiles && !*aborted; ++j) {
-                const int s = j % kStages;
-                if (!mbar_wait(&bars->kv_full[s], (j / kStages) & 1)) { atomicExch(error_word, 3); *aborted = 1; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const uint32_t k_addr = kv_s + s * (kKBytes + kVBytes), v_addr = k_addr + kKBytes;
-#pragma unroll
-                for (int k = 0; k < kHD / 16; ++k) {        // S = Q K^T over the head width
-                    const uint32_t half = k >> 2, kk = k & 3;
-                    umma(tmem_s, desc_k_major(q_s + half * (kQBytes / 2) + kk * 32),
-                         desc_k_major(k_addr + half * (kKBytes / 2) + kk * 32), id_s, k > 0 ? 1u : 0u);
-                }
-                umma_commit(&bars->s_full);
-                if (!mbar_wait(&bars->p_full, j & 1)) { atomicExch(error_word, 4); *aborted = 1; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-#pragma unroll
-                for (int k = 0; k < kBN / 16; ++k) {        // O_tile = P V over the tile's keys
-                    umma(tmem_o, desc_k_major(p_s + k * 32), desc_mn_major(v_addr + k * 2048, kVBytes / 2), id_o,
-                         k > 0 ? 1u : 0u);
-                }
-                umma_commit(&bars->o_full);
-                umma_commit(&bars->kv_empty[s]);
+                v_issued = jv + 1;
             }
         }
-    } else {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;\n" ::);
+        __syncwarp();
+        if (stop && lane == 0) {      // do not leave while copies into this block's shared memory are in flight
+            if (q_issued) mbar_wait(&bars->q_full, 0);
+            for (int j = max(0, k_issued - kKStages); j < k_issued; ++j)
+                mbar_wait(&bars->k_full[j % kKStages], (j / kKStages) & 1);
+            for (int j = max(0, v_issued - kVStages); j < v_issued; ++j)
+                mbar_wait(&bars->v_full[j % kVStages], (j / kVStages) & 1);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // -------------------------------------------------------------------- MMA issuer
+        constexpr uint32_t id_s = idesc(kBM, kBN, 0), id_o = idesc(kBM, kHD, 1);
+        auto issue_s = [&](int j) -> bool {
+            const int s = j % kKStages;
+            if (!mbar_wait(&bars->k_full[s], (j / kKStages) & 1)) return false;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const uint32_t k_addr = k_s + s * kKBytes;
+#pragma unroll
+            for (int k = 0; k < kHD / 16; ++k) {            // S = Q K^T over the head width
+                const uint32_t half = k >> 2, kk = k & 3;
+                umma(tmem_s + (j & 1) * kBN, desc_k_major(q_s + half * (kQBytes / 2) + kk * 32),
+                     desc_k_major(k_addr + half * (kKBytes / 2) + kk * 32), id_s, k > 0 ? 1u : 0u);
+            }
+            umma_commit(&bars->k_empty[s]);
+            umma_commit(&bars->s_full[j & 1]);
+            return true;
+        };
+        if (!mbar_wait(&bars->q_full, 0)) { atomicExch(error_word, 3); *aborted = 1; }
+        if (!*aborted && !issue_s(0)) { atomicExch(error_word, 4); *aborted = 1; }
+        for (int j = 0; j < n_tiles && !*aborted; ++j) {
+            if (j + 1 < n_tiles) {
+                // S(j+1) goes where PV(j-1) reads its P: MMAs into different accumulators are not
+                // ordered among themselves, so that one has to have completed
+                if (j > 0 && !mbar_wait(&bars->o_full, (j - 1) & 1)) { atomicExch(error_word, 4); *aborted = 1; break; }
+                if (!issue_s(j + 1)) { atomicExch(error_word, 4); *aborted = 1; break; }
+            }
+            const int s = j % kVStages;
+            if (!mbar_wait(&bars->v_full[s], (j / kVStages) & 1) || !mbar_wait(&bars->p_full[j & 1], (j >> 1) & 1)) {
+                atomicExch(error_word, 5);
+                *aborted = 1;
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const uint32_t v_addr = v_s + s * kVBytes;
+#pragma unroll
+            for (int k = 0; k < kBN / 16; ++k) {            // O += P V over the tile's keys
+                umma_ta(tmem_o, tmem_s + (j & 1) * kBN + k * 8, desc_mn_major(v_addr + k * 2048, kVBytes / 2), id_o,
+                        (j > 0 || k > 0) ? 1u : 0u);
+            }
+            umma_commit(&bars->v_empty[s]);
+            umma_commit(&bars->o_full);
+        }
+        if (*aborted) {      // tensor memory is freed below: let the MMAs in flight end first
+            umma_commit(&bars->drain);
+            mbar_wait(&bars->drain, 0);
+        }
+    } else if (warp >= 4) {
         // -------------------------------------------------------------------- softmax, one row per thread
         const int quad = warp & 3, r = quad * 32 + lane;
         const int pos = first_pos + r;
         const int min_key = window > 0 ? pos - window + 1 : 0;
         const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
-        float acc[kHD];
-#pragma unroll
-        for (int i = 0; i < kHD; ++i) acc[i] = 0.0f;
-        float m_run = -INFINITY, l_run = 0.0f;
-        for (int j = 0; j < n_tiles; ++j) {
-            if (!mbar_wait(&bars->s_full, j & 1)) {
-                if (lane == 0) atomicExch(error_word, 5);
+        float m_ref = -INFINITY, l_run = 0.0f;
+        bool alive = !*aborted;
+        for (int j = 0; j < n_tiles && alive; ++j) {
+            const uint32_t t_s = tmem_s + lane_sel + (j & 1) * kBN;
+            if (!mbar_wait(&bars->s_full[j & 1], (j >> 1) & 1)) {
+                atomicExch(error_word, 6);
                 *aborted = 1;
             }
-            if (*aborted) break;
+            if (__any_sync(0xffffffffu, *aborted != 0)) { alive = false; break; }     // a warp leaves as one
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            uint32_t s0[32], s1[32];
-            tmem_ld32(tmem_s + lane_sel, s0);
-            tmem_ld32(tmem_s + lane_sel + 32, s1);
+            uint32_t sv[kBN];
+            tmem_ld32(t_s, *reinterpret_cast<uint32_t(*)[32]>(sv));
+            tmem_ld32(t_s + 32, *reinterpret_cast<uint32_t(*)[32]>(sv + 32));
             tmem_ld_wait();
             const int key0 = (kt_first + j) * kBN;
-            float sv[kBN];
-            float tile_max = -INFINITY;
+            // only tiles on the diagonal or at the window's far edge hold keys some row may not see
+            if (key0 + kBN - 1 > first_pos || (window > 0 && key0 < last_pos - window + 1)) {
 #pragma unroll
-            for (int i = 0; i < kBN; ++i) {
-                const int key = key0 + i;
-                const float raw = __uint_as_float(i < 32 ? s0[i] : s1[i - 32]);
-                sv[i] = (key <= pos && key >= min_key) ? raw * scale_log2e : -INFINITY;
-                tile_max = fmaxf(tile_max, sv[i]);
-            }
-            const float m_new = fmaxf(m_run, tile_max);
-            const float m_safe = m_new == -INFINITY ? 0.0f : m_new;
-            const float corr = exp2f(m_run - m_safe);
-            m_run = m_new;
-            float sum = 0.0f;
-            // P as bfloat16 into the K-major swizzled operand layout: row r, 16-byte chunk c at c ^ (r & 7)
-            const uint32_t p_row = p_s + r * 128;
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                uint32_t w[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float a = exp2f(sv[c * 8 + 2 * e] - m_safe), b = exp2f(sv[c * 8 + 2 * e + 1] - m_safe);
-                    sum += a + b;
-                    w[e] = pack2(a, b);
+                for (int i = 0; i < kBN; ++i) {
+                    const int key = key0 + i;
+                    if (key > pos || key < min_key) sv[i] = 0xff800000u;      // -inf
                 }
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(p_row + ((c ^ (r & 7)) << 4)), "r"(w[0]),
-                             "r"(w[1]), "r"(w[2]), "r"(w[3])
-                             : "memory");
             }
-            l_run = l_run * corr + sum;
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");     // P visible to the tensor core
-            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");  // S has been read
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int i = 0; i < kBN; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sv[i]));
+            const float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2e;
+            // raise the reference maximum only when this tile is far above it
+            const bool raise = tile_max > m_ref + kRaise;
+            float factor = 1.0f;
+            if (raise) {
+                factor = ex2(m_ref - tile_max);             // 0 for the first keys a row sees
+                m_ref = tile_max;
+                l_run *= factor;
+            }
+            // Every warp follows every phase of o_full (a parity wait can only tell the current phase
+            // from the one before it): PV(j-1) has completed.  Early if O must be scaled, else late.
+            auto wait_prev = [&]() -> bool {
+                if (!mbar_wait(&bars->o_full, (j - 1) & 1)) {
+                    atomicExch(error_word, 7);
+                    *aborted = 1;
+                }
+                return !__any_sync(0xffffffffu, *aborted != 0);
+            };
+            const bool scale_o = j > 0 && __any_sync(0xffffffffu, raise);
+            if (scale_o) {
+                if (!wait_prev()) { alive = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll 1
+                for (int c = 0; c < kHD; c += 32) {
+                    uint32_t o[32];
+                    tmem_ld32(tmem_o + lane_sel + c, o);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+                    tmem_st32(tmem_o + lane_sel + c, o);
+                }
+                tmem_st_wait();
+            }
+            const float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
+            float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            uint32_t pw[kBN / 2];
+#pragma unroll
+            for (int i = 0; i < kBN; i += 2) {
+                const float a = ex2(fmaf(__uint_as_float(sv[i]), scale_log2e, -m_use));
+                const float b = ex2(fmaf(__uint_as_float(sv[i + 1]), scale_log2e, -m_use));
+                sum[(i >> 1) & 3] += a + b;
+                pw[i >> 1] = pack2(a, b);
+            }
+            l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+            if (j > 0 && !scale_o && !wait_prev()) { alive = false; break; }
+            tmem_st32(t_s, pw);                              // P over the S it came from
+            tmem_st_wait();
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bars->p_full);
-            if (!mbar_wait(&bars->o_full, j & 1)) {
-                if (lane == 0) atomicExch(error_word, 6);
+            if (lane == 0) mbar_arrive(&bars->p_full[j & 1]);
+        }
+        if (alive) {
+            if (!mbar_wait(&bars->o_full, (n_tiles - 1) & 1)) {
+                atomicExch(error_word, 8);
                 *aborted = 1;
             }
-            if (*aborted) break;
+        }
+        // ---- result: through shared memory (the query tile is no longer needed) for whole-line stores
+        asm volatile("bar.sync 1, 128;\n" ::: "memory");
+        if (alive && !__any_sync(0xffffffffu, *aborted != 0)) {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-#pragma unroll
+            const float inv = 1.0f / l_run;
+            const uint32_t stage_row = q_s + r * 256;
+#pragma unroll 1
             for (int c = 0; c < kHD; c += 32) {
                 uint32_t o[32];
                 tmem_ld32(tmem_o + lane_sel + c, o);
                 tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) acc[c + i] = acc[c + i] * corr + __uint_as_float(o[i]);
-            }
-        }
-        // ---- result: through shared memory (the query tile is no longer needed) for whole-line stores
-        const bool finished = !*aborted;
-        asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-        asm volatile("bar.sync 1, 128;\n" ::: "memory");       // all softmax warps are done with Q and P
-        if (finished) {
-            const float inv = 1.0f / l_run;
-            const uint32_t stage_row = q_s + r * 256;
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    uint32_t w[4];
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
-                uint32_t w[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) w[e] = pack2(acc[c * 8 + 2 * e] * inv, acc[c * 8 + 2 * e + 1] * inv);
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(stage_row + ((c ^ (r & 15)) << 4)),
-                             "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
-                             : "memory");
+                    for (int e = 0; e < 4; ++e)
+                        w[e] = pack2(__uint_as_float(o[q4 * 8 + 2 * e]) * inv, __uint_as_float(o[q4 * 8 + 2 * e + 1]) * inv);
+                    const int chunk = c / 8 + q4;
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(stage_row + ((chunk ^ (r & 15)) << 4)),
+                                 "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                                 : "memory");
+                }
             }
             __syncwarp();
             // a warp stores its 32 rows, two rows (2 x 256 bytes) per instruction
