@@ -390,9 +390,10 @@ def test_prefill_kernel_segments(ops, nh, nkv, hd, ps, window):
 
 
 @pytest.mark.parametrize("nh,nkv,ps,window", [(8, 2, 16, None), (3, 3, 32, None), (6, 1, 16, 70), (2, 1, 64, 9),
-                                              (4, 2, 48, 200)])
+                                              (4, 2, 48, 200), (5, 1, 16, None), (3, 1, 32, 130)])
 def test_prefill_tcgen05_kernel_segments(ops, nh, nkv, ps, window):
-    """The tcgen05 kernel (head width 128, blocks of 128 rows) on segments that start inside a
+    """The tcgen05 kernel (head width 128; a thread block takes two heads at 128 positions where
+    the group is even, else 256 positions of one head) on segments that start inside a
     request, are shorter and longer than a block, start and end off the edges of key tiles
     and pages; each row's query points at one key (the window's first, the row's own, the
     last of the tile before, the one before its own), so that a key that is missed, masked
@@ -407,7 +408,7 @@ def test_prefill_tcgen05_kernel_segments(ops, nh, nkv, ps, window):
     seg_info, tiles, pos_rows, slot_rows, row = [], [], [], [], 0
     for i, (s, p0, n) in enumerate(segs):
         seg_info.append([s, row, n, p0])
-        tiles += [[i, off] for off in range(0, n, 128)]
+        tiles += [[i, off] for off in range(0, n, ops.prefill_tcgen05_block_rows(nh, nkv))]
         pos_rows += list(range(p0, p0 + n))
         slot_rows += [s] * n
         row += n

@@ -7,27 +7,32 @@
 // kernels/src/paged_attention_cuda.cu:70-120; the mma.sync version of this kernel is
 // attention_prefill.cu, which stays for head width 64 and as the comparison in the tests.)
 //
-// A block owns 128 consecutive query rows of one portion and one query head, and walks the
-// request's keys in tiles of 64.
-//   warp 0   producer: eight lanes each look one group of 16 keys up in the block table and issue
-//            one TMA load (128-byte swizzle) of 16 keys x 64 columns into a ring of three key
-//            tiles and a ring of two value tiles; the 128 x 128 query tile is loaded once.
-//   warp 1   issues the MMAs (one thread).  S[128 x 64] = Q K^T (8 x tcgen05.mma 128x64x16, both
-//            operands K-major in shared memory) goes into one of two S buffers, one tile ahead
-//            of the softmax (and only after the P V product that read that buffer has completed).  Once the softmax has put P into tensor memory (over the S it
-//            read), O[128 x 128] += P V (4 x tcgen05.mma 128x128x16 with A from tensor memory and
-//            V as it lies in the cache: an MN-major operand).  tcgen05.commit frees the stages
-//            and tells the softmax warps.
-//   warps 4-7 softmax, one query row per thread (TMEM lane = row): read S, mask by the row's
-//            position and window where the tile needs it, softmax in base 2 in float32 against
-//            a reference maximum that is only raised when a tile exceeds it by more than 2^8
-//            (then O, which stays in tensor memory, and the row sum are scaled down: rare after
-//            the first tiles), write P as bfloat16 back into tensor memory.  At the end O / sum
-//            goes through shared memory to whole-line stores.
-// Two blocks fit on an SM (112 KB of shared memory, 256 TMEM columns each), so that one
-// block's MMAs run under the other's softmax.  Every mbarrier wait is bounded; on a timeout
-// the block sets the caller's error word, stops, waits (bounded) for copies in flight, frees
-// its tensor memory and returns.
+// A block owns TWO tiles of 128 query rows that read the same keys and values, so that every
+// key tile fetched from L2 serves 256 rows (with one tile per block the kernel ran at the L2's
+// bandwidth): two query heads of one key/value head at the same 128 positions where the group
+// is even, else two consecutive blocks of 128 positions of one head.  It walks the request's
+// keys in tiles of 64; a tile outside one of the two ranges is skipped for that one.
+//   warp 0    producer: eight lanes each look one group of 16 keys up in the block table and issue
+//             one TMA load (128-byte swizzle) of 16 keys x 64 columns into rings of five key and
+//             five value tiles; the two 128 x 128 query tiles are loaded once.
+//   warp 1    issues the MMAs (one thread).  Per query tile, S[128 x 64] = Q K^T (8 x tcgen05.mma
+//             128x64x16, both operands K-major in shared memory) goes into one of two S buffers,
+//             one key tile ahead of the softmax (and only after the P V product that read that
+//             buffer has completed: MMAs into different accumulators are not ordered).  Once the
+//             softmax has put P into tensor memory (over the S it read), O[128 x 128] += P V
+//             (4 x tcgen05.mma 128x128x16 with A from tensor memory and V as it lies in the
+//             cache: an MN-major operand).  tcgen05.commit frees the stages and tells the
+//             softmax warps.
+//   warps 4-7, 8-11  softmax of the first and second query tile, one row per thread (TMEM lane =
+//             row): read S, mask by the row's position and window where the tile needs it,
+//             softmax in base 2 in float32 against a reference maximum that is only raised when
+//             a tile exceeds it by more than 2^8 (then O, which stays in tensor memory, and the
+//             row sum are scaled down: rare after the first tiles), write P as bfloat16 back
+//             into tensor memory.  At the end O / sum goes through shared memory to whole-line
+//             stores.
+// One block per SM (224 KB of shared memory, all 512 TMEM columns).  Every mbarrier wait is
+// bounded; on a timeout the block sets the caller's error word, stops, waits (bounded) for
+// copies and MMAs in flight, frees its tensor memory and returns.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -39,11 +44,12 @@ constexpr int kHD = 128, kBM = 128, kBN = 64;
 constexpr int kQBytes = kBM * kHD * 2;            // 32 KB: two column halves of [128 rows x 128 B]
 constexpr int kKBytes = kBN * kHD * 2;            // 16 KB: two column halves of [64 keys x 128 B]
 constexpr int kVBytes = kKBytes;
-constexpr int kKStages = 3, kVStages = 2;
-constexpr int kTilesBytes = kQBytes + kKStages * kKBytes + kVStages * kVBytes;   // 112 KB
-constexpr int kSmemBytes = kTilesBytes + 256;     // + barriers and the TMEM slot
-constexpr int kThreads = 256;
-constexpr uint32_t kTmemCols = 256;               // S (and P over it): columns 0..63 and 64..127, O: 128..255
+constexpr int kKStages = 5, kVStages = 5;
+constexpr int kTilesBytes = 2 * kQBytes + kKStages * kKBytes + kVStages * kVBytes;   // 224 KB
+constexpr int kSmemBytes = kTilesBytes + 512;     // + barriers and the TMEM slot
+constexpr int kThreads = 384;
+// query tile x: S buffers (and P over them) at columns x * 128 + {0, 64}, O at 256 + x * 128
+constexpr uint32_t kTmemCols = 512;
 constexpr float kRaise = 8.0f;                    // the reference maximum follows only beyond 2^8
 constexpr int kSpinLimit = 1 << 20;
 
@@ -155,9 +161,15 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 
 struct Barriers {
     uint64_t q_full, k_full[kKStages], k_empty[kKStages], v_full[kVStages], v_empty[kVStages];
-    uint64_t s_full[2], p_full[2], o_full, drain;
+    uint64_t s_full[2][2], p_full[2][2], o_full[2], drain;
     uint32_t tmem_slot;
     int abort_flag;
+};
+static_assert(sizeof(Barriers) <= 512, "barrier block");
+
+// One of the block's two query tiles: `n` key tiles from `kt_first` on (n = 0: no such tile).
+struct QTile {
+    int head, q_off, rows, first_pos, last_pos, kt_first, n;
 };
 
 // The 16 keys from key0 on, for K (kv = 0) or V (kv = 1): the row of the cache seen as
@@ -171,39 +183,53 @@ __device__ __forceinline__ int cache_row(const int* table, int key0, int last_po
     return (int)((((long long)page * 2 + kv) * kv_heads + g) * page_size + (key0 % page_size));
 }
 
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 1)
 paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                                   const int* __restrict__ seg_info, const int* __restrict__ tiles,
                                   const int* __restrict__ block_table, int max_pages, int page_size, int q_heads,
-                                  int kv_heads, long long kv_rows, int window, float scale_log2e,
+                                  int kv_heads, long long kv_rows, int window, float scale_log2e, int pair_heads,
                                   bf16* __restrict__ out, int* __restrict__ error_word) {
     extern __shared__ __align__(1024) unsigned char smem[];
     Barriers* bars = reinterpret_cast<Barriers*>(smem + kTilesBytes);
     volatile int* aborted = &bars->abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t q_s = sa(smem), k_s = q_s + kQBytes, v_s = k_s + kKStages * kKBytes;
+    const uint32_t q_s = sa(smem), k_s = q_s + 2 * kQBytes, v_s = k_s + kKStages * kKBytes;
 
-    const int seg = tiles[2 * blockIdx.x], q_off = tiles[2 * blockIdx.x + 1];
-    const int head = blockIdx.y;
+    const int seg = tiles[2 * blockIdx.x], q_off0 = tiles[2 * blockIdx.x + 1];
     const int slot = seg_info[4 * seg], start = seg_info[4 * seg + 1];
     const int len = seg_info[4 * seg + 2], pos0 = seg_info[4 * seg + 3];
-    const int g = head / (q_heads / kv_heads);
-    const int rows_here = min(kBM, len - q_off);
-    const int first_pos = pos0 + q_off, last_pos = first_pos + rows_here - 1;
-    const int lo_all = (window > 0 && first_pos - window + 1 > 0) ? first_pos - window + 1 : 0;
-    const int kt_first = lo_all / kBN, kt_last = last_pos / kBN;
-    const int n_tiles = kt_last - kt_first + 1;
+    QTile qt[2];
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        QTile& t = qt[x];
+        t.head = pair_heads ? 2 * blockIdx.y + x : blockIdx.y;
+        t.q_off = pair_heads ? q_off0 : q_off0 + x * kBM;
+        t.rows = min(kBM, len - t.q_off);
+        t.first_pos = pos0 + t.q_off;
+        t.last_pos = t.first_pos + t.rows - 1;
+        const int lo = (window > 0 && t.first_pos - window + 1 > 0) ? t.first_pos - window + 1 : 0;
+        t.kt_first = lo / kBN;
+        t.n = t.rows > 0 ? t.last_pos / kBN - t.kt_first + 1 : 0;
+    }
+    const int g = qt[0].head / (q_heads / kv_heads);           // both tiles read this key/value head
+    const bool two = qt[1].n > 0;
+    const int kt_lo = two ? min(qt[0].kt_first, qt[1].kt_first) : qt[0].kt_first;
+    const int kt_hi = two ? max(qt[0].kt_first + qt[0].n, qt[1].kt_first + qt[1].n) - 1 : qt[0].kt_first + qt[0].n - 1;
+    const int n_tiles = kt_hi - kt_lo + 1;
+    const int last_pos = two ? max(qt[0].last_pos, qt[1].last_pos) : qt[0].last_pos;
 
     if (threadIdx.x == 0) {
         if (q_s & 1023) atomicExch(error_word, 9);         // operand tiles need a 1024-byte aligned window
         mbar_init(&bars->q_full, 1);
         for (int s = 0; s < kKStages; ++s) { mbar_init(&bars->k_full[s], 1); mbar_init(&bars->k_empty[s], 1); }
         for (int s = 0; s < kVStages; ++s) { mbar_init(&bars->v_full[s], 1); mbar_init(&bars->v_empty[s], 1); }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(&bars->s_full[b], 1);
-            mbar_init(&bars->p_full[b], 4);                 // one arrival per softmax warp
+        for (int x = 0; x < 2; ++x) {
+            for (int b = 0; b < 2; ++b) {
+                mbar_init(&bars->s_full[x][b], 1);
+                mbar_init(&bars->p_full[x][b], 4);          // one arrival per softmax warp
+            }
+            mbar_init(&bars->o_full[x], 1);
         }
-        mbar_init(&bars->o_full, 1);
         mbar_init(&bars->drain, 1);
         bars->abort_flag = (q_s & 1023) ? 1 : 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -217,7 +243,7 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    const uint32_t tmem_s = bars->tmem_slot, tmem_o = tmem_s + 128;
+    const uint32_t tmem = bars->tmem_slot;
 
     if (warp == 0) {
         // -------------------------------------------------------------------- producer (the whole warp)
@@ -227,9 +253,14 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
         bool stop = __any_sync(0xffffffffu, *aborted != 0);
         const bool q_issued = !stop;
         if (!stop && lane == 0) {
-            mbar_expect_tx(&bars->q_full, kQBytes);
-            tma_load_2d(q_s, &map_q, head * kHD, start + q_off, &bars->q_full);
-            tma_load_2d(q_s + kQBytes / 2, &map_q, head * kHD + 64, start + q_off, &bars->q_full);
+            mbar_expect_tx(&bars->q_full, two ? 2 * kQBytes : kQBytes);
+#pragma unroll
+            for (int x = 0; x < 2; ++x) {
+                if (qt[x].n == 0) continue;
+                tma_load_2d(q_s + x * kQBytes, &map_q, qt[x].head * kHD, start + qt[x].q_off, &bars->q_full);
+                tma_load_2d(q_s + x * kQBytes + kQBytes / 2, &map_q, qt[x].head * kHD + 64, start + qt[x].q_off,
+                            &bars->q_full);
+            }
         }
         const int grp = lane >> 1, half = lane & 1;
         int k_issued = 0, v_issued = 0;
@@ -245,8 +276,8 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
                 if (lane == 0) mbar_expect_tx(&bars->k_full[s], kKBytes);
                 __syncwarp();
                 if (lane < 8) {
-                    const int row = cache_row(table, (kt_first + jk) * kBN + grp * 16, last_pos, page_size, kv_heads,
-                                              g, 0, kv_rows);
+                    const int row = cache_row(table, (kt_lo + jk) * kBN + grp * 16, last_pos, page_size, kv_heads, g, 0,
+                                              kv_rows);
                     tma_load_2d(k_s + s * kKBytes + half * (kKBytes / 2) + grp * 2048, &map_kv, half * 64, row,
                                 &bars->k_full[s]);
                 }
@@ -261,8 +292,8 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
                 if (lane == 0) mbar_expect_tx(&bars->v_full[s], kVBytes);
                 __syncwarp();
                 if (lane < 8) {
-                    const int row = cache_row(table, (kt_first + jv) * kBN + grp * 16, last_pos, page_size, kv_heads,
-                                              g, 1, kv_rows);
+                    const int row = cache_row(table, (kt_lo + jv) * kBN + grp * 16, last_pos, page_size, kv_heads, g, 1,
+                                              kv_rows);
                     tma_load_2d(v_s + s * kVBytes + half * (kVBytes / 2) + grp * 2048, &map_kv, half * 64, row,
                                 &bars->v_full[s]);
                 }
@@ -280,62 +311,74 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
     } else if (warp == 1 && lane == 0) {
         // -------------------------------------------------------------------- MMA issuer
         constexpr uint32_t id_s = idesc(kBM, kBN, 0), id_o = idesc(kBM, kHD, 1);
-        auto issue_s = [&](int j) -> bool {
+        // S of both query tiles for the block's key tile j; 0 or the error code of the wait that gave up
+        auto issue_s = [&](int j) -> int {
             const int s = j % kKStages;
-            if (!mbar_wait(&bars->k_full[s], (j / kKStages) & 1)) return false;
-            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            if (!mbar_wait(&bars->k_full[s], (j / kKStages) & 1)) return 4;
             const uint32_t k_addr = k_s + s * kKBytes;
 #pragma unroll
-            for (int k = 0; k < kHD / 16; ++k) {            // S = Q K^T over the head width
-                const uint32_t half = k >> 2, kk = k & 3;
-                umma(tmem_s + (j & 1) * kBN, desc_k_major(q_s + half * (kQBytes / 2) + kk * 32),
-                     desc_k_major(k_addr + half * (kKBytes / 2) + kk * 32), id_s, k > 0 ? 1u : 0u);
+            for (int x = 0; x < 2; ++x) {
+                const int jx = kt_lo + j - qt[x].kt_first;
+                if (jx < 0 || jx >= qt[x].n) continue;
+                // S(jx) goes where PV(jx-2) read its P: that one has to have completed
+                if (jx >= 2 && !mbar_wait(&bars->o_full[x], (jx - 2) & 1)) return 5;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t d = tmem + x * 128 + (jx & 1) * kBN, q_addr = q_s + x * kQBytes;
+#pragma unroll
+                for (int k = 0; k < kHD / 16; ++k) {        // S = Q K^T over the head width
+                    const uint32_t half = k >> 2, kk = k & 3;
+                    umma(d, desc_k_major(q_addr + half * (kQBytes / 2) + kk * 32),
+                         desc_k_major(k_addr + half * (kKBytes / 2) + kk * 32), id_s, k > 0 ? 1u : 0u);
+                }
+                umma_commit(&bars->s_full[x][jx & 1]);
             }
             umma_commit(&bars->k_empty[s]);
-            umma_commit(&bars->s_full[j & 1]);
-            return true;
+            return 0;
         };
-        if (!mbar_wait(&bars->q_full, 0)) { atomicExch(error_word, 3); *aborted = 1; }
-        if (!*aborted && !issue_s(0)) { atomicExch(error_word, 4); *aborted = 1; }
-        for (int j = 0; j < n_tiles && !*aborted; ++j) {
-            if (j + 1 < n_tiles) {
-                // S(j+1) goes where PV(j-1) reads its P: MMAs into different accumulators are not
-                // ordered among themselves, so that one has to have completed
-                if (j > 0 && !mbar_wait(&bars->o_full, (j - 1) & 1)) { atomicExch(error_word, 4); *aborted = 1; break; }
-                if (!issue_s(j + 1)) { atomicExch(error_word, 4); *aborted = 1; break; }
-            }
+        int err = mbar_wait(&bars->q_full, 0) ? 0 : 3;
+        if (!err && !*aborted) err = issue_s(0);
+        for (int j = 0; j < n_tiles && !err && !*aborted; ++j) {
+            if (j + 1 < n_tiles && (err = issue_s(j + 1)) != 0) break;
             const int s = j % kVStages;
-            if (!mbar_wait(&bars->v_full[s], (j / kVStages) & 1) || !mbar_wait(&bars->p_full[j & 1], (j >> 1) & 1)) {
-                atomicExch(error_word, 5);
-                *aborted = 1;
-                break;
-            }
-            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            if (!mbar_wait(&bars->v_full[s], (j / kVStages) & 1)) { err = 6; break; }
             const uint32_t v_addr = v_s + s * kVBytes;
 #pragma unroll
-            for (int k = 0; k < kBN / 16; ++k) {            // O += P V over the tile's keys
-                umma_ta(tmem_o, tmem_s + (j & 1) * kBN + k * 8, desc_mn_major(v_addr + k * 2048, kVBytes / 2), id_o,
-                        (j > 0 || k > 0) ? 1u : 0u);
+            for (int x = 0; x < 2; ++x) {
+                const int jx = kt_lo + j - qt[x].kt_first;
+                if (jx < 0 || jx >= qt[x].n) continue;
+                if (!mbar_wait(&bars->p_full[x][jx & 1], (jx >> 1) & 1)) { err = 7; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t p = tmem + x * 128 + (jx & 1) * kBN, d = tmem + 256 + x * 128;
+#pragma unroll
+                for (int k = 0; k < kBN / 16; ++k) {        // O += P V over the tile's keys
+                    umma_ta(d, p + k * 8, desc_mn_major(v_addr + k * 2048, kVBytes / 2), id_o,
+                            (jx > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(&bars->o_full[x]);
             }
+            if (err) break;
             umma_commit(&bars->v_empty[s]);
-            umma_commit(&bars->o_full);
         }
+        if (err) { atomicExch(error_word, err); *aborted = 1; }
         if (*aborted) {      // tensor memory is freed below: let the MMAs in flight end first
             umma_commit(&bars->drain);
             mbar_wait(&bars->drain, 0);
         }
     } else if (warp >= 4) {
         // -------------------------------------------------------------------- softmax, one row per thread
-        const int quad = warp & 3, r = quad * 32 + lane;
-        const int pos = first_pos + r;
+        const int x = (warp - 4) >> 2, quad = warp & 3, r = quad * 32 + lane;
+        const QTile t = x ? qt[1] : qt[0];
+        const int pos = t.first_pos + r;
         const int min_key = window > 0 ? pos - window + 1 : 0;
         const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
+        const uint32_t tmem_sx = tmem + lane_sel + x * 128, tmem_ox = tmem + lane_sel + 256 + x * 128;
+        uint64_t* const o_full = &bars->o_full[x];
         float m_ref = -INFINITY, l_run = 0.0f;
-        bool alive = !*aborted;
-        for (int j = 0; j < n_tiles && alive; ++j) {
-            const uint32_t t_s = tmem_s + lane_sel + (j & 1) * kBN;
-            if (!mbar_wait(&bars->s_full[j & 1], (j >> 1) & 1)) {
-                atomicExch(error_word, 6);
+        bool alive = t.n > 0 && !*aborted;
+        for (int j = 0; j < t.n && alive; ++j) {
+            const uint32_t t_s = tmem_sx + (j & 1) * kBN;
+            if (!mbar_wait(&bars->s_full[x][j & 1], (j >> 1) & 1)) {
+                atomicExch(error_word, 10);
                 *aborted = 1;
             }
             if (__any_sync(0xffffffffu, *aborted != 0)) { alive = false; break; }     // a warp leaves as one
@@ -344,9 +387,9 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
             tmem_ld32(t_s, *reinterpret_cast<uint32_t(*)[32]>(sv));
             tmem_ld32(t_s + 32, *reinterpret_cast<uint32_t(*)[32]>(sv + 32));
             tmem_ld_wait();
-            const int key0 = (kt_first + j) * kBN;
+            const int key0 = (t.kt_first + j) * kBN;
             // only tiles on the diagonal or at the window's far edge hold keys some row may not see
-            if (key0 + kBN - 1 > first_pos || (window > 0 && key0 < last_pos - window + 1)) {
+            if (key0 + kBN - 1 > t.first_pos || (window > 0 && key0 < t.last_pos - window + 1)) {
 #pragma unroll
                 for (int i = 0; i < kBN; ++i) {
                     const int key = key0 + i;
@@ -368,8 +411,8 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
             // Every warp follows every phase of o_full (a parity wait can only tell the current phase
             // from the one before it): PV(j-1) has completed.  Early if O must be scaled, else late.
             auto wait_prev = [&]() -> bool {
-                if (!mbar_wait(&bars->o_full, (j - 1) & 1)) {
-                    atomicExch(error_word, 7);
+                if (!mbar_wait(o_full, (j - 1) & 1)) {
+                    atomicExch(error_word, 11);
                     *aborted = 1;
                 }
                 return !__any_sync(0xffffffffu, *aborted != 0);
@@ -381,11 +424,11 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
 #pragma unroll 1
                 for (int c = 0; c < kHD; c += 32) {
                     uint32_t o[32];
-                    tmem_ld32(tmem_o + lane_sel + c, o);
+                    tmem_ld32(tmem_ox + c, o);
                     tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
-                    tmem_st32(tmem_o + lane_sel + c, o);
+                    tmem_st32(tmem_ox + c, o);
                 }
                 tmem_st_wait();
             }
@@ -405,24 +448,27 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
             tmem_st_wait();
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bars->p_full[j & 1]);
+            if (lane == 0) mbar_arrive(&bars->p_full[x][j & 1]);
         }
         if (alive) {
-            if (!mbar_wait(&bars->o_full, (n_tiles - 1) & 1)) {
-                atomicExch(error_word, 8);
+            if (!mbar_wait(o_full, (t.n - 1) & 1)) {
+                atomicExch(error_word, 12);
                 *aborted = 1;
             }
         }
-        // ---- result: through shared memory (the query tile is no longer needed) for whole-line stores
-        asm volatile("bar.sync 1, 128;\n" ::: "memory");
+        // ---- result: through shared memory (this query tile is no longer needed) for whole-line stores
+        if (t.n > 0) {
+            if (x == 0) asm volatile("bar.sync 1, 128;\n" ::: "memory");
+            else asm volatile("bar.sync 2, 128;\n" ::: "memory");
+        }
         if (alive && !__any_sync(0xffffffffu, *aborted != 0)) {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const float inv = 1.0f / l_run;
-            const uint32_t stage_row = q_s + r * 256;
+            const uint32_t stage = q_s + x * kQBytes, stage_row = stage + r * 256;
 #pragma unroll 1
             for (int c = 0; c < kHD; c += 32) {
                 uint32_t o[32];
-                tmem_ld32(tmem_o + lane_sel + c, o);
+                tmem_ld32(tmem_ox + c, o);
                 tmem_ld_wait();
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
@@ -441,12 +487,12 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
 #pragma unroll 1
             for (int i = 0; i < 16; ++i) {
                 const int rr = quad * 32 + i * 2 + (lane >> 4), c = lane & 15;
-                if (rr < rows_here) {
+                if (rr < t.rows) {
                     uint4 val;
                     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
                                  : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w)
-                                 : "r"(q_s + rr * 256 + ((c ^ (rr & 15)) << 4)));
-                    *reinterpret_cast<uint4*>(out + ((size_t)(start + q_off + rr) * q_heads + head) * kHD + c * 8) = val;
+                                 : "r"(stage + rr * 256 + ((c ^ (rr & 15)) << 4)));
+                    *reinterpret_cast<uint4*>(out + ((size_t)(start + t.q_off + rr) * q_heads + t.head) * kHD + c * 8) = val;
                 }
             }
         }
@@ -454,7 +500,7 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_s), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(kTmemCols) : "memory");
     }
 }
 
@@ -492,7 +538,14 @@ static bool make_map(CUtensorMap* map, const void* base, long long rows, long lo
 
 using namespace tllm;
 
-// tiles: int[n_tiles][2] = segment, offset of the block's first query row (blocks of 128 rows).
+// Query rows per block of the tile list: 128 where two heads of a key/value head share a block
+// (an even group), else 256 (two blocks of positions of one head).
+extern "C" int tllm_paged_attention_prefill_tc_rows(int q_heads, int kv_heads) {
+    return (kv_heads > 0 && q_heads % kv_heads == 0 && (q_heads / kv_heads) % 2 == 0) ? 128 : 256;
+}
+
+// tiles: int[n_tiles][2] = segment, offset of the block's first query row; the offsets are the
+// multiples of tllm_paged_attention_prefill_tc_rows() below the segment's length.
 // q [tokens, q_heads * 128], cache [num_pages, 2, kv_heads, page_size, 128], both bfloat16.
 extern "C" int tllm_paged_attention_prefill_tc(
     const void* q, int tokens, const void* cache, int num_pages, const int* seg_info, const int* tiles, int n_tiles,
@@ -518,8 +571,10 @@ extern "C" int tllm_paged_attention_prefill_tc(
         if (e != cudaSuccess) { set_error("paged_attention_prefill_tc: %s", cudaGetErrorString(e)); return (int)e; }
         configured = true;
     }
-    pftc::paged_attention_prefill_tc_kernel<<<dim3(n_tiles, q_heads), pftc::kThreads, pftc::kSmemBytes, stream>>>(
+    const int pair_heads = tllm_paged_attention_prefill_tc_rows(q_heads, kv_heads) == 128;
+    pftc::paged_attention_prefill_tc_kernel<<<dim3(n_tiles, pair_heads ? q_heads / 2 : q_heads), pftc::kThreads,
+                                              pftc::kSmemBytes, stream>>>(
         mq, mkv, seg_info, tiles, block_table, max_pages, page_size, q_heads, kv_heads, kv_rows, window,
-        scale * 1.4426950408889634f, (bf16*)out, error_word);
+        scale * 1.4426950408889634f, pair_heads, (bf16*)out, error_word);
     return finish_launch("paged_attention_prefill_tc");
 }

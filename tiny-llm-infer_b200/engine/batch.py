@@ -45,12 +45,14 @@ class StepContext:
     seg_info: Optional[torch.Tensor] = None   # [segments, 4] = slot, start, length, pos0
     # rows of one-token segments (None: every row is one) and, for the longer segments,
     # blocks of 64 query rows as (segment, offset) pairs, the first n_tiles128 of which start at
-    # multiples of 128 rows (the list of 128-row blocks); faster attention kernels use them
+    # multiples of 128 rows and the first n_tiles256 of these at multiples of 256 (the lists of
+    # 128- and 256-row blocks); faster attention kernels use them
     dec_rows: Optional[torch.Tensor] = None
     n_dec: int = 0
     pf_tiles: Optional[torch.Tensor] = None
     n_tiles: int = 0
     n_tiles128: int = 0
+    n_tiles256: int = 0
     decode_only: bool = False
     max_context: int = 0          # largest position + 1 among the rows
     max_segment: int = 0          # longest segment

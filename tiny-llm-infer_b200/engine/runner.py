@@ -167,10 +167,11 @@ class ModelRunner:
         o_tiles = o_dec + n_dec
         used = o_tiles + 2 * n_tiles
         host[o_dec:o_tiles] = dec_rows
-        # blocks with the most keys start first; those at a multiple of 128 rows lead the list, so
-        # that its head is also the list of 128-row blocks
-        tiles.sort(key=lambda t: (t[1] % 128 != 0, -t[2]))
+        # blocks with the most keys start first; those at a multiple of 256 rows lead the list, then
+        # those at other multiples of 128, so that its heads are also the lists of 256- and 128-row blocks
+        tiles.sort(key=lambda t: (t[1] % 256 != 0, t[1] % 128 != 0, -t[2]))
         n_tiles128 = sum(1 for t in tiles if t[1] % 128 == 0)
+        n_tiles256 = sum(1 for t in tiles if t[1] % 256 == 0)
         for i, (s, off, _) in enumerate(tiles):
             host[o_tiles + 2 * i], host[o_tiles + 2 * i + 1] = s, off
         self.cache.sync()
@@ -186,7 +187,7 @@ class ModelRunner:
             token_slot=d[o_slot:o_slot + row], want_rows=d[o_want:o_want + n_want],
             segments=segments, seg_info=d[o_seg:o_seg + 4 * len(segments)].view(-1, 4),
             dec_rows=None if n_dec == row else d[o_dec:o_tiles], n_dec=n_dec,
-            pf_tiles=d[o_tiles:used].view(-1, 2), n_tiles=n_tiles, n_tiles128=n_tiles128,
+            pf_tiles=d[o_tiles:used].view(-1, 2), n_tiles=n_tiles, n_tiles128=n_tiles128, n_tiles256=n_tiles256,
             decode_only=(max_seg == 1), max_context=max_ctx, max_segment=max_seg)
         return ctx, commits
 

@@ -81,6 +81,8 @@ def _declare(h) -> None:
         fn = getattr(h, name)
         fn.argtypes = args
         fn.restype = i32
+    h.tllm_paged_attention_prefill_tc_rows.argtypes = [i32, i32]
+    h.tllm_paged_attention_prefill_tc_rows.restype = i32
     h.tllm_uniform_of.argtypes = [ctypes.c_ulonglong, i32]
     h.tllm_uniform_of.restype = f32
 
@@ -250,11 +252,17 @@ def paged_attention_prefill(q, cache, seg_info, tiles, n_tiles, block_table, pag
 PREFILL_TCGEN05 = True     # head width 128 takes the tcgen05 kernel; False keeps the mma.sync one
 
 
+def prefill_tcgen05_block_rows(q_heads: int, kv_heads: int) -> int:
+    """Query rows per entry of the tile list that ``paged_attention_prefill_tcgen05`` wants: 128
+    where two heads of one key/value head share a thread block (an even group), else 256."""
+    return int(lib().tllm_paged_attention_prefill_tc_rows(q_heads, kv_heads))
+
+
 def paged_attention_prefill_tcgen05(q, cache, seg_info, tiles, n_tiles, block_table, page_size, q_heads,
                                     kv_heads, head_dim, window, scale, out):
-    """As ``paged_attention_prefill`` with blocks of 128 query rows, on tcgen05 tensor cores with
-    TMA loads: bfloat16, head width 128.  The kernel's waits are bounded; what they report is
-    read by ``check_error_word``."""
+    """As ``paged_attention_prefill`` on tcgen05 tensor cores with TMA loads: bfloat16, head width
+    128, ``tiles`` at multiples of ``prefill_tcgen05_block_rows`` rows.  The kernel's waits are
+    bounded; what they report is read by ``check_error_word``."""
     _cuda(q, cache, seg_info, tiles, block_table, out)
     assert q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
     assert q.shape[1] == q_heads * head_dim and tuple(out.shape) == tuple(q.shape)
@@ -285,8 +293,9 @@ def paged_attention(q: torch.Tensor, cache: torch.Tensor, positions, token_slot,
                                    page_size, q_heads, kv_heads, head_dim, window, scale, out,
                                    ctx.max_context)
         if ctx.n_tiles:
-            if PREFILL_TCGEN05 and head_dim == 128 and getattr(ctx, "n_tiles128", 0):
-                paged_attention_prefill_tcgen05(q, cache, ctx.seg_info, ctx.pf_tiles, ctx.n_tiles128,
+            if PREFILL_TCGEN05 and head_dim == 128 and getattr(ctx, "n_tiles256", 0):
+                blocks = ctx.n_tiles128 if prefill_tcgen05_block_rows(q_heads, kv_heads) == 128 else ctx.n_tiles256
+                paged_attention_prefill_tcgen05(q, cache, ctx.seg_info, ctx.pf_tiles, blocks,
                                                 block_table, page_size, q_heads, kv_heads, head_dim,
                                                 window, scale, out)
             else:
