@@ -1,5 +1,5 @@
 // Attention of prompt portions over the paged cache on the fifth-generation tensor cores:
-// TMA brings queries, keys and values into shared memory, tcgen05.mma computes S = Q K^T and
+// queries (TMA), keys and values (cp.async) come into shared memory, tcgen05.mma computes S = Q K^T and
 // O += P V with S, P and O in tensor memory, and the softmax runs on what tcgen05.ld reads back.
 // Head width 128, bfloat16, pages of a multiple of 16 tokens.
 //
@@ -12,10 +12,14 @@
 // bandwidth): two query heads of one key/value head at the same 128 positions where the group
 // is even, else two consecutive blocks of 128 positions of one head.  It walks the request's
 // keys in tiles of 64; a tile outside one of the two ranges is skipped for that one.
-//   warp 0    producer: eight lanes each look one group of 16 keys up in the block table and issue
-//             one TMA load (128-byte swizzle) of 16 keys x 64 columns into rings of five key and
-//             five value tiles; the two 128 x 128 query tiles are loaded once.
-//   warp 1    issues the MMAs (one thread).  Per query tile, S[128 x 64] = Q K^T (8 x tcgen05.mma
+//   warps 2-3 copy the key and value tiles with 16-byte cp.async into the layout the MMAs read
+//             (the copy engine takes some 300 cycles per box whatever its size, and pages of 16
+//             keys make for small boxes), into rings of five key and five value tiles; the block
+//             table is looked up for 32 groups of 16 keys at a time.  The two 128 x 128 query
+//             tiles come by TMA, once.
+//   warps 1, 0  issue the MMAs of the first and second query tile (one elected thread each; an
+//             issue costs the thread some 50 cycles, a look at a barrier some 200, and one thread
+//             for both tiles was the bottleneck).  S[128 x 64] = Q K^T (8 x tcgen05.mma
 //             128x64x16, both operands K-major in shared memory) goes into one of two S buffers,
 //             one key tile ahead of the softmax (and only after the P V product that read that
 //             buffer has completed: MMAs into different accumulators are not ordered).  Once the
@@ -44,8 +48,8 @@ constexpr int kHD = 128, kBM = 128, kBN = 64;
 constexpr int kQBytes = kBM * kHD * 2;            // 32 KB: two column halves of [128 rows x 128 B]
 constexpr int kKBytes = kBN * kHD * 2;            // 16 KB: two column halves of [64 keys x 128 B]
 constexpr int kVBytes = kKBytes;
-constexpr int kKStages = 5, kVStages = 5;
-constexpr int kTilesBytes = 2 * kQBytes + kKStages * kKBytes + kVStages * kVBytes;   // 224 KB
+constexpr int kStages = 5;                        // of the key ring and of the value ring
+constexpr int kTilesBytes = 2 * kQBytes + kStages * (kKBytes + kVBytes);   // 224 KB
 constexpr int kSmemBytes = kTilesBytes + 512;     // + barriers and the TMEM slot
 constexpr int kThreads = 384;
 // query tile x: S buffers (and P over them) at columns x * 128 + {0, 64}, O at 256 + x * 128
@@ -120,6 +124,11 @@ __device__ __forceinline__ void umma_ta(uint32_t d_tmem, uint32_t a_tmem, uint64
         "r"(a_tmem), "l"(b_desc), "r"(id), "r"(acc)
         : "memory");
 }
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}\n" : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(sa(bar))
                  : "memory");
@@ -160,8 +169,8 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 }
 
 struct Barriers {
-    uint64_t q_full, k_full[kKStages], k_empty[kKStages], v_full[kVStages], v_empty[kVStages];
-    uint64_t s_full[2][2], p_full[2][2], o_full[2], drain;
+    uint64_t q_full, full[kStages], k_empty[kStages], v_empty[kStages];
+    uint64_t s_full[2][2], p_full[2][2], o_full[2], o_done[2], drain[2];
     uint32_t tmem_slot;
     int abort_flag;
 };
@@ -172,28 +181,17 @@ struct QTile {
     int head, q_off, rows, first_pos, last_pos, kt_first, n;
 };
 
-// The 16 keys from key0 on, for K (kv = 0) or V (kv = 1): the row of the cache seen as
-// [pages * 2 * kv_heads * page_size, 128], or `kv_rows` (outside: reads as zeros) if the
-// request holds no such key.
-__device__ __forceinline__ int cache_row(const int* table, int key0, int last_pos, int page_size, int kv_heads, int g,
-                                         int kv, long long kv_rows) {
-    if (key0 > last_pos) return (int)kv_rows;
-    const int page = table[key0 / page_size];
-    if (page < 0) return (int)kv_rows;
-    return (int)((((long long)page * 2 + kv) * kv_heads + g) * page_size + (key0 % page_size));
-}
-
 __global__ void __launch_bounds__(kThreads, 1)
-paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const bf16* __restrict__ cache,
                                   const int* __restrict__ seg_info, const int* __restrict__ tiles,
                                   const int* __restrict__ block_table, int max_pages, int page_size, int q_heads,
-                                  int kv_heads, long long kv_rows, int window, float scale_log2e, int pair_heads,
+                                  int kv_heads, int window, float scale_log2e, int pair_heads,
                                   bf16* __restrict__ out, int* __restrict__ error_word) {
     extern __shared__ __align__(1024) unsigned char smem[];
     Barriers* bars = reinterpret_cast<Barriers*>(smem + kTilesBytes);
     volatile int* aborted = &bars->abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t q_s = sa(smem), k_s = q_s + 2 * kQBytes, v_s = k_s + kKStages * kKBytes;
+    const uint32_t q_s = sa(smem), k_s = q_s + 2 * kQBytes, v_s = k_s + kStages * kKBytes;
 
     const int seg = tiles[2 * blockIdx.x], q_off0 = tiles[2 * blockIdx.x + 1];
     const int slot = seg_info[4 * seg], start = seg_info[4 * seg + 1];
@@ -221,16 +219,21 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
     if (threadIdx.x == 0) {
         if (q_s & 1023) atomicExch(error_word, 9);         // operand tiles need a 1024-byte aligned window
         mbar_init(&bars->q_full, 1);
-        for (int s = 0; s < kKStages; ++s) { mbar_init(&bars->k_full[s], 1); mbar_init(&bars->k_empty[s], 1); }
-        for (int s = 0; s < kVStages; ++s) { mbar_init(&bars->v_full[s], 1); mbar_init(&bars->v_empty[s], 1); }
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&bars->full[s], 2);                   // two copying warps
+            mbar_init(&bars->k_empty[s], 2);                // two MMA warps
+            mbar_init(&bars->v_empty[s], 2);
+        }
         for (int x = 0; x < 2; ++x) {
             for (int b = 0; b < 2; ++b) {
                 mbar_init(&bars->s_full[x][b], 1);
                 mbar_init(&bars->p_full[x][b], 4);          // one arrival per softmax warp
             }
             mbar_init(&bars->o_full[x], 1);
+            mbar_init(&bars->o_done[x], 1);
         }
-        mbar_init(&bars->drain, 1);
+        mbar_init(&bars->drain[0], 1);
+        mbar_init(&bars->drain[1], 1);
         bars->abort_flag = (q_s & 1023) ? 1 : 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
@@ -245,125 +248,157 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const uint32_t tmem = bars->tmem_slot;
 
-    if (warp == 0) {
-        // -------------------------------------------------------------------- producer (the whole warp)
-        // A tile is 8 boxes (4 groups of 16 keys x 2 column halves): lanes 0-7 each look one
-        // group's page up and issue one box, so that a tile costs one lookup's latency, not eight.
-        const int* table = block_table + (size_t)slot * max_pages;
-        bool stop = __any_sync(0xffffffffu, *aborted != 0);
-        const bool q_issued = !stop;
-        if (!stop && lane == 0) {
+    if (warp < 2) {
+        // -------------------------------------------------------------------- MMA issuers (and the query tiles)
+        // Warp 1 issues for the first query tile, warp 0 for the second: an issue costs the thread
+        // some 50 cycles and a wait on a barrier some 200, so one thread for both tiles was the
+        // kernel's bottleneck.  The whole warp runs the loop, so that addresses and descriptors
+        // are warp-uniform values; one elected lane issues the MMAs and commits (a commit covers
+        // that thread's MMAs).
+        const int x = warp == 1 ? 0 : 1;
+        const QTile t = x ? qt[1] : qt[0];
+        if (warp == 0 && lane == 0 && !*aborted) {           // query tiles, by TMA, once
             mbar_expect_tx(&bars->q_full, two ? 2 * kQBytes : kQBytes);
 #pragma unroll
-            for (int x = 0; x < 2; ++x) {
-                if (qt[x].n == 0) continue;
-                tma_load_2d(q_s + x * kQBytes, &map_q, qt[x].head * kHD, start + qt[x].q_off, &bars->q_full);
-                tma_load_2d(q_s + x * kQBytes + kQBytes / 2, &map_q, qt[x].head * kHD + 64, start + qt[x].q_off,
+            for (int y = 0; y < 2; ++y) {
+                if (qt[y].n == 0) continue;
+                tma_load_2d(q_s + y * kQBytes, &map_q, qt[y].head * kHD, start + qt[y].q_off, &bars->q_full);
+                tma_load_2d(q_s + y * kQBytes + kQBytes / 2, &map_q, qt[y].head * kHD + 64, start + qt[y].q_off,
                             &bars->q_full);
             }
         }
-        const int grp = lane >> 1, half = lane & 1;
-        int k_issued = 0, v_issued = 0;
-        // keys run one tile ahead of values, as the MMAs use them: K0, then K(j+1), V(j)
-        for (int step = 0; step <= n_tiles && !stop; ++step) {
-            const int jk = step, jv = step - 1;
-            if (jk < n_tiles) {
-                const int s = jk % kKStages;
-                bool ok = true;
-                if (jk >= kKStages && lane == 0) ok = mbar_wait(&bars->k_empty[s], ((jk / kKStages) - 1) & 1);
-                if (!ok) { atomicExch(error_word, 1); *aborted = 1; }
-                if (__any_sync(0xffffffffu, !ok || *aborted != 0)) { stop = true; break; }
-                if (lane == 0) mbar_expect_tx(&bars->k_full[s], kKBytes);
-                __syncwarp();
-                if (lane < 8) {
-                    const int row = cache_row(table, (kt_lo + jk) * kBN + grp * 16, last_pos, page_size, kv_heads, g, 0,
-                                              kv_rows);
-                    tma_load_2d(k_s + s * kKBytes + half * (kKBytes / 2) + grp * 2048, &map_kv, half * 64, row,
-                                &bars->k_full[s]);
-                }
-                k_issued = jk + 1;
-            }
-            if (jv >= 0) {
-                const int s = jv % kVStages;
-                bool ok = true;
-                if (jv >= kVStages && lane == 0) ok = mbar_wait(&bars->v_empty[s], ((jv / kVStages) - 1) & 1);
-                if (!ok) { atomicExch(error_word, 2); *aborted = 1; }
-                if (__any_sync(0xffffffffu, !ok || *aborted != 0)) { stop = true; break; }
-                if (lane == 0) mbar_expect_tx(&bars->v_full[s], kVBytes);
-                __syncwarp();
-                if (lane < 8) {
-                    const int row = cache_row(table, (kt_lo + jv) * kBN + grp * 16, last_pos, page_size, kv_heads, g, 1,
-                                              kv_rows);
-                    tma_load_2d(v_s + s * kVBytes + half * (kVBytes / 2) + grp * 2048, &map_kv, half * 64, row,
-                                &bars->v_full[s]);
-                }
-                v_issued = jv + 1;
-            }
-        }
         __syncwarp();
-        if (stop && lane == 0) {      // do not leave while copies into this block's shared memory are in flight
-            if (q_issued) mbar_wait(&bars->q_full, 0);
-            for (int j = max(0, k_issued - kKStages); j < k_issued; ++j)
-                mbar_wait(&bars->k_full[j % kKStages], (j / kKStages) & 1);
-            for (int j = max(0, v_issued - kVStages); j < v_issued; ++j)
-                mbar_wait(&bars->v_full[j % kVStages], (j / kVStages) & 1);
-        }
-    } else if (warp == 1 && lane == 0) {
-        // -------------------------------------------------------------------- MMA issuer
+        const bool leader = elect_one();
         constexpr uint32_t id_s = idesc(kBM, kBN, 0), id_o = idesc(kBM, kHD, 1);
-        // S of both query tiles for the block's key tile j; 0 or the error code of the wait that gave up
+        const uint32_t q_addr = q_s + x * kQBytes, tmem_s = tmem + x * 128, tmem_o = tmem + 256 + x * 128;
+        auto wait_all = [&](uint64_t* bar, uint32_t parity) -> bool {
+            return __all_sync(0xffffffffu, mbar_wait(bar, parity));
+        };
+        // S of this query tile for the block's key tile j (copied in step j); 0 or an error code
         auto issue_s = [&](int j) -> int {
-            const int s = j % kKStages;
-            if (!mbar_wait(&bars->k_full[s], (j / kKStages) & 1)) return 4;
-            const uint32_t k_addr = k_s + s * kKBytes;
-#pragma unroll
-            for (int x = 0; x < 2; ++x) {
-                const int jx = kt_lo + j - qt[x].kt_first;
-                if (jx < 0 || jx >= qt[x].n) continue;
+            const int jx = kt_lo + j - t.kt_first, s = j % kStages;
+            if (jx >= 0 && jx < t.n) {
                 // S(jx) goes where PV(jx-2) read its P: that one has to have completed
-                if (jx >= 2 && !mbar_wait(&bars->o_full[x], (jx - 2) & 1)) return 5;
+                if (jx >= 2 && !wait_all(&bars->o_full[x], (jx - 2) & 1)) return 5;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const uint32_t d = tmem + x * 128 + (jx & 1) * kBN, q_addr = q_s + x * kQBytes;
+                const uint32_t d = tmem_s + (jx & 1) * kBN, k_addr = k_s + s * kKBytes;
 #pragma unroll
                 for (int k = 0; k < kHD / 16; ++k) {        // S = Q K^T over the head width
                     const uint32_t half = k >> 2, kk = k & 3;
-                    umma(d, desc_k_major(q_addr + half * (kQBytes / 2) + kk * 32),
-                         desc_k_major(k_addr + half * (kKBytes / 2) + kk * 32), id_s, k > 0 ? 1u : 0u);
+                    const uint64_t da = desc_k_major(q_addr + half * (kQBytes / 2) + kk * 32);
+                    const uint64_t db = desc_k_major(k_addr + half * (kKBytes / 2) + kk * 32);
+                    if (leader) umma(d, da, db, id_s, k > 0 ? 1u : 0u);
                 }
-                umma_commit(&bars->s_full[x][jx & 1]);
+                if (leader) umma_commit(&bars->s_full[x][jx & 1]);
             }
-            umma_commit(&bars->k_empty[s]);
+            if (leader) umma_commit(&bars->k_empty[s]);
             return 0;
         };
-        int err = mbar_wait(&bars->q_full, 0) ? 0 : 3;
-        if (!err && !*aborted) err = issue_s(0);
-        for (int j = 0; j < n_tiles && !err && !*aborted; ++j) {
+        // the query tiles have to be there before anything is issued (and before warp 0 may leave)
+        int err = wait_all(&bars->q_full, 0) ? 0 : 3;
+        if (!err && !wait_all(&bars->full[0], 0)) err = 4;
+        if (!err && !__any_sync(0xffffffffu, *aborted != 0)) err = issue_s(0);
+        for (int j = 0; j < n_tiles && !err; ++j) {
+            if (__any_sync(0xffffffffu, *aborted != 0)) break;
+            // step j+1 brought K(j+1) and V(j)
+            if (!wait_all(&bars->full[(j + 1) % kStages], ((j + 1) / kStages) & 1)) { err = 4; break; }
             if (j + 1 < n_tiles && (err = issue_s(j + 1)) != 0) break;
-            const int s = j % kVStages;
-            if (!mbar_wait(&bars->v_full[s], (j / kVStages) & 1)) { err = 6; break; }
-            const uint32_t v_addr = v_s + s * kVBytes;
-#pragma unroll
-            for (int x = 0; x < 2; ++x) {
-                const int jx = kt_lo + j - qt[x].kt_first;
-                if (jx < 0 || jx >= qt[x].n) continue;
-                if (!mbar_wait(&bars->p_full[x][jx & 1], (jx >> 1) & 1)) { err = 7; break; }
+            const int jx = kt_lo + j - t.kt_first, s = j % kStages;
+            if (jx >= 0 && jx < t.n) {
+                if (!wait_all(&bars->p_full[x][jx & 1], (jx >> 1) & 1)) { err = 7; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const uint32_t p = tmem + x * 128 + (jx & 1) * kBN, d = tmem + 256 + x * 128;
+                const uint32_t p = tmem_s + (jx & 1) * kBN, v_addr = v_s + s * kVBytes;
 #pragma unroll
                 for (int k = 0; k < kBN / 16; ++k) {        // O += P V over the tile's keys
-                    umma_ta(d, p + k * 8, desc_mn_major(v_addr + k * 2048, kVBytes / 2), id_o,
-                            (jx > 0 || k > 0) ? 1u : 0u);
+                    const uint64_t db = desc_mn_major(v_addr + k * 2048, kVBytes / 2);
+                    if (leader) umma_ta(tmem_o, p + k * 8, db, id_o, (jx > 0 || k > 0) ? 1u : 0u);
                 }
-                umma_commit(&bars->o_full[x]);
+                if (leader) {
+                    umma_commit(&bars->o_full[x]);
+                    if (jx == t.n - 1) umma_commit(&bars->o_done[x]);
+                }
             }
-            if (err) break;
-            umma_commit(&bars->v_empty[s]);
+            if (leader) umma_commit(&bars->v_empty[s]);
         }
-        if (err) { atomicExch(error_word, err); *aborted = 1; }
-        if (*aborted) {      // tensor memory is freed below: let the MMAs in flight end first
-            umma_commit(&bars->drain);
-            mbar_wait(&bars->drain, 0);
+        if (err && leader) { atomicExch(error_word, err); *aborted = 1; }
+        __syncwarp();
+        if (__any_sync(0xffffffffu, *aborted != 0) && leader) {   // tensor memory is freed below: let the MMAs end first
+            umma_commit(&bars->drain[x]);
+            mbar_wait(&bars->drain[x], 0);
         }
+        __syncwarp();
+    } else if (warp == 2 || warp == 3) {
+        // -------------------------------------------------------------------- key and value tiles (cp.async)
+        // Pages are 16 keys or more apart in memory, and the copy engine takes some 300 cycles per
+        // box whatever its size, so the tiles are gathered with 16-byte asynchronous copies into
+        // the layout the MMAs read (rows of 128 bytes per column half, 16-byte chunks swizzled by
+        // the row).  Warp w - 2 copies keys 32 (w - 2) .. +31 of every tile: an instruction moves
+        // two whole rows of 256 bytes, 16 lanes each.  The cache rows of the warp's next 32 groups
+        // of 16 keys (16 tiles) are looked up at once, one group per lane, and handed out by
+        // shuffle; the 32 after them are fetched while these are in use.
+        const int w = warp - 2;
+        const int* table = block_table + (size_t)slot * max_pages;
+        const char* cache_b = reinterpret_cast<const char*>(cache);
+        const int v_off = kv_heads * page_size;              // from a key's row to its value's
+        auto lookup = [&](int chunk) -> int {                // row of K of this lane's group, -1: none
+            const int idx = chunk * 32 + lane;
+            const int key0 = ((kt_lo + (idx >> 1)) * 4 + w * 2 + (idx & 1)) * 16;
+            if (key0 > last_pos) return -1;
+            const int page = table[key0 / page_size];
+            return page < 0 ? -1 : (int)(((long long)page * 2 * kv_heads + g) * page_size + key0 % page_size);
+        };
+        int rows0 = lookup(0), rows1 = -1;                   // chunks of even and odd number
+        auto copy_tile = [&](int j, int value, uint32_t dst) {
+            const int held = ((j >> 4) & 1) ? rows1 : rows0;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int base = __shfl_sync(0xffffffffu, held, (j & 15) * 2 + h);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int in_grp = 2 * i + (lane >> 4), key = w * 32 + h * 16 + in_grp, c = lane & 15;
+                    const long long row = (long long)base + in_grp + (value ? v_off : 0);
+                    const char* src = base < 0 ? cache_b : cache_b + row * (kHD * 2) + c * 16;
+                    const uint32_t d = dst + (c >> 3) * (kKBytes / 2) + key * 128 + (((c & 7) ^ (key & 7)) << 4);
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src),
+                                 "r"(base < 0 ? 0 : 16)
+                                 : "memory");                // zero-filled where the request holds no key
+                }
+            }
+        };
+        // Step s copies K(s) and V(s-1) as one group and publishes them on full[s % kStages];
+        // kInFlight groups are under way per thread.
+        constexpr int kInFlight = 3;
+        auto publish = [&](int st) {      // the step's copies of this warp have landed: tell the MMA thread
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->full[st % kStages]);
+        };
+        bool stop = __any_sync(0xffffffffu, *aborted != 0);
+        int committed = 0, published = 0;
+        for (int st = 0; st <= n_tiles && !stop; ++st) {
+            const int jk = st, jv = st - 1;
+            bool ok = true;
+            if (jk < n_tiles) {
+                if ((jk & 15) == 1) {                        // values have left the chunk before: fetch the next
+                    const int next = lookup((jk >> 4) + 1);
+                    if ((jk >> 4) & 1) rows0 = next; else rows1 = next;
+                }
+                if (jk >= kStages && lane == 0) ok = mbar_wait(&bars->k_empty[jk % kStages], ((jk / kStages) - 1) & 1);
+            }
+            if (ok && jv >= kStages && lane == 0) ok = mbar_wait(&bars->v_empty[jv % kStages], ((jv / kStages) - 1) & 1);
+            if (!ok) { atomicExch(error_word, 1); *aborted = 1; }
+            if (__any_sync(0xffffffffu, !ok || *aborted != 0)) { stop = true; break; }
+            if (jk < n_tiles) copy_tile(jk, 0, k_s + (jk % kStages) * kKBytes);
+            if (jv >= 0) copy_tile(jv, 1, v_s + (jv % kStages) * kVBytes);
+            asm volatile("cp.async.commit_group;\n" ::: "memory");
+            ++committed;
+            if (committed - published >= kInFlight) {
+                asm volatile("cp.async.wait_group %0;\n" ::"n"(kInFlight - 1) : "memory");
+                publish(published++);
+            }
+        }
+        asm volatile("cp.async.wait_group 0;\n" ::: "memory");   // nothing in flight when this warp leaves
+        while (!stop && published < committed) publish(published++);
     } else if (warp >= 4) {
         // -------------------------------------------------------------------- softmax, one row per thread
         const int x = (warp - 4) >> 2, quad = warp & 3, r = quad * 32 + lane;
@@ -408,18 +443,15 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
                 m_ref = tile_max;
                 l_run *= factor;
             }
-            // Every warp follows every phase of o_full (a parity wait can only tell the current phase
-            // from the one before it): PV(j-1) has completed.  Early if O must be scaled, else late.
-            auto wait_prev = [&]() -> bool {
+            if (j > 0 && __any_sync(0xffffffffu, raise)) {
+                // O holds the tiles before this one: wait for PV(j-1), then scale it down.  (S(j) was
+                // issued after PV(j-2) completed and PV(j) waits for this warp, so o_full is in
+                // phase j-1 or j: the parity tells them apart.)
                 if (!mbar_wait(o_full, (j - 1) & 1)) {
                     atomicExch(error_word, 11);
                     *aborted = 1;
                 }
-                return !__any_sync(0xffffffffu, *aborted != 0);
-            };
-            const bool scale_o = j > 0 && __any_sync(0xffffffffu, raise);
-            if (scale_o) {
-                if (!wait_prev()) { alive = false; break; }
+                if (__any_sync(0xffffffffu, *aborted != 0)) { alive = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 #pragma unroll 1
                 for (int c = 0; c < kHD; c += 32) {
@@ -443,7 +475,6 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
                 pw[i >> 1] = pack2(a, b);
             }
             l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
-            if (j > 0 && !scale_o && !wait_prev()) { alive = false; break; }
             tmem_st32(t_s, pw);                              // P over the S it came from
             tmem_st_wait();
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -451,7 +482,7 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
             if (lane == 0) mbar_arrive(&bars->p_full[x][j & 1]);
         }
         if (alive) {
-            if (!mbar_wait(o_full, (t.n - 1) & 1)) {
+            if (!mbar_wait(&bars->o_done[x], 0)) {
                 atomicExch(error_word, 12);
                 *aborted = 1;
             }
@@ -558,11 +589,14 @@ extern "C" int tllm_paged_attention_prefill_tc(
                  page_size);
     TLLM_REQUIRE(error_word != nullptr && n_tiles >= 0 && tokens > 0, "paged_attention_prefill_tc: bad arguments");
     const long long kv_rows = (long long)num_pages * 2 * kv_heads * page_size;
-    TLLM_REQUIRE(kv_rows < (1ll << 31), "paged_attention_prefill_tc: cache of %lld rows exceeds the copy engine's coordinates",
+    TLLM_REQUIRE(kv_rows < (1ll << 31), "paged_attention_prefill_tc: a cache of %lld rows exceeds the kernel's 32-bit row index",
                  kv_rows);
     if (n_tiles == 0) return 0;
-    CUtensorMap mq, mkv;
-    TLLM_REQUIRE(pftc::make_map(&mq, q, tokens, (long long)q_heads * 128, 128) && pftc::make_map(&mkv, cache, kv_rows, 128, 16),
+    TLLM_REQUIRE((reinterpret_cast<uintptr_t>(cache) & 15u) == 0 && (reinterpret_cast<uintptr_t>(q) & 15u) == 0 &&
+                     (reinterpret_cast<uintptr_t>(out) & 15u) == 0,
+                 "paged_attention_prefill_tc: pointers must be 16-byte aligned");
+    CUtensorMap mq;
+    TLLM_REQUIRE(pftc::make_map(&mq, q, tokens, (long long)q_heads * 128, 128),
                  "paged_attention_prefill_tc: cuTensorMapEncodeTiled failed or is not available");
     static bool configured = false;
     if (!configured) {
@@ -574,7 +608,7 @@ extern "C" int tllm_paged_attention_prefill_tc(
     const int pair_heads = tllm_paged_attention_prefill_tc_rows(q_heads, kv_heads) == 128;
     pftc::paged_attention_prefill_tc_kernel<<<dim3(n_tiles, pair_heads ? q_heads / 2 : q_heads), pftc::kThreads,
                                               pftc::kSmemBytes, stream>>>(
-        mq, mkv, seg_info, tiles, block_table, max_pages, page_size, q_heads, kv_heads, kv_rows, window,
+        mq, (const bf16*)cache, seg_info, tiles, block_table, max_pages, page_size, q_heads, kv_heads, window,
         scale * 1.4426950408889634f, pair_heads, (bf16*)out, error_word);
     return finish_launch("paged_attention_prefill_tc");
 }
