@@ -193,14 +193,15 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t q_s = sa(smem), k_s = q_s + 2 * kQBytes, v_s = k_s + kStages * kKBytes;
 
-    const int seg = tiles[2 * blockIdx.x], q_off0 = tiles[2 * blockIdx.x + 1];
+    // blocks start in the order of the tile list (the caller puts the longest first), heads fastest
+    const int seg = tiles[2 * blockIdx.y], q_off0 = tiles[2 * blockIdx.y + 1];
     const int slot = seg_info[4 * seg], start = seg_info[4 * seg + 1];
     const int len = seg_info[4 * seg + 2], pos0 = seg_info[4 * seg + 3];
     QTile qt[2];
 #pragma unroll
     for (int x = 0; x < 2; ++x) {
         QTile& t = qt[x];
-        t.head = pair_heads ? 2 * blockIdx.y + x : blockIdx.y;
+        t.head = pair_heads ? 2 * blockIdx.x + x : blockIdx.x;
         t.q_off = pair_heads ? q_off0 : q_off0 + x * kBM;
         t.rows = min(kBM, len - t.q_off);
         t.first_pos = pos0 + t.q_off;
@@ -587,7 +588,8 @@ extern "C" int tllm_paged_attention_prefill_tc(
                  "paged_attention_prefill_tc: %d query heads over %d key/value heads", q_heads, kv_heads);
     TLLM_REQUIRE(page_size > 0 && page_size % 16 == 0, "paged_attention_prefill_tc: page size %d is no multiple of 16",
                  page_size);
-    TLLM_REQUIRE(error_word != nullptr && n_tiles >= 0 && tokens > 0, "paged_attention_prefill_tc: bad arguments");
+    TLLM_REQUIRE(error_word != nullptr && n_tiles >= 0 && n_tiles <= 65535 && tokens > 0,
+                 "paged_attention_prefill_tc: bad arguments (at most 65535 blocks of query rows)");
     const long long kv_rows = (long long)num_pages * 2 * kv_heads * page_size;
     TLLM_REQUIRE(kv_rows < (1ll << 31), "paged_attention_prefill_tc: a cache of %lld rows exceeds the kernel's 32-bit row index",
                  kv_rows);
@@ -606,7 +608,7 @@ extern "C" int tllm_paged_attention_prefill_tc(
         configured = true;
     }
     const int pair_heads = tllm_paged_attention_prefill_tc_rows(q_heads, kv_heads) == 128;
-    pftc::paged_attention_prefill_tc_kernel<<<dim3(n_tiles, pair_heads ? q_heads / 2 : q_heads), pftc::kThreads,
+    pftc::paged_attention_prefill_tc_kernel<<<dim3(pair_heads ? q_heads / 2 : q_heads, n_tiles), pftc::kThreads,
                                               pftc::kSmemBytes, stream>>>(
         mq, (const bf16*)cache, seg_info, tiles, block_table, max_pages, page_size, q_heads, kv_heads, window,
         scale * 1.4426950408889634f, pair_heads, (bf16*)out, error_word);
