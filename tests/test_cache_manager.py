@@ -134,3 +134,129 @@ def test_state_slots_are_zeroed_at_admission():
     m.release("a")
     assert m.admit("b") == slot and float(m.view(0).state[slot].abs().sum()) == 0.0
     assert m.view(0).kv is None and m.view(1).state is None
+
+
+# ---------------------------------------------------------------------------- prefix cache
+def prefix_manager(pages=12, slots=4, page=4):
+    return CacheManager(FULL, page_size=page, num_pages=pages, max_slots=slots, max_seq_len=64, prefix_cache=True)
+
+
+def run_request(m, rid, tokens):
+    """Admit with the tokens, compute what is not shared in one step; returns what was shared."""
+    m.admit(rid, tokens)
+    shared = m.computed(rid)
+    m.reserve(rid, len(tokens))
+    m.commit(rid, len(tokens), tokens[shared:])
+    m.audit()
+    return shared
+
+
+def test_prefix_pages_are_shared_counted_and_freed_by_the_last_user():
+    m = prefix_manager()
+    a = list(range(100, 111))                       # 11 tokens: two full pages and a part
+    assert run_request(m, "a", a) == 0              # nothing to share yet
+    b = a[:9] + [7, 7, 7]
+    assert run_request(m, "b", b) == 8              # both full pages of the common beginning
+    pa, pb = m.pages_of("a")[None], m.pages_of("b")[None]
+    assert pa[:2] == pb[:2] and pa[2] != pb[2]
+    assert m.free_pages() == {None: 12 - 4}
+    c = a[:8]                                       # ends on a page edge: its last page is computed
+    assert run_request(m, "c", c) == 4
+    assert m.pages_of("c")[None][0] == pa[0] and m.pages_of("c")[None][1] not in pa + pb
+    m.release("a")
+    assert m.free_pages() == {None: 12 - 5 + 1}     # only a's own third page came back
+    m.release("b")
+    m.release("c")
+    m.audit()
+    assert m.free_pages() == {None: 12}
+    # freed pages keep their hash until they are handed out again: the prompt comes back for free
+    assert run_request(m, "d", a) == 8
+    assert m.pages_of("d")[None][:2] == pa[:2]
+    assert m.prefix_hit_pages == 2 + 1 + 2
+
+
+def test_prefix_differs_in_the_first_page_or_in_tokens_behind_an_equal_page():
+    m = prefix_manager(pages=16)
+    a = list(range(20))
+    run_request(m, "a", a)
+    assert run_request(m, "b", [99] + a[1:]) == 0           # a later page alone never matches: the chain differs
+    assert run_request(m, "c", a[:4] + [98] + a[5:]) == 4
+    m.audit()
+
+
+def test_prefix_hash_is_dropped_when_the_page_is_handed_out_again():
+    """Freed pages that the prefix cache still knows are handed out last, the one freed
+    longest ago first; a page that is handed out again no longer stands for its old tokens."""
+    m = prefix_manager(pages=4)
+    a = list(range(13))                                     # pages 0-2 full (hashed), page 3 part
+    run_request(m, "a", a)
+    m.release("a")                                          # freed in the order 3, 2, 1, 0
+    other = list(range(50, 59))
+    assert run_request(m, "x", other) == 0
+    assert m.pages_of("x")[None] == [3, 2, 1]               # the unhashed page first, then the oldest
+    m.release("x")
+    assert run_request(m, "b", a) == 4                      # page 0 still holds a's beginning
+    assert m.pages_of("b")[None][0] == 0
+    m.release("b")
+    assert run_request(m, "c", list(range(70, 83))) == 0    # takes all four pages
+    m.release("c")
+    assert run_request(m, "d", a) == 0 and m.computed("d") == 13
+    m.audit()
+
+
+def test_prefix_needs_tokens_and_full_caches_without_state():
+    m = prefix_manager()
+    m.admit("a")                                            # no tokens told: never hashed, never shares
+    m.reserve("a", 9)
+    m.commit("a", 9)
+    assert run_request(m, "b", list(range(9))) == 0
+    m.admit("c", list(range(30, 39)))
+    m.reserve("c", 9)
+    m.commit("c", 5)                                        # tokens not told for this step: hashing stops
+    m.commit("c", 9, list(range(35, 39)))
+    assert run_request(m, "d", list(range(30, 39))) == 0
+    assert not CacheManager(MIXED, 4, 8, 2, 64, prefix_cache=True).prefix_active
+    with_state = {0: (CacheSpec(2, 16, None), StateSpec((3,), "float32"))}
+    assert not CacheManager(with_state, 4, 8, 2, 64, prefix_cache=True).prefix_active
+
+
+@pytest.mark.parametrize("seed", range(5))
+def test_random_orders_with_shared_prefixes_keep_every_invariant(seed):
+    rng = random.Random(100 + seed)
+    m = CacheManager(FULL, page_size=4, num_pages=30, max_slots=5, max_seq_len=64, prefix_cache=True)
+    stems = [[rng.randrange(50) for _ in range(40)] for _ in range(3)]
+    live, next_id, shared_total = {}, 0, 0
+    for _ in range(600):
+        action = rng.random()
+        if action < 0.3 and m.free_slots:
+            stem = rng.choice(stems)
+            cut = rng.randrange(1, 40)
+            tokens = stem[:cut] + [rng.randrange(50, 60) for _ in range(rng.randrange(0, 9))]
+            m.admit(next_id, tokens)
+            done = m.computed(next_id)
+            assert done % 4 == 0 and done < len(tokens)
+            # what is shared holds the request's own tokens
+            for i, page in enumerate(m.pages_of(next_id)[None]):
+                assert m.groups[None].tokens_of[page] == tuple(tokens[4 * i:4 * i + 4])
+            shared_total += done
+            live[next_id] = (tokens, done)
+            next_id += 1
+        elif action < 0.8 and live:
+            rid = rng.choice(list(live))
+            tokens, done = live[rid]
+            if done == len(tokens):
+                tokens = tokens + [rng.randrange(60)]           # decoding
+            new_len = min(len(tokens), done + rng.choice([1, 2, 5, 16]))
+            if m.can_reserve(rid, new_len):
+                m.reserve(rid, new_len)
+                m.commit(rid, new_len, tokens[done:new_len])
+                live[rid] = (tokens, new_len)
+        elif live:
+            rid = rng.choice(list(live))
+            m.release(rid)
+            del live[rid]
+        m.audit()
+    for rid in list(live):
+        m.release(rid)
+    m.audit()
+    assert m.free_pages() == {None: 30} and m.free_slots == 5 and shared_total > 0

@@ -41,3 +41,26 @@ def test_preemption_and_sampling_keys(tmp_path, cpu_ops):
 def test_toy_parts_on_the_host_side(tmp_path, cpu_ops):
     from test_engine_gpu import run_toy
     run_toy(tmp_path, "cpu")
+
+
+def test_prefix_cache_changes_no_token(tmp_path, cpu_ops):
+    """Prompts that begin alike share full pages (the second call finds the pages of the first,
+    freed but not yet handed out again); what is generated is what the plain implementation
+    generates, with the cache on and off."""
+    from tiny_llm_infer_b200 import LLM, SamplingParams
+    folder = make_folder(TINIES["A"], tmp_path / "m")
+    cfg, w = plain.read_model(folder)
+    stem = prompt(1, 40, 256)
+    prompts = [stem, stem[:37] + prompt(2, 6, 256), stem[:32], stem + prompt(3, 3, 256)]
+    want = [plain.greedy(cfg, w, p, 6) for p in prompts]
+    for on in (True, False):
+        llm = LLM(str(folder), dtype="float32", max_model_len=128, num_kv_blocks=24, block_size=16,
+                  max_num_batched_tokens=64, max_num_seqs=4, device="cpu", enable_prefix_caching=on)
+        sp = SamplingParams(max_tokens=6, ignore_eos=True)
+        first = llm.generate(prompts[:1], sp)
+        rest = llm.generate(prompts[1:], sp)
+        assert [o.token_ids for o in first + rest] == want
+        llm.cache.audit()
+        assert llm.cache.free_pages() == {None: 24}
+        # stem[:37] shares 2 pages, stem[:32] one (its last page is computed), stem + 3 two
+        assert llm.engine.counters.prefix_cached_tokens == (16 * (2 + 1 + 2) if on else 0)

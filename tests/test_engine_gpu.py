@@ -99,6 +99,33 @@ def test_long_prompts_head_width_128(folders, budget):
         assert ok, info
 
 
+def test_prefix_cache_on_the_gpu(folders):
+    """Shared beginnings: the pages of an earlier prompt are read instead of computed again, by
+    live requests and after the earlier one has ended; float32 tokens equal the plain
+    implementation's, bfloat16 ones are within its margin.  A model with a windowed layer (E)
+    shares nothing and is none the worse for the option."""
+    from tiny_llm_infer_b200 import LLM, SamplingParams
+    for name, dtype, margin in (("B", "float32", None), ("B", "bfloat16", 0.08), ("E", "bfloat16", 0.08)):
+        tiny = TINIES[name]
+        cfg, w = plain.read_model(folders[name])
+        ps = tiny["page_size"]
+        stem = prompt(31, 5 * ps + 3, cfg["vocab_size"])
+        prompts = [stem, stem[:4 * ps + 1] + prompt(32, 9, cfg["vocab_size"]), stem[:2 * ps],
+                   stem + prompt(33, 2 * ps, cfg["vocab_size"])]
+        llm = LLM(str(folders[name]), dtype=dtype, max_model_len=400, num_kv_blocks=40, block_size=ps,
+                  max_num_batched_tokens=512, max_num_seqs=4)
+        sp = SamplingParams(max_tokens=10, ignore_eos=True)
+        outs = llm.generate(prompts[:1], sp) + llm.generate(prompts[1:], sp)
+        assert llm.engine.counters.prefix_cached_tokens == (ps * (4 + 1 + 5) if name == "B" else 0)
+        for p, o in zip(prompts, outs):
+            if margin is None:
+                assert o.token_ids == plain.greedy(cfg, w, p, 10)
+            else:
+                ok, info = teacher_forced_ok(cfg, w, p, o.token_ids, margin)
+                assert ok, info
+        llm.cache.audit()
+
+
 def test_eos_stops_and_is_ignored_on_request(folders, tmp_path):
     from tiny_llm_infer_b200 import LLM, SamplingParams
     cfg, w = plain.read_model(folders["A"])

@@ -131,3 +131,33 @@ def test_empty_request_and_wrong_sample_count():
     plan = sched.schedule()
     with pytest.raises(SchedulerError, match="wrong number"):
         sched.postprocess(plan, [], lambda t: False)
+
+
+def test_prefix_cache_starts_a_prompt_behind_what_is_shared():
+    """A prompt that begins like an earlier one is admitted with its full shared pages counted
+    as computed (engine/src/block_manager.cpp:97-125); at least one token is always computed."""
+    cache = CacheManager(NEEDS, 8, 16, 4, 256, prefix_cache=True)
+    sched = Scheduler(SchedulerConfig(4, 64, 8, 16), cache)
+
+    def step():
+        plan = sched.schedule()
+        for item in plan.sequences:
+            s = item.sequence
+            assert cache.computed(s.id) == item.token_start
+            cache.reserve(s.id, item.token_start + item.token_count)
+            cache.commit(s.id, item.token_start + item.token_count,
+                         s.tokens[item.token_start:item.token_start + item.token_count])
+        done = sched.postprocess(plan, [7 if i.samples else -1 for i in plan.sequences], lambda t: False)
+        cache.audit()
+        return plan, done
+
+    sched.add(seq(1, 20, max_tokens=1))
+    plan, done = step()
+    assert shape(plan) == [(1, 0, 20, True)] and [d.id for d in done] == [1]
+    sched.add(seq(2, 20, max_tokens=2))                  # same 20 tokens: two full pages are there
+    sched.add(seq(3, 16, max_tokens=1))                  # ends on a page edge: its last page is computed
+    plan, _ = step()
+    assert shape(plan) == [(2, 16, 4, True), (3, 8, 8, True)]
+    plan, done = step()
+    assert shape(plan) == [(2, 20, 1, False)] and [d.id for d in done] == [2]
+    assert cache.free_pages() == {None: 16} and cache.prefix_hit_pages == 3

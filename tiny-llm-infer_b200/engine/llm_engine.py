@@ -46,6 +46,7 @@ class EngineCounters:
     decode_tokens: int = 0
     generated_tokens: int = 0
     preemptions: int = 0
+    prefix_cached_tokens: int = 0      # prompt tokens found in the cache instead of computed
 
 
 class LLMEngine:
@@ -122,6 +123,8 @@ class LLMEngine:
         c.steps += 1
         c.generated_tokens += len(tokens)
         c.preemptions = self.scheduler.num_preemptions
+        cache = self.runner.cache
+        c.prefix_cached_tokens = cache.prefix_hit_pages * cache.page_size
         for item in plan.sequences:
             if item.is_prefill:
                 c.prefill_tokens += item.token_count
@@ -186,13 +189,16 @@ class LLM:
     (model/model_main.cpp:403-428, 470-475): ``max_model_len`` (``--max-seq-len``),
     ``num_kv_blocks`` (0: sized from free memory and ``gpu_memory_utilization``),
     ``block_size`` 16, ``max_num_batched_tokens`` min(max_model_len, 256),
-    ``max_num_seqs`` 16.
+    ``max_num_seqs`` 16.  ``enable_prefix_caching`` (on, as in the reference, whose block
+    manager always shares hashed pages): prompts that begin like an earlier one reuse its
+    full pages; it stays off by itself for models with windows or per-request state.
     """
 
     def __init__(self, model: str, dtype: str = "bfloat16", max_model_len: int = 2048,
                  num_kv_blocks: int = 0, block_size: int = 16, max_num_batched_tokens: Optional[int] = None,
                  max_num_seqs: int = 16, gpu_memory_utilization: float = 0.9, device: str = "cuda:0",
-                 tokenizer: Optional[str] = None, loaded=None, use_cuda_graphs: bool = True):
+                 tokenizer: Optional[str] = None, loaded=None, use_cuda_graphs: bool = True,
+                 enable_prefix_caching: bool = True):
         if device.startswith("cuda") and not torch.cuda.is_available():
             raise RuntimeError("no CUDA device; this engine has no CPU path")
         torch_dtype = DTYPES[dtype] if isinstance(dtype, str) else dtype
@@ -209,7 +215,7 @@ class LLM:
             if num_kv_blocks <= 0:
                 raise RuntimeError("no memory left for the key/value cache")
         self.cache = CacheManager(self.model.cache_needs(), block_size, num_kv_blocks, max_num_seqs,
-                                  max_model_len, torch_dtype, device)
+                                  max_model_len, torch_dtype, device, prefix_cache=enable_prefix_caching)
         self.runner = ModelRunner(self.model, self.cache, max_num_batched_tokens, use_graphs=use_cuda_graphs)
         self.tokenizer = None
         if tokenizer:

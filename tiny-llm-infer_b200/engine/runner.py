@@ -106,9 +106,9 @@ class ModelRunner:
             self.cache.release(request)
 
     # ------------------------------------------------------------------ the step
-    def build_context(self, entries: Sequence[StepEntry]) -> Tuple[StepContext, List[Tuple[Hashable, int]]]:
+    def build_context(self, entries: Sequence[StepEntry]) -> Tuple[StepContext, List[Tuple[Hashable, int, Sequence[int]]]]:
         """Reserve pages, lay the rows out, upload them.  Returns the context and, per
-        entry, (request, length after this step) to commit once the step has run."""
+        entry, (request, length after this step, its tokens) to commit once the step has run."""
         if not entries:
             raise StepError("a step needs at least one entry")
         seen = set()
@@ -132,7 +132,7 @@ class ModelRunner:
         if self._uploaded is not None:
             self._uploaded.synchronize()
         segments: List[Segment] = []
-        commits: List[Tuple[Hashable, int]] = []
+        commits: List[Tuple[Hashable, int, Sequence[int]]] = []
         row = n_want = max_ctx = max_seg = 0
         for e in entries:
             if not self.cache.has(e.request):
@@ -159,7 +159,7 @@ class ModelRunner:
                 dec_rows.append(row)
             else:
                 tiles += [(s, off, pos0 + min(off + 64, n)) for off in range(0, n, 64)]
-            commits.append((e.request, pos0 + n))
+            commits.append((e.request, pos0 + n, e.tokens))
             row += n
             max_ctx = max(max_ctx, pos0 + n)
             max_seg = max(max_seg, n)
@@ -200,8 +200,8 @@ class ModelRunner:
             return self._step_graph(entries)
         ctx, commits = self.build_context(entries)
         logits = self.model.forward(ctx, self.cache)
-        for request, length in commits:
-            self.cache.commit(request, length)
+        for request, length, tokens in commits:
+            self.cache.commit(request, length, tokens)
         return logits
 
     # ------------------------------------------------------------------ decode steps as CUDA graphs
@@ -251,7 +251,7 @@ class ModelRunner:
                 if w != 0:
                     raise StepError(f"request {e.request!r}: wanted place {w} outside its 1 token")
                 wanted.append(i)
-            commits.append((e.request, pos + 1))
+            commits.append((e.request, pos + 1, e.tokens))
             max_ctx = max(max_ctx, pos + 1)
         ctx_bucket = 256
         while ctx_bucket < max_ctx:
@@ -267,8 +267,8 @@ class ModelRunner:
         graph.replay()
         ops.launches += kernels                      # the replay launches what the capture recorded
         logits = self._graph_logits
-        for request, length in commits:
-            self.cache.commit(request, length)
+        for request, length, tokens in commits:
+            self.cache.commit(request, length, tokens)
         if wanted == list(range(rows)):
             return logits[:rows]
         if not wanted:

@@ -20,8 +20,9 @@ Policy of the reference (engine/src/scheduler.cpp:40-160), kept:
 
 Differences: pages are asked of the cache manager (several groups, windows) instead of
 a block manager of the scheduler's own; ``max_num_seqs`` bounds the requests that hold a
-slot at any time (the reference bounds the requests in one step); there is no prefix
-cache.
+slot at any time (the reference bounds the requests in one step); the prefix cache
+(engine/src/block_manager.cpp:97-125: a prompt's full pages that are already in the cache
+are shared, and its first portion starts behind them) lives in the cache manager too.
 """
 from __future__ import annotations
 
@@ -181,11 +182,12 @@ class Scheduler:
                 raise SchedulerError("The prompt requires more KV blocks than the engine owns.")
         if self.cache.free_slots == 0:
             return False
-        self.cache.admit(seq.id)
+        self.cache.admit(seq.id, seq.tokens)
         if not self.cache.can_reserve(seq.id, len(seq)):
             self.cache.release(seq.id)
             return False
         self.cache.reserve(seq.id, len(seq))
+        seq.num_cached_tokens = self.cache.computed(seq.id)     # what the prefix cache already holds
         return True
 
     def postprocess(self, plan: BatchPlan, sampled: Seq[int], is_eos: Callable[[int], bool]) -> List[Sequence]:
