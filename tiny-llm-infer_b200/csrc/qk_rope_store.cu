@@ -177,41 +177,55 @@ __global__ void qk_norm_rope_store_vec_kernel(
     if (flags & kFlagStore) page = block_table[(size_t)slot * max_pages + pos / page_size];
     __syncthreads();
     T* row = qkv + (size_t)t * heads_total * HD;
-    // with few tokens the heads of a token are spread over gridDim.y blocks (one round per warp)
-    for (int head = blockIdx.y * warps + warp; head < heads_total; head += warps * gridDim.y) {
-        const bool is_q = head < q_heads, is_k = !is_q && head < q_heads + kv_heads;
-        T* src = row + (size_t)head * HD + e0;
-        float x[VEC];
-        VecIO<T, VEC>::load(src, x);
-        if ((is_q || is_k) && (flags & kFlagNorm)) {
-            float ss = 0.0f;
+    // With few tokens the heads of a token are spread over gridDim.y blocks (one round per warp);
+    // with many a warp takes several heads, and loads kRounds of them before it works on the
+    // first, so that their latencies overlap.
+    constexpr int kRounds = 6;
+    const int stride = warps * gridDim.y;
+    for (int first = blockIdx.y * warps + warp; first < heads_total; first += stride * kRounds) {
+        float xs[kRounds][VEC];
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) ss += x[i] * x[i];
-            ss = warp_sum(ss);
-            const float scale = 1.0f / sqrtf(ss / (float)HD + eps);
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) x[i] = (is_q ? gq[i] : gk[i]) * x[i] * scale;
+        for (int r = 0; r < kRounds; ++r) {
+            const int head = first + r * stride;
+            if (head < heads_total) VecIO<T, VEC>::load(row + (size_t)head * HD + e0, xs[r]);
         }
-        if ((is_q || is_k) && rope) {
-            const bool low = lane < 16;
-            const int f0 = low ? e0 : e0 - HALF;
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) {
-                const float other = __shfl_xor_sync(0xffffffffu, x[i], 16);
-                const float c = cs[f0 + i], s = sn[f0 + i];
-                x[i] = low ? x[i] * c - other * s : other * s + x[i] * c;
+        for (int r = 0; r < kRounds; ++r) {
+            const int head = first + r * stride;
+            if (head >= heads_total) break;
+            float (&x)[VEC] = xs[r];
+            const bool is_q = head < q_heads, is_k = !is_q && head < q_heads + kv_heads;
+            T* src = row + (size_t)head * HD + e0;
+            if ((is_q || is_k) && (flags & kFlagNorm)) {
+                float ss = 0.0f;
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) ss += x[i] * x[i];
+                ss = warp_sum(ss);
+                const float scale = 1.0f / sqrtf(ss / (float)HD + eps);
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) x[i] = (is_q ? gq[i] : gk[i]) * x[i] * scale;
             }
-        }
-        if (is_q) {
-            if (flags & kFlagQOut) VecIO<T, VEC>::store(q_out + ((size_t)t * q_heads + head) * HD + e0, x);
-        } else {
-            if ((flags & kFlagStore) && page >= 0) {
-                const int kvh = is_k ? head - q_heads : head - q_heads - kv_heads;
-                T* dst = cache + ((((size_t)page * 2 + (is_k ? 0 : 1)) * kv_heads + kvh) * page_size +
-                                  (pos % page_size)) * HD + e0;
-                VecIO<T, VEC>::store(dst, x);
+            if ((is_q || is_k) && rope) {
+                const bool low = lane < 16;
+                const int f0 = low ? e0 : e0 - HALF;
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) {
+                    const float other = __shfl_xor_sync(0xffffffffu, x[i], 16);
+                    const float c = cs[f0 + i], s = sn[f0 + i];
+                    x[i] = low ? x[i] * c - other * s : other * s + x[i] * c;
+                }
             }
-            if (flags & kFlagKvOut) VecIO<T, VEC>::store(src, x);
+            if (is_q) {
+                if (flags & kFlagQOut) VecIO<T, VEC>::store(q_out + ((size_t)t * q_heads + head) * HD + e0, x);
+            } else {
+                if ((flags & kFlagStore) && page >= 0) {
+                    const int kvh = is_k ? head - q_heads : head - q_heads - kv_heads;
+                    T* dst = cache + ((((size_t)page * 2 + (is_k ? 0 : 1)) * kv_heads + kvh) * page_size +
+                                      (pos % page_size)) * HD + e0;
+                    VecIO<T, VEC>::store(dst, x);
+                }
+                if (flags & kFlagKvOut) VecIO<T, VEC>::store(src, x);
+            }
         }
     }
 }
