@@ -438,6 +438,44 @@ def test_prefill_tcgen05_kernel_segments(ops, nh, nkv, ps, window):
         assert err < tol(torch.bfloat16, want.abs().max().item()), (s, p0, n, err)
 
 
+@pytest.mark.parametrize("nh,nkv,window", [(4, 2, None), (3, 1, None), (2, 1, 1000)])
+def test_prefill_tcgen05_long_request(ops, nh, nkv, window):
+    """One portion of 3000 tokens behind 1100 that are already in the cache: some 65 key tiles per
+    block, so the rings of key and value tiles, the S buffers and every barrier's parity wrap
+    many times.  Checked against float64 attention on sampled rows of every block."""
+    hd, ps, have, new = 128, 16, 1100, 3000
+    n = have + new
+    pages = -(-n // ps)
+    g = torch.Generator(device="cuda").manual_seed(7)
+    cache = (torch.randn((pages + 3, 2, nkv, ps, hd), generator=g, device="cuda") * 0.5).to(torch.bfloat16)
+    table = (torch.randperm(pages + 3, generator=torch.Generator().manual_seed(8))[:pages]).to(torch.int32).view(1, -1)
+    q = (torch.randn((new, nh * hd), generator=g, device="cuda") * 0.5).to(torch.bfloat16)
+    rows = ops.prefill_tcgen05_block_rows(nh, nkv)
+    tiles = torch.tensor([[0, off] for off in range(0, new, rows)][::-1], dtype=torch.int32)
+    out = torch.zeros_like(q)
+    ops.paged_attention_prefill_tcgen05(q, cache, dev(torch.tensor([[0, 0, new, have]], dtype=torch.int32)),
+                                        dev(tiles), len(tiles), dev(table), ps, nh, nkv, hd, window,
+                                        1 / math.sqrt(hd), out)
+    ops.check_error_word(torch.device("cuda"))
+    # keys and values of the request in position order, float64
+    kv = cache[table[0].long().cuda()].double()                       # [pages, 2, nkv, ps, hd]
+    K = kv[:, 0].permute(1, 0, 2, 3).reshape(nkv, pages * ps, hd)[:, :n]
+    V = kv[:, 1].permute(1, 0, 2, 3).reshape(nkv, pages * ps, hd)[:, :n]
+    sample = torch.cat([torch.arange(0, new, 37), torch.tensor([127, 128, 255, 256, new - 1])]).cuda()
+    pos = have + sample
+    qq = q.double().view(new, nh, hd)[sample]
+    got = out.double().view(new, nh, hd)[sample]
+    keys = torch.arange(n, device="cuda")
+    mask = keys[None, :] <= pos[:, None]
+    if window:
+        mask &= keys[None, :] > pos[:, None] - window
+    for h in range(nh):
+        s = qq[:, h] @ K[h // (nh // nkv)].T / math.sqrt(hd)
+        want = torch.softmax(s.masked_fill(~mask, float("-inf")), -1) @ V[h // (nh // nkv)]
+        err = (got[:, h] - want).abs().max().item()
+        assert err < tol(torch.bfloat16, want.abs().max().item()), (h, err)       # a lost key tile would show at four times this
+
+
 def test_prefill_tcgen05_refuses_other_shapes(ops):
     z = torch.zeros((1, 4), dtype=torch.int32, device="cuda")
     for nh, nkv, hd, ps, match in ((2, 2, 64, 16, "head_dim"), (2, 2, 128, 8, "page size"), (3, 2, 128, 16, "heads")):
