@@ -47,26 +47,25 @@ __device__ __forceinline__ uint4 ld_coherent(const void* p) {
     return v;
 }
 
-template <int NT, bool SWIGLU>
+template <int NT>
 struct SkinnyStage {
     uint4 a_lo[kSkinnyUnroll], a_hi[kSkinnyUnroll], b[kSkinnyUnroll][NT];
-    uint4 u_lo[SWIGLU ? kSkinnyUnroll : 1], u_hi[SWIGLU ? kSkinnyUnroll : 1];     // the "up" rows of a SwiGLU pair
 };
 
-// SWIGLU: w is [gate rows; up rows] with N rows each; the block owns gate rows r0..r0+15 and the
-// up rows that belong to them, and writes silu(gate) * up: y is [M, N].
+// SWIGLU: w is [gate rows; up rows] with N rows each; the block owns gate rows r0..r0+7 as the
+// upper half of its 16-row tile and the up rows that belong to them as the lower half, so that
+// a gate sum and its up sum meet in one thread's accumulator; it writes silu(gate) * up: y is
+// [M, N].  The grid, the bytes per block and the registers are those of the plain product of
+// the 2 N rows.
 template <int NT, typename TOut, bool SWIGLU>
 __global__ void __launch_bounds__(kSkinnyWarps * 32)
 skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, TOut* y, int M, int N, int K) {
     __shared__ float red[kSkinnyWarps][16][NT * 8 + 1];
-    __shared__ float red_up[SWIGLU ? kSkinnyWarps : 1][16][NT * 8 + 1];
     asm volatile("griddepcontrol.launch_dependents;\n" ::);
-    const int r0 = blockIdx.x * 16;
+    const int r0 = blockIdx.x * (SWIGLU ? 8 : 16);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, c = lane & 3, rq = lane >> 2;
     const bf16* w_lo = w + (size_t)min(r0 + rq, N - 1) * K;
-    const bf16* w_hi = w + (size_t)min(r0 + rq + 8, N - 1) * K;
-    const bf16* u_lo = w_lo + (size_t)N * K;
-    const bf16* u_hi = w_hi + (size_t)N * K;
+    const bf16* w_hi = SWIGLU ? w_lo + (size_t)N * K : w + (size_t)min(r0 + rq + 8, N - 1) * K;
     const bf16* xr[NT];
     bool xv[NT];
 #pragma unroll
@@ -75,32 +74,25 @@ skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, TOut* y, int M, in
         xv[nt] = tok < M;
         xr[nt] = x + (size_t)(xv[nt] ? tok : 0) * K;
     }
-    float acc[NT][4], acc_up[NT][4];
+    float acc[NT][4];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-        acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
-        acc_up[nt][0] = acc_up[nt][1] = acc_up[nt][2] = acc_up[nt][3] = 0.0f;
-    }
+    for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
 
     const int kblocks = (K + 31) >> 5;                       // 32 k per block: 8 per lane of a quad
     const int per_warp = (kblocks + kSkinnyWarps - 1) / kSkinnyWarps;
     const int kb0 = warp * per_warp, kb1 = min(kblocks, kb0 + per_warp);
     const uint4 zero = make_uint4(0, 0, 0, 0);
 
-    auto load_w = [&](SkinnyStage<NT, SWIGLU>& s, int kb) {
+    auto load_w = [&](SkinnyStage<NT>& s, int kb) {
 #pragma unroll
         for (int u = 0; u < kSkinnyUnroll; ++u) {
             const int k = (kb + u) * 32 + c * 8;
             const bool ok = kb + u < kb1 && k < K;
             s.a_lo[u] = ok ? ld_stream(w_lo + k) : zero;
             s.a_hi[u] = ok ? ld_stream(w_hi + k) : zero;
-            if (SWIGLU) {
-                s.u_lo[u] = ok ? ld_stream(u_lo + k) : zero;
-                s.u_hi[u] = ok ? ld_stream(u_hi + k) : zero;
-            }
         }
     };
-    auto load_x = [&](SkinnyStage<NT, SWIGLU>& s, int kb) {
+    auto load_x = [&](SkinnyStage<NT>& s, int kb) {
 #pragma unroll
         for (int u = 0; u < kSkinnyUnroll; ++u) {
             const int k = (kb + u) * 32 + c * 8;
@@ -110,7 +102,7 @@ skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, TOut* y, int M, in
                 s.b[u][nt] = (ok && xv[nt]) ? ld_coherent(xr[nt] + k) : zero;
         }
     };
-    auto multiply = [&](const SkinnyStage<NT, SWIGLU>& s) {
+    auto multiply = [&](const SkinnyStage<NT>& s) {
 #pragma unroll
         for (int u = 0; u < kSkinnyUnroll; ++u) {
             const uint32_t a1[4] = {s.a_lo[u].x, s.a_hi[u].x, s.a_lo[u].y, s.a_hi[u].y};
@@ -120,17 +112,11 @@ skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, TOut* y, int M, in
                 const uint32_t b1[2] = {s.b[u][nt].x, s.b[u][nt].y}, b2[2] = {s.b[u][nt].z, s.b[u][nt].w};
                 mma_bf16_16816(acc[nt], a1, b1);
                 mma_bf16_16816(acc[nt], a2, b2);
-                if (SWIGLU) {
-                    const uint32_t u1[4] = {s.u_lo[u].x, s.u_hi[u].x, s.u_lo[u].y, s.u_hi[u].y};
-                    const uint32_t u2[4] = {s.u_lo[u].z, s.u_hi[u].z, s.u_lo[u].w, s.u_hi[u].w};
-                    mma_bf16_16816(acc_up[nt], u1, b1);
-                    mma_bf16_16816(acc_up[nt], u2, b2);
-                }
             }
         }
     };
 
-    SkinnyStage<NT, SWIGLU> s0, s1, s2;
+    SkinnyStage<NT> s0, s1, s2;
     load_w(s0, kb0);                                         // weights depend on no earlier kernel
     load_w(s1, kb0 + kSkinnyUnroll);
     asm volatile("griddepcontrol.wait;\n" ::: "memory");     // from here on x may be read, y written
@@ -153,16 +139,11 @@ skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, TOut* y, int M, in
         red[warp][rq][nt * 8 + c * 2 + 1] = acc[nt][1];
         red[warp][rq + 8][nt * 8 + c * 2] = acc[nt][2];
         red[warp][rq + 8][nt * 8 + c * 2 + 1] = acc[nt][3];
-        if (SWIGLU) {
-            red_up[warp][rq][nt * 8 + c * 2] = acc_up[nt][0];
-            red_up[warp][rq][nt * 8 + c * 2 + 1] = acc_up[nt][1];
-            red_up[warp][rq + 8][nt * 8 + c * 2] = acc_up[nt][2];
-            red_up[warp][rq + 8][nt * 8 + c * 2 + 1] = acc_up[nt][3];
-        }
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < 16 * NT * 8; idx += blockDim.x) {
-        const int row = idx & 15, tok = idx >> 4;
+    constexpr int kRows = SWIGLU ? 8 : 16;                   // output columns of the block
+    for (int idx = threadIdx.x; idx < kRows * NT * 8; idx += blockDim.x) {
+        const int row = idx % kRows, tok = idx / kRows;
         if (tok < M && r0 + row < N) {
             float s = 0.0f;
 #pragma unroll
@@ -170,7 +151,7 @@ skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, TOut* y, int M, in
             if (SWIGLU) {
                 float up = 0.0f;
 #pragma unroll
-                for (int ww = 0; ww < kSkinnyWarps; ++ww) up += red_up[ww][row][tok];
+                for (int ww = 0; ww < kSkinnyWarps; ++ww) up += red[ww][row + 8][tok];
                 s = s / (1.0f + expf(-s)) * up;
             }
             y[(size_t)tok * N + r0 + row] = from_f32<TOut>(s);
@@ -181,7 +162,7 @@ skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, TOut* y, int M, in
 template <int NT, typename TOut, bool SWIGLU>
 static int launch_skinny(const void* x, const void* w, void* y, int M, int N, int K, cudaStream_t stream) {
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((N + 15) / 16);
+    cfg.gridDim = dim3(SWIGLU ? (N + 7) / 8 : (N + 15) / 16);
     cfg.blockDim = dim3(kSkinnyWarps * 32);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = stream;
@@ -229,6 +210,7 @@ extern "C" int tllm_gemm_skinny_swiglu(const void* x, const void* w, void* y, in
                                        cudaStream_t stream) {
     TLLM_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_skinny_swiglu: bad sizes");
     TLLM_REQUIRE(M <= 16, "gemm_skinny_swiglu: %d rows exceed 16", M);
+    TLLM_REQUIRE(N % 8 == 0, "gemm_skinny_swiglu: N = %d is no multiple of 8", N);
     TLLM_REQUIRE(K % 8 == 0, "gemm_skinny_swiglu: K = %d is no multiple of 8", K);
     TLLM_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15u) == 0,
                  "gemm_skinny_swiglu: operands must be 16-byte aligned");
