@@ -267,12 +267,12 @@ static int launch_decode(const void* q, const void* cache, const int* positions,
         configured = true;
     }
     const dim3 grid(splits, kv_heads, n_rows);
-    launch_pdl(paged_attention_decode_kernel<HD>, grid, dim3(kDecWarps * 32), smem, stream,
+    launch_pdl(kPdlAttention, paged_attention_decode_kernel<HD>, grid, dim3(kDecWarps * 32), smem, stream,
         (const bf16*)q, (const bf16*)cache, positions, token_slot, rows, block_table, max_pages, page_size,
         q_heads, kv_heads, window, scale * 1.4426950408889634f, splits, part_o, part_ml, (bf16*)out);
     int rc = finish_launch("paged_attention_decode");
     if (rc != 0 || splits == 1) return rc;
-    launch_pdl(paged_attention_combine_kernel<HD>, dim3(n_rows, q_heads), dim3(HD), 0, stream,
+    launch_pdl(kPdlCombine, paged_attention_combine_kernel<HD>, dim3(n_rows, q_heads), dim3(HD), 0, stream,
         (const float*)part_o, (const float*) part_ml, token_slot, rows, q_heads, splits, (bf16*)out);
     return finish_launch("paged_attention_combine");
 }

@@ -110,7 +110,7 @@ static int launch_general(const void* q, const void* cache, const int* positions
     const size_t smem = ((size_t)head_dim * (1 + kWarps) + 2 * kWarps) * sizeof(float);
     const int chunks = (head_dim + 31) / 32;
 #define LAUNCH(C)                                                                              \
-    launch_pdl(paged_attention_general_kernel<T, C>, grid, block, smem, stream,                 \
+    launch_pdl(kPdlAttention, paged_attention_general_kernel<T, C>, grid, block, smem, stream,                 \
         (const T*)q, (const T*)cache, positions, token_slot, block_table, max_pages, page_size, \
         q_heads, kv_heads, head_dim, window, scale, (T*)out)
     if (chunks <= 1) LAUNCH(1);

@@ -201,7 +201,7 @@ static int launch_prefill(const void* q, const void* cache, const int* seg_info,
         if (e != cudaSuccess) { set_error("paged_attention_prefill: %s", cudaGetErrorString(e)); return (int)e; }
         configured = true;
     }
-    launch_pdl(paged_attention_prefill_kernel<HD>, dim3(n_tiles, q_heads), dim3(kPfWarps * 32), smem, stream,
+    launch_pdl(kPdlAttention, paged_attention_prefill_kernel<HD>, dim3(n_tiles, q_heads), dim3(kPfWarps * 32), smem, stream,
         (const bf16*)q, (const bf16*)cache, seg_info, tiles, block_table, max_pages, page_size, q_heads,
         kv_heads, window, scale * 1.4426950408889634f, (bf16*)out);
     return finish_launch("paged_attention_prefill");

@@ -61,18 +61,23 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
         TLLM_PDL_WAIT();    \
     } while (0)
 
-// Whether `launch_pdl` really asks for the early start.  Measured on a decode step of a
-// Qwen3-8B-sized model: early starts pay for the kernels that have something to fetch before
-// they wait (the weight-streaming product); for the short element-wise kernels between them
-// an ordinary launch is faster as long as they still let their successor start early.  The
-// default is therefore off for the callers of this function; TLLM_PDL=1 switches it on.
-inline bool pdl_enabled() {
-    static const bool on = [] { const char* v = getenv("TLLM_PDL"); return v != nullptr && v[0] == '1'; }();
-    return on;
+// Whether `launch_pdl` really asks for the early start, by the class of the kernel.  Measured on
+// a decode step of a Qwen3-8B-sized model (4.16 ms): early starts pay for the kernels that have
+// something to fetch before they wait (the weight-streaming product, which always asks); for the
+// short kernels between them an ordinary launch is as fast or faster (norm 4.17 ms, q/k 4.17,
+// SwiGLU 4.22, attention 4.22, combine 4.24), and when several classes start early at once whole
+// chains of products are resident and fetching long before their turn (norm + q/k + SwiGLU +
+// combine: 4.93 ms).  So the default is none; the environment variable TLLM_PDL holds the sum of
+// the classes to switch on, for measurements.  All kernels still let their successor start early.
+enum PdlClass { kPdlNorm = 1, kPdlQk = 2, kPdlSwiglu = 4, kPdlAttention = 8, kPdlCombine = 16, kPdlOther = 32 };
+
+inline bool pdl_enabled(int cls) {
+    static const int mask = [] { const char* v = getenv("TLLM_PDL"); return v != nullptr ? atoi(v) : 0; }();
+    return (mask & cls) != 0;
 }
 
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+inline cudaError_t launch_pdl(int cls, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
                               cudaStream_t stream, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
@@ -83,7 +88,7 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = pdl_enabled(cls) ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

@@ -261,7 +261,7 @@ static int launch_add_rmsnorm_typed(float* h, const void* delta, const void* gai
         while (block < 1024 && block < chunks) block *= 2;
         const int per_thread = (chunks + block - 1) / block;
 #define VEC_LAUNCH(C)                                                                 \
-    launch_pdl(add_rmsnorm_vec_kernel<TD, TG, TO, C>, dim3(n_out), dim3(block), 0, stream, \
+    launch_pdl(kPdlNorm, add_rmsnorm_vec_kernel<TD, TG, TO, C>, dim3(n_out), dim3(block), 0, stream, \
                h, (const TD*)delta, (const TG*)gain, eps, (TO*)out, rows, width)
         if (per_thread <= 1) VEC_LAUNCH(1);
         else if (per_thread <= 2) VEC_LAUNCH(2);
@@ -269,7 +269,7 @@ static int launch_add_rmsnorm_typed(float* h, const void* delta, const void* gai
 #undef VEC_LAUNCH
     } else {
         const int block = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
-        launch_pdl(add_rmsnorm_kernel<TD, TG, TO>, dim3(n_out), dim3(block), 0, stream,
+        launch_pdl(kPdlNorm, add_rmsnorm_kernel<TD, TG, TO>, dim3(n_out), dim3(block), 0, stream,
                    h, (const TD*)delta, (const TG*)gain, eps, (TO*)out, rows, width);
     }
     return finish_launch("add_rmsnorm");
@@ -300,11 +300,11 @@ int tllm_embedding(const int* ids, const void* table, int table_dtype, float* ou
     const bool vec = hidden % 8 == 0 && aligned16(table) && aligned16(out);
     const int block = vec ? (hidden >= 2048 ? 256 : 128) : (hidden >= 1024 ? 256 : 128);
     if (table_dtype == kBF16) {
-        if (vec) launch_pdl(embedding_vec_kernel<bf16>, dim3(tokens), dim3(block), 0, stream, ids, (const bf16*)table, out, hidden, vocab);
-        else launch_pdl(embedding_kernel<bf16>, dim3(tokens), dim3(block), 0, stream, ids, (const bf16*)table, out, hidden, vocab);
+        if (vec) launch_pdl(kPdlOther, embedding_vec_kernel<bf16>, dim3(tokens), dim3(block), 0, stream, ids, (const bf16*)table, out, hidden, vocab);
+        else launch_pdl(kPdlOther, embedding_kernel<bf16>, dim3(tokens), dim3(block), 0, stream, ids, (const bf16*)table, out, hidden, vocab);
     } else {
-        if (vec) launch_pdl(embedding_vec_kernel<float>, dim3(tokens), dim3(block), 0, stream, ids, (const float*)table, out, hidden, vocab);
-        else launch_pdl(embedding_kernel<float>, dim3(tokens), dim3(block), 0, stream, ids, (const float*)table, out, hidden, vocab);
+        if (vec) launch_pdl(kPdlOther, embedding_vec_kernel<float>, dim3(tokens), dim3(block), 0, stream, ids, (const float*)table, out, hidden, vocab);
+        else launch_pdl(kPdlOther, embedding_kernel<float>, dim3(tokens), dim3(block), 0, stream, ids, (const float*)table, out, hidden, vocab);
     }
     return finish_launch("embedding");
 }
@@ -335,15 +335,15 @@ int tllm_swiglu(const void* gate_up, void* out, int dtype, int tokens, int inter
         const size_t chunks = total / 8;
         const int grid = grid_for(chunks, block);
         if (dtype == kBF16)
-            launch_pdl(swiglu_vec_kernel<bf16>, dim3(grid), dim3(block), 0, stream, (const bf16*)gate_up, (bf16*)out, inter, chunks);
+            launch_pdl(kPdlSwiglu, swiglu_vec_kernel<bf16>, dim3(grid), dim3(block), 0, stream, (const bf16*)gate_up, (bf16*)out, inter, chunks);
         else
-            launch_pdl(swiglu_vec_kernel<float>, dim3(grid), dim3(block), 0, stream, (const float*)gate_up, (float*)out, inter, chunks);
+            launch_pdl(kPdlSwiglu, swiglu_vec_kernel<float>, dim3(grid), dim3(block), 0, stream, (const float*)gate_up, (float*)out, inter, chunks);
     } else {
         const int grid = grid_for(total, block);
         if (dtype == kBF16)
-            launch_pdl(swiglu_kernel<bf16>, dim3(grid), dim3(block), 0, stream, (const bf16*)gate_up, (bf16*)out, inter, total);
+            launch_pdl(kPdlSwiglu, swiglu_kernel<bf16>, dim3(grid), dim3(block), 0, stream, (const bf16*)gate_up, (bf16*)out, inter, total);
         else
-            launch_pdl(swiglu_kernel<float>, dim3(grid), dim3(block), 0, stream, (const float*)gate_up, (float*)out, inter, total);
+            launch_pdl(kPdlSwiglu, swiglu_kernel<float>, dim3(grid), dim3(block), 0, stream, (const float*)gate_up, (float*)out, inter, total);
     }
     return finish_launch("swiglu");
 }

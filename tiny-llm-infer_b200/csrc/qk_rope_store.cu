@@ -260,7 +260,7 @@ extern "C" int tllm_qk_norm_rope_store(
             const int vblock = 256;
             const int vgroups = tokens <= 64 ? (q_heads + 2 * kv_heads + 7) / 8 : 1;
 #define VLAUNCH(T, TG, VEC)                                                                         \
-    launch_pdl(qk_norm_rope_store_vec_kernel<T, TG, VEC>, dim3(tokens, vgroups), dim3(vblock), 0, stream, \
+    launch_pdl(kPdlQk, qk_norm_rope_store_vec_kernel<T, TG, VEC>, dim3(tokens, vgroups), dim3(vblock), 0, stream, \
         (T*)qkv, (const TG*)q_gain, (const TG*)k_gain, eps, inv_freq, positions, token_slot,        \
         block_table, max_pages, (T*)cache, page_size, (T*)q_out, q_heads, kv_heads, flags)
 #define VDISPATCH(T, TG)                                              \
@@ -284,7 +284,7 @@ extern "C" int tllm_qk_norm_rope_store(
     const int grid = (int)((units + warps - 1) / warps);
     const size_t smem = (size_t)warps * head_dim * sizeof(float);
 #define LAUNCH(T, TG)                                                                            \
-    launch_pdl(qk_norm_rope_store_kernel<T, TG>, dim3(grid), dim3(block), smem, stream,          \
+    launch_pdl(kPdlQk, qk_norm_rope_store_kernel<T, TG>, dim3(grid), dim3(block), smem, stream,          \
         (T*)qkv, (const TG*)q_gain, (const TG*)k_gain, eps, inv_freq, rotary_dim, positions,     \
         token_slot, block_table, max_pages, (T*)cache, page_size, (T*)q_out, tokens, q_heads,    \
         kv_heads, head_dim, flags)

@@ -190,11 +190,11 @@ extern "C" int tllm_sample_split(const float* logits, int rows, int vocab, long 
     TLLM_REQUIRE(partial != nullptr && blocks_per_row >= 1 && blocks_per_row <= 1024 && rows <= 65535,
                  "sample: bad split");
     if (rows == 0) return 0;
-    launch_pdl(sample_partial_kernel, dim3(blocks_per_row, rows), dim3(256), 0, stream,
+    launch_pdl(kPdlOther, sample_partial_kernel, dim3(blocks_per_row, rows), dim3(256), 0, stream,
         logits, vocab, row_stride, params, seeds, (Best*)partial, blocks_per_row);
     int rc = finish_launch("sample_partial");
     if (rc) return rc;
-    launch_pdl(sample_final_kernel, dim3(rows), dim3(64), 0, stream, (const Best*)partial, blocks_per_row, params, out);
+    launch_pdl(kPdlOther, sample_final_kernel, dim3(rows), dim3(64), 0, stream, (const Best*)partial, blocks_per_row, params, out);
     rc = finish_launch("sample_final");
     if (rc || !any_nucleus) return rc;
     sample_kernel<<<rows, vocab >= 8192 ? 1024 : 256, 0, stream>>>(logits, vocab, row_stride, params, seeds, out, 1);
