@@ -313,8 +313,8 @@ def request_data(lens, nkv, hd, ps, seed, num_pages, max_pages):
 
 @pytest.mark.parametrize("nh,nkv,hd,ps,window", [(32, 8, 128, 16, None), (4, 2, 64, 16, None), (16, 1, 128, 32, None),
                                                  (6, 2, 64, 64, 100), (3, 3, 128, 16, 33), (14, 2, 64, 16, None)])
-@pytest.mark.parametrize("splits", [1, 3, 8])
-def test_decode_kernel_split_keys(ops, nh, nkv, hd, ps, window, splits):
+@pytest.mark.parametrize("splits,cluster", [(1, True), (3, True), (8, True), (13, True), (3, False), (8, False), (20, True)])
+def test_decode_kernel_split_keys(ops, nh, nkv, hd, ps, window, splits, cluster):
     """One-token rows of four requests (contexts 1 to 700), a padding row, a row list; for
     each query one far key dominates: the first key the window admits or a page's last."""
     lens = [700, 1, 130, 65]
@@ -337,7 +337,8 @@ def test_decode_kernel_split_keys(ops, nh, nkv, hd, ps, window, splits):
     rows = torch.tensor([0, 1, 3, 4, 6, 5, 2], dtype=torch.int32)          # every row, in another order
     out = torch.full((T, nh * hd), 3.0, dtype=torch.bfloat16, device="cuda")
     ops.paged_attention_decode(dev(q.reshape(T, -1).to(torch.bfloat16)), cache, dev(pos), dev(slot), dev(rows), T,
-                               dev(table), ps, nh, nkv, hd, window, 1 / math.sqrt(hd), out, 700, splits=splits)
+                               dev(table), ps, nh, nkv, hd, window, 1 / math.sqrt(hd), out, 700, splits=splits,
+                               cluster=cluster)
     got = out.cpu().double().view(T, nh, hd)
     assert (got[2] == 0).all()
     for t in range(T):

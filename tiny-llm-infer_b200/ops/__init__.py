@@ -219,14 +219,23 @@ def fast_attention_ok(dtype, page_size: int, q_heads: int, kv_heads: int, head_d
 
 
 def paged_attention_decode(q, cache, positions, token_slot, rows, n_rows, block_table, page_size,
-                           q_heads, kv_heads, head_dim, window, scale, out, max_context, splits=None):
+                           q_heads, kv_heads, head_dim, window, scale, out, max_context, splits=None,
+                           cluster=False):
     """Attention of one-token rows (``rows``: their indices, None for all), keys split over
-    ``splits`` blocks per (row, key/value head)."""
+    ``splits`` blocks per (row, key/value head); the splits' partial results go through scratch
+    in global memory to a second small kernel.  ``cluster=True`` (up to 16 splits): the blocks
+    of a (row, key/value head) run as one thread-block cluster and combine through
+    distributed shared memory instead, with no scratch and no second kernel.  Measured at
+    Qwen3-8B sizes, context 4096: alone the cluster form is the faster one (26.0 against 27.8 µs
+    per layer at 8 rows, 11.1 against 11.5 at one row; 169 against 164 at 64 rows), inside a
+    decode step the slower one (4.21 against 4.17 ms at 8 rows: the short combine kernel hides
+    the start of the product that follows), so the engine does not ask for it."""
     _cuda(q, cache, positions, token_slot, rows, block_table, out)
     if splits is None:
         splits = decode_splits(n_rows, kv_heads, max_context)
     part_o = part_ml = None
-    if splits > 1:
+    scratch = splits > 1 and not (cluster and splits <= 16)
+    if scratch:
         n = n_rows * q_heads * splits
         ws = workspace(q.device, n * (head_dim + 2))
         part_o, part_ml = ws[:n * head_dim], ws[n * head_dim:n * (head_dim + 2)]
@@ -234,7 +243,7 @@ def paged_attention_decode(q, cache, positions, token_slot, rows, n_rows, block_
         _p(q), _p(cache), _p(positions), _p(token_slot), _p(rows), n_rows, _p(block_table),
         block_table.shape[1], page_size, q_heads, kv_heads, head_dim, int(window or 0), float(scale),
         splits, _p(part_o), _p(part_ml), _p(out), _stream()), "paged_attention_decode",
-        kernels=2 if splits > 1 else 1)
+        kernels=2 if scratch else 1)
     return out
 
 
