@@ -14,7 +14,7 @@ import torch
 from tiny_llm_infer_b200 import ops
 
 NAMES = ["embedding", "add_rmsnorm", "swiglu", "cast", "qk_norm_rope_store", "paged_attention",
-         "sample", "linear", "linear_swiglu"]
+         "sample", "linear", "linear_swiglu", "interleave_gate_up"]
 
 
 def install(monkeypatch):
@@ -40,9 +40,13 @@ def add_rmsnorm(h, delta, gain, eps, out, rows=None):
     return out
 
 
-def swiglu(gate_up, out):
+def swiglu(gate_up, out, interleaved=False):
     inter = out.shape[1]
-    g, u = gate_up[:, :inter].float(), gate_up[:, inter:].float()
+    if interleaved:                  # groups of sixteen columns: eight gates, their eight ups
+        pairs = gate_up.float().reshape(gate_up.shape[0], inter // 8, 2, 8)
+        g, u = pairs[:, :, 0].reshape(-1, inter), pairs[:, :, 1].reshape(-1, inter)
+    else:
+        g, u = gate_up[:, :inter].float(), gate_up[:, inter:].float()
     out.copy_((g / (1 + torch.exp(-g)) * u).to(out.dtype))
     return out
 
@@ -56,10 +60,15 @@ def linear(x, weight, out_dtype=None):
     return (x.float() @ weight.float().t()).to(want)
 
 
-def linear_swiglu(x, w_gate_up, out_dtype):
+def interleave_gate_up(gate, up):
+    inter, k = gate.shape
+    return torch.stack([gate.reshape(inter // 8, 8, k), up.reshape(inter // 8, 8, k)], dim=1).reshape(2 * inter, k)
+
+
+def linear_swiglu(x, w_gate_up, out_dtype, interleaved=False):
     gate_up = linear(x, w_gate_up, out_dtype)
     out = torch.empty((x.shape[0], w_gate_up.shape[0] // 2), dtype=out_dtype)
-    return swiglu(gate_up, out)
+    return swiglu(gate_up, out, interleaved)
 
 
 def qk_norm_rope_store(qkv, q_gain, k_gain, eps, inv_freq, rotary_dim, positions, token_slot,

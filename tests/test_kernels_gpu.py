@@ -78,12 +78,20 @@ def test_add_rmsnorm(ops, dtype, width, eps):
     assert torch.equal(h2.cpu(), h)
 
 
+def interleaved_columns(t):
+    """[rows, 2 I] with gate columns first, up columns after -> gate and up interleaved by eight."""
+    rows, two_i = t.shape
+    inter = two_i // 2
+    return torch.stack([t[:, :inter].reshape(rows, inter // 8, 8), t[:, inter:].reshape(rows, inter // 8, 8)],
+                       dim=2).reshape(rows, two_i).contiguous()
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("inter", [200, 1000])
-def test_swiglu(ops, dtype, inter):
+@pytest.mark.parametrize("inter,interleaved", [(200, False), (1000, False), (77, False), (200, True), (1000, True)])
+def test_swiglu(ops, dtype, inter, interleaved):
     gu = rnd(9, 2 * inter, seed=5, scale=3.0).to(dtype)
     out = torch.empty((9, inter), dtype=dtype, device="cuda")
-    ops.swiglu(dev(gu), out)
+    ops.swiglu(dev(interleaved_columns(gu) if interleaved else gu), out, interleaved)
     g, u = gu[:, :inter].double(), gu[:, inter:].double()
     want = plain.silu(g) * u
     assert (out.cpu().double() - want).abs().max() < tol(dtype, want.abs().max().item())
@@ -524,12 +532,15 @@ def test_gemm_skinny(ops, M, N, K):
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (200, 304, 328), (300, 1000, 136), (1000, 512, 4104),
                                    (2048, 1536, 1024)])
-@pytest.mark.parametrize("swiglu", [False, True])
+@pytest.mark.parametrize("swiglu", [False, "stacked", "interleaved"])
 @pytest.mark.parametrize("short_tiles", [False, True])
 def test_gemm_tcgen05(ops, M, N, K, swiglu, short_tiles):
     """The TMA + tcgen05 product: row and column counts that end inside a tile, K that ends
-    inside a 64-wide block, several tiles per block (both accumulators in turn), fused SwiGLU.
-    One weight row and one k-column are made much larger than the rest."""
+    inside a 64-wide block, several tiles per block (both accumulators in turn), fused SwiGLU
+    with gate and up rows stacked or interleaved by eight.  One weight row and one k-column are
+    made much larger than the rest."""
+    if swiglu == "interleaved" and N % 16:
+        pytest.skip("interleaved rows come in sixteens")
     x = rnd(M, K, seed=400, scale=0.5).to(torch.bfloat16)
     w = rnd(N, K, seed=401, scale=0.5).to(torch.bfloat16)
     w[N - 1] *= 8
@@ -537,7 +548,9 @@ def test_gemm_tcgen05(ops, M, N, K, swiglu, short_tiles):
     ref = x.double() @ w.double().T
     if swiglu:
         ref = plain.silu(ref[:, :N // 2]) * ref[:, N // 2:]
-    y = ops.gemm_tcgen05(dev(x), dev(w), swiglu, short_tiles)
+    if swiglu == "interleaved":
+        w = ops.interleave_gate_up(w[:N // 2], w[N // 2:])
+    y = ops.gemm_tcgen05(dev(x), dev(w), bool(swiglu), short_tiles, interleaved=swiglu == "interleaved")
     ops.check_error_word("cuda:0")
     assert y.shape == ref.shape and y.dtype == torch.bfloat16
     assert (y.cpu().double() - ref).abs().max() < 1.6e-2 * ref.abs().max()
@@ -558,6 +571,12 @@ def test_linear_takes_the_tcgen05_path_for_many_rows(ops):
     small = ops.linear_swiglu(dev(x[:9]), dev(w), torch.bfloat16)           # few rows: two kernels, same values
     assert ops.tcgen05_calls == before + 1
     assert (small.cpu().double() - ref[:9]).abs().max() < 1.6e-2 * ref.abs().max()
+    wi = dev(ops.interleave_gate_up(w[:5376], w[5376:]))                     # the layout the feed-forward part stores
+    for rows in (600, 9, 40):
+        act = ops.linear_swiglu(dev(x[:rows]), wi, torch.bfloat16, interleaved=True)
+        ops.check_error_word("cuda:0")
+        assert (act.cpu().double() - ref[:rows]).abs().max() < 1.6e-2 * ref.abs().max()
+    assert ops.tcgen05_calls == before + 2
 
 
 @pytest.mark.parametrize("M", [1, 5, 8])
@@ -571,6 +590,14 @@ def test_linear_swiglu_few_rows(ops, M, inter, K):
     w[2 * inter - 1] *= 10
     ref = x.double() @ w.double().T
     ref = plain.silu(ref[:, :inter]) * ref[:, inter:]
-    for act in (ops.linear_swiglu(dev(x), dev(w), torch.bfloat16), ops.gemm_skinny_swiglu(dev(x), dev(w))):
+    acts = [ops.linear_swiglu(dev(x), dev(w), torch.bfloat16)]
+    if inter % 8 == 0:
+        wi = dev(ops.interleave_gate_up(w[:inter], w[inter:]))
+        acts += [ops.gemm_skinny_swiglu(dev(x), dev(w)), ops.gemm_skinny_swiglu(dev(x), wi, interleaved=True),
+                 ops.linear_swiglu(dev(x), wi, torch.bfloat16, interleaved=True)]
+    else:
+        with pytest.raises(ops.KernelError, match="multiple of 8"):
+            ops.gemm_skinny_swiglu(dev(x), dev(w))
+    for act in acts:
         assert act.shape == (M, inter)
         assert (act.cpu().double() - ref).abs().max() < 1.6e-2 * ref.abs().max()

@@ -103,17 +103,20 @@ def test_attention_part_through_its_own_cache(dtype, nh, nkv, hd, window):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_swiglu_part(dtype):
+@pytest.mark.parametrize("I", [328, 330])       # gate and up rows interleaved by eight, or stacked
+def test_swiglu_part(dtype, I):
     from tiny_llm_infer_b200.parts.feed_forward import SwiGLUFeedForward
-    H, I = 136, 328
+    H = 136
     part = SwiGLUFeedForward(hidden_size=H, intermediate_size=I, dtype=dtype, device=DEV)
     w = {"gate_proj.weight": rnd(I, H, seed=1, scale=0.1).to(dtype), "up_proj.weight": rnd(I, H, seed=2, scale=0.1).to(dtype),
          "down_proj.weight": rnd(H, I, seed=3, scale=0.1).to(dtype)}
     part.load({k: v.to(DEV) for k, v in w.items()})
-    x = rnd(11, H, seed=4).to(dtype)
-    got = part.forward(x.to(DEV), None).cpu().double()
-    want = plain.feed_forward(x.double(), *(w[k].double() for k in ("gate_proj.weight", "up_proj.weight", "down_proj.weight")))
-    assert (got - want).abs().max() < tol(dtype, want.abs().max().item())
+    assert part.interleaved == (I % 8 == 0)
+    for rows in (5, 11, 300):                    # the few-row kernels, the library, the tcgen05 kernel
+        x = rnd(rows, H, seed=4).to(dtype)
+        got = part.forward(x.to(DEV), None).cpu().double()
+        want = plain.feed_forward(x.double(), *(w[k].double() for k in ("gate_proj.weight", "up_proj.weight", "down_proj.weight")))
+        assert (got - want).abs().max() < tol(dtype, want.abs().max().item())
 
 
 def test_prenorm_block_equals_a_plain_decoder_layer():

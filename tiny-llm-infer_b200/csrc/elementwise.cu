@@ -203,23 +203,26 @@ __global__ void add_rmsnorm_vec_kernel(float* h, const TD* delta,
 }
 
 // ---------------------------------------------------------------- SwiGLU
-// out[t, i] = silu(gu[t, i]) * gu[t, inter + i], silu(x) = x / (1 + exp(-x)), in float32.
+// out[t, i] = silu(gate) * up, silu(x) = x / (1 + exp(-x)), in float32.  Stacked columns: gate at
+// gu[t, i], up at gu[t, inter + i].  Interleaved by eight: columns come in groups of sixteen,
+// eight gates followed by their eight ups, so gate at gu[t, 16 (i / 8) + i % 8] and up 8 further.
 template <typename T>
-__global__ void swiglu_kernel(const T* gu, T* out, int inter,
+__global__ void swiglu_kernel(const T* gu, T* out, int inter, int interleaved,
                               size_t total) {
     TLLM_PDL_ENTER();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; idx < total; idx += stride) {
         const size_t t = idx / inter, i = idx - t * inter;
-        const float g = to_f32<T>(gu[t * 2 * inter + i]);
-        const float u = to_f32<T>(gu[t * 2 * inter + inter + i]);
+        const size_t gi = interleaved ? 16 * (i >> 3) + (i & 7) : i, ui = interleaved ? gi + 8 : inter + i;
+        const float g = to_f32<T>(gu[t * 2 * inter + gi]);
+        const float u = to_f32<T>(gu[t * 2 * inter + ui]);
         out[idx] = from_f32<T>(g / (1.0f + expf(-g)) * u);
     }
 }
 
 template <typename T>
-__global__ void swiglu_vec_kernel(const T* gu, T* out, int inter,
+__global__ void swiglu_vec_kernel(const T* gu, T* out, int inter, int interleaved,
                                   size_t total_chunks) {
     TLLM_PDL_ENTER();
     const int per_row = inter >> 3;
@@ -228,8 +231,8 @@ __global__ void swiglu_vec_kernel(const T* gu, T* out, int inter,
     for (; idx < total_chunks; idx += stride) {
         const size_t t = idx / per_row, c = idx - t * per_row;
         float g[8], u[8];
-        Vec8<T>::load(gu + t * 2 * inter + c * 8, g);
-        Vec8<T>::load(gu + t * 2 * inter + inter + c * 8, u);
+        Vec8<T>::load(gu + t * 2 * inter + (interleaved ? c * 16 : c * 8), g);
+        Vec8<T>::load(gu + t * 2 * inter + (interleaved ? c * 16 + 8 : inter + c * 8), u);
 #pragma unroll
         for (int e = 0; e < 8; ++e) g[e] = g[e] / (1.0f + expf(-g[e])) * u[e];
         Vec8<T>::store(out + t * inter + c * 8, g);
@@ -324,9 +327,10 @@ int tllm_add_rmsnorm(float* h, const void* delta, const void* gain, int gain_dty
     TLLM_REQUIRE(false, "add_rmsnorm: unknown dtype %d", act_dtype);
 }
 
-int tllm_swiglu(const void* gate_up, void* out, int dtype, int tokens, int inter,
+int tllm_swiglu(const void* gate_up, void* out, int dtype, int tokens, int inter, int interleaved,
                 cudaStream_t stream) {
     TLLM_REQUIRE(tokens >= 0 && inter > 0, "swiglu: bad sizes");
+    TLLM_REQUIRE(!interleaved || inter % 8 == 0, "swiglu: interleaved columns need a multiple of 8, not %d", inter);
     TLLM_REQUIRE(dtype == kBF16 || dtype == kF32, "swiglu: unknown dtype %d", dtype);
     const size_t total = (size_t)tokens * inter;
     if (total == 0) return 0;
@@ -335,15 +339,15 @@ int tllm_swiglu(const void* gate_up, void* out, int dtype, int tokens, int inter
         const size_t chunks = total / 8;
         const int grid = grid_for(chunks, block);
         if (dtype == kBF16)
-            launch_pdl(kPdlSwiglu, swiglu_vec_kernel<bf16>, dim3(grid), dim3(block), 0, stream, (const bf16*)gate_up, (bf16*)out, inter, chunks);
+            launch_pdl(kPdlSwiglu, swiglu_vec_kernel<bf16>, dim3(grid), dim3(block), 0, stream, (const bf16*)gate_up, (bf16*)out, inter, interleaved, chunks);
         else
-            launch_pdl(kPdlSwiglu, swiglu_vec_kernel<float>, dim3(grid), dim3(block), 0, stream, (const float*)gate_up, (float*)out, inter, chunks);
+            launch_pdl(kPdlSwiglu, swiglu_vec_kernel<float>, dim3(grid), dim3(block), 0, stream, (const float*)gate_up, (float*)out, inter, interleaved, chunks);
     } else {
         const int grid = grid_for(total, block);
         if (dtype == kBF16)
-            launch_pdl(kPdlSwiglu, swiglu_kernel<bf16>, dim3(grid), dim3(block), 0, stream, (const bf16*)gate_up, (bf16*)out, inter, total);
+            launch_pdl(kPdlSwiglu, swiglu_kernel<bf16>, dim3(grid), dim3(block), 0, stream, (const bf16*)gate_up, (bf16*)out, inter, interleaved, total);
         else
-            launch_pdl(kPdlSwiglu, swiglu_kernel<float>, dim3(grid), dim3(block), 0, stream, (const float*)gate_up, (float*)out, inter, total);
+            launch_pdl(kPdlSwiglu, swiglu_kernel<float>, dim3(grid), dim3(block), 0, stream, (const float*)gate_up, (float*)out, inter, interleaved, total);
     }
     return finish_launch("swiglu");
 }

@@ -142,8 +142,11 @@ __device__ __forceinline__ void store_row32(bf16* row_ptr, int col0, int cols, c
     }
 }
 
-// SWIGLU: W is [gate rows; up rows] with `half_n` rows each, a column tile is 128 outputs and y
-// is [M, half_n].  Otherwise a column tile is 256 outputs of N and y is [M, N].
+// SWIGLU: W holds `half_n` gate rows and as many up rows, a column tile is 128 outputs and y is
+// [M, half_n]; stacked ([gate; up]: the tile's gate and up rows are two boxes, accumulator columns
+// 0..127 and 128..255) or interleaved by eight (eight gate rows, their eight up rows, ...: the
+// tile is 256 neighbouring rows and a gate's up is eight columns further).  Otherwise a column
+// tile is 256 outputs of N and y is [M, N].
 // MT: row tiles of 128 per block.  MT = 1: two accumulators of 128 x 256 take turns, the
 // epilogue of a tile overlaps the MMAs of the next, four stages of 48 KB.  MT = 2: the block
 // owns 256 rows, both accumulators belong to one tile, every slab of W fetched from L2 feeds
@@ -152,8 +155,8 @@ __device__ __forceinline__ void store_row32(bf16* row_ptr, int col0, int cols, c
 template <bool SWIGLU, int MT>
 __global__ void __launch_bounds__(kGemmThreads)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                    bf16* __restrict__ y, int M, int N, int K, int half_n, int tiles_m, int tiles_n,
-                    int* __restrict__ error_word) {
+                    bf16* __restrict__ y, int M, int N, int K, int half_n, int interleaved, int tiles_m,
+                    int tiles_n, int* __restrict__ error_word) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[4], empty_bar[4], acc_full[2], acc_empty[2];
     __shared__ uint32_t tmem_base_slot;
@@ -214,7 +217,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     unsigned char* b_dst = a_dst + kStageABytes;
                     mbar_expect_tx(&full_bar[s], kStageBytes);
                     tma_load_2d(a_dst, &map_x, kb * kBK, tile_m * kRows, &full_bar[s]);
-                    if (SWIGLU) {
+                    if (SWIGLU && !interleaved) {
                         tma_load_2d(b_dst, &map_w, kb * kBK, tile_n * 128, &full_bar[s]);
                         tma_load_2d(b_dst + kStageBBytes / 2, &map_w, kb * kBK, half_n + tile_n * 128, &full_bar[s]);
                     } else {
@@ -288,7 +291,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 #pragma unroll 1
                 for (int c = 0; c < kColTile; c += 64) {                          // 64 output columns at a time
                     float v[64];
-                    if (SWIGLU) {
+                    if (SWIGLU && interleaved) {
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {             // 64 accumulator columns: 32 outputs
+                            uint32_t r0[32], r1[32];
+                            tmem_ld32_issue(lane_addr + 2 * c + 64 * h, r0);
+                            tmem_ld32_issue(lane_addr + 2 * c + 64 * h + 32, r1);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                const int gi = 16 * (i >> 3) + (i & 7);
+                                const float g0 = __uint_as_float(r0[gi]), g1 = __uint_as_float(r1[gi]);
+                                v[32 * h + i] = __fdividef(g0, 1.0f + __expf(-g0)) * __uint_as_float(r0[gi + 8]);
+                                v[32 * h + 16 + i] = __fdividef(g1, 1.0f + __expf(-g1)) * __uint_as_float(r1[gi + 8]);
+                            }
+                        }
+                    } else if (SWIGLU) {
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
                             uint32_t gr[32], ur[32];
@@ -394,7 +412,7 @@ static int sm_count() {
 
 template <bool SWIGLU, int MT>
 static int launch_tcgen05(const CUtensorMap& mx, const CUtensorMap& mw, void* y, int M, int N, int K, int half_n,
-                          int* error_word, cudaStream_t stream) {
+                          int interleaved, int* error_word, cudaStream_t stream) {
     const size_t smem = (size_t)(MT == 1 ? 4 : 3) * (kBM * MT * kBK * 2 + kStageBBytes) + 1024 + 4 * 32 * (64 * 2 + 16);
     static bool configured = false;
     if (!configured) {
@@ -408,8 +426,8 @@ static int launch_tcgen05(const CUtensorMap& mx, const CUtensorMap& mw, void* y,
     const int tiles_n = (out_cols + col_tile - 1) / col_tile, tiles_m = (M + kBM * MT - 1) / (kBM * MT);
     const int total = tiles_m * tiles_n;
     const int grid = total < sm_count() ? total : sm_count();
-    gemm_tcgen05_kernel<SWIGLU, MT><<<grid, kGemmThreads, smem, stream>>>(mx, mw, (bf16*)y, M, N, K, half_n, tiles_m,
-                                                                      tiles_n, error_word);
+    gemm_tcgen05_kernel<SWIGLU, MT><<<grid, kGemmThreads, smem, stream>>>(mx, mw, (bf16*)y, M, N, K, half_n, interleaved,
+                                                                      tiles_m, tiles_n, error_word);
     return finish_launch("gemm_tcgen05");
 }
 
@@ -417,15 +435,19 @@ static int launch_tcgen05(const CUtensorMap& mx, const CUtensorMap& mw, void* y,
 
 using namespace tllm;
 
-// y = x . w^T (swiglu == 0: y is [M, N]) or y = silu(x . w[:N/2]^T) * (x . w[N/2:]^T)
-// (swiglu != 0: y is [M, N / 2]).  x [M, K], w [N, K] bfloat16 row-major, K a multiple of 8,
+// y = x . w^T (y is [M, N]) or, with bit 1 of `swiglu`, y = silu(x . gate^T) * (x . up^T) (y is
+// [M, N / 2]) for w = [gate; up], or with bit 4 as well for gate and up rows interleaved by eight.
+// Bit 2 keeps blocks of 128 rows.  x [M, K], w [N, K] bfloat16 row-major, K a multiple of 8,
 // operands 16-byte aligned.  `error_word` is a device int the kernel sets to a non-zero code if
 // one of its bounded waits ran out (the result is then invalid); the caller clears and reads it.
 extern "C" int tllm_gemm_tcgen05(const void* x, const void* w, void* y, int M, int N, int K, int swiglu,
                                  int* error_word, cudaStream_t stream) {
     TLLM_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tcgen05: bad sizes");
     TLLM_REQUIRE(K % 8 == 0, "gemm_tcgen05: K = %d is no multiple of 8", K);
-    TLLM_REQUIRE(!swiglu || N % 2 == 0, "gemm_tcgen05: SwiGLU needs an even number of weight rows");
+    TLLM_REQUIRE(!(swiglu & 1) || N % 2 == 0, "gemm_tcgen05: SwiGLU needs an even number of weight rows");
+    const int interleaved = (swiglu & 4) ? 1 : 0;
+    TLLM_REQUIRE(!interleaved || ((swiglu & 1) && N % 16 == 0),
+                 "gemm_tcgen05: interleaved gate and up rows come in sixteens, N = %d", N);
     TLLM_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(y)) & 15u) == 0,
                  "gemm_tcgen05: operands must be 16-byte aligned");
     TLLM_REQUIRE(error_word != nullptr, "gemm_tcgen05: no error word");
@@ -434,8 +456,8 @@ extern "C" int tllm_gemm_tcgen05(const void* x, const void* w, void* y, int M, i
     TLLM_REQUIRE(make_map(&mx, x, M, K, tall ? 2 * kBM : kBM) && make_map(&mw, w, N, K, 128),
                  "gemm_tcgen05: cuTensorMapEncodeTiled failed or is not available");
     if (swiglu & 1)
-        return tall ? launch_tcgen05<true, 2>(mx, mw, y, M, N, K, N / 2, error_word, stream)
-                    : launch_tcgen05<true, 1>(mx, mw, y, M, N, K, N / 2, error_word, stream);
-    return tall ? launch_tcgen05<false, 2>(mx, mw, y, M, N, K, 0, error_word, stream)
-                : launch_tcgen05<false, 1>(mx, mw, y, M, N, K, 0, error_word, stream);
+        return tall ? launch_tcgen05<true, 2>(mx, mw, y, M, N, K, N / 2, interleaved, error_word, stream)
+                    : launch_tcgen05<true, 1>(mx, mw, y, M, N, K, N / 2, interleaved, error_word, stream);
+    return tall ? launch_tcgen05<false, 2>(mx, mw, y, M, N, K, 0, 0, error_word, stream)
+                : launch_tcgen05<false, 1>(mx, mw, y, M, N, K, 0, 0, error_word, stream);
 }

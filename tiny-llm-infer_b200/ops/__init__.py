@@ -60,7 +60,7 @@ def _declare(h) -> None:
     sigs = {
         "tllm_embedding": [vp, vp, i32, vp, i32, i32, i32, vp],
         "tllm_add_rmsnorm": [vp, vp, vp, i32, f32, vp, i32, vp, i32, i32, vp],
-        "tllm_swiglu": [vp, vp, i32, i32, i32, vp],
+        "tllm_swiglu": [vp, vp, i32, i32, i32, i32, vp],
         "tllm_cast": [vp, i32, vp, i32, i64, vp],
         "tllm_qk_norm_rope_store": [vp, vp, vp, i32, f32, vp, i32, vp, vp, vp, i32, vp, i32, vp,
                                     i32, i32, i32, i32, i32, i32, vp],
@@ -70,7 +70,7 @@ def _declare(h) -> None:
         "tllm_sample_split": [vp, i32, i32, i64, vp, vp, vp, vp, i32, i32, vp],
         "tllm_gemm_skinny": [vp, vp, vp, i32, i32, i32, i32, vp],
         "tllm_gemm_tcgen05": [vp, vp, vp, i32, i32, i32, i32, vp, vp],
-        "tllm_gemm_skinny_swiglu": [vp, vp, vp, i32, i32, i32, vp],
+        "tllm_gemm_skinny_swiglu": [vp, vp, vp, i32, i32, i32, i32, vp],
         "tllm_paged_attention_decode": [vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32,
                                         i32, vp, vp, vp, vp],
         "tllm_paged_attention_prefill": [vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32, vp, vp],
@@ -143,12 +143,24 @@ def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], gain: torch.Tens
     return out
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[2 I, K] with the rows of ``gate`` and ``up`` ([I, K], I a multiple of 8) interleaved by
+    eight: eight gate rows, the eight up rows that belong to them, and so on.  A block of the
+    weight-streaming product and a tile of the tcgen05 product then read neighbouring rows and
+    find a gate and its up in one accumulator, so SwiGLU fits their epilogues."""
+    inter, k = gate.shape
+    assert up.shape == gate.shape and inter % 8 == 0
+    return torch.stack([gate.reshape(inter // 8, 8, k), up.reshape(inter // 8, 8, k)], dim=1).reshape(2 * inter, k)
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> torch.Tensor:
+    """out[t, i] = silu(gate) * up with gate = gate_up[t, i], up = gate_up[t, I + i], or, for columns
+    interleaved by eight, gate = gate_up[t, 16 (i // 8) + i % 8] and up eight columns further."""
     _cuda(gate_up, out)
     tokens, two_i = gate_up.shape
     assert out.shape == (tokens, two_i // 2) and out.dtype == gate_up.dtype
-    _check(lib().tllm_swiglu(_p(gate_up), _p(out), _dt(out), tokens, two_i // 2, _stream()), "swiglu")
+    _check(lib().tllm_swiglu(_p(gate_up), _p(out), _dt(out), tokens, two_i // 2, int(interleaved), _stream()),
+           "swiglu")
     return out
 
 
@@ -346,12 +358,13 @@ def uniform_of(seed: int, token: int) -> float:
     return float(lib().tllm_uniform_of(seed & 0xFFFFFFFFFFFFFFFF, token))
 
 
-# Rows up to which gate/up product and SwiGLU are one weight-streaming kernel.  0: not used.
-# Measured at Qwen3-8B sizes, 8 rows: the fused kernel (a block streams eight gate rows and the
-# eight up rows that belong to them, 96 MB apart) takes 43.0 µs where the product of all 2 N rows
-# (sixteen neighbouring rows per block) takes 35.1 µs and the SwiGLU kernel 2.1 µs more; a decode
-# step takes 4.45 ms with it and 4.16 ms without.  Rows of gate and up interleaved in memory would
-# make the two patterns the same.  The kernel stays tested.
+# Rows up to which gate/up product and SwiGLU are one weight-streaming kernel when the weight is
+# stacked [gate; up].  0: not used.  Measured at Qwen3-8B sizes, 8 rows: a block then streams eight
+# gate rows and the eight up rows that belong to them, 96 MB apart, and takes 43.0 µs where the
+# product of all 2 N rows (sixteen neighbouring rows per block) takes 35.1 µs and the SwiGLU kernel
+# 2.1 µs more; a decode step takes 4.45 ms with it and 4.16 ms without.  With gate and up rows
+# interleaved by eight (what the feed-forward part stores) the patterns are the same and the
+# fused kernel is used up to SKINNY_MAX_ROWS.
 SKINNY_SWIGLU_MAX_ROWS = 0
 SKINNY_MAX_ROWS = 8       # up to this many rows the weight-streaming product beats the library
 
@@ -402,11 +415,13 @@ def tcgen05_pays(rows: int, out_cols: int, k: int, dtype, col_tile: int = 256) -
     return tiles / (rounds * SM_COUNT) >= 0.85
 
 
-def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, swiglu: bool = False, short_tiles: bool = False) -> torch.Tensor:
+def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, swiglu: bool = False, short_tiles: bool = False,
+                 interleaved: bool = False) -> torch.Tensor:
     """y = x . weight^T on tcgen05 tensor cores fed by TMA (csrc/gemm_tcgen05.cu), bfloat16 in
     and out, float32 accumulation in tensor memory.  With ``swiglu`` the weight is [gate; up]
-    and the result is silu(x . gate^T) * (x . up^T), [rows, weight rows / 2].  ``short_tiles``
-    keeps blocks of 128 rows even when there are more (for measurements)."""
+    (or, ``interleaved``, gate and up rows interleaved by eight) and the result is
+    silu(x . gate^T) * (x . up^T), [rows, weight rows / 2].  ``short_tiles`` keeps blocks of 128
+    rows even when there are more (for measurements)."""
     _cuda(x, weight)
     rows, k = x.shape
     n = weight.shape[0]
@@ -416,7 +431,7 @@ def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, swiglu: bool = False, sh
         return y
     global tcgen05_calls
     tcgen05_calls += 1
-    _check(lib().tllm_gemm_tcgen05(_p(x), _p(weight), _p(y), rows, n, k, int(swiglu) | (2 if short_tiles else 0),
+    _check(lib().tllm_gemm_tcgen05(_p(x), _p(weight), _p(y), rows, n, k, int(swiglu) | (2 if short_tiles else 0) | (4 if interleaved else 0),
                                    _p(error_word(x.device)), _stream()), "gemm_tcgen05")
     return y
 
@@ -446,29 +461,31 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     return torch.mm(x, weight.t(), out_dtype=want)
 
 
-def gemm_skinny_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+def gemm_skinny_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, interleaved: bool = False) -> torch.Tensor:
     """silu(x . Wg^T) * (x . Wu^T) for at most 16 bfloat16 rows as one weight-streaming kernel."""
     _cuda(x, w_gate_up)
     rows, k = x.shape
     inter = w_gate_up.shape[0] // 2
     act = torch.empty((rows, inter), dtype=torch.bfloat16, device=x.device)
-    _check(lib().tllm_gemm_skinny_swiglu(_p(x), _p(w_gate_up), _p(act), rows, inter, k, _stream()),
-           "gemm_skinny_swiglu")
+    _check(lib().tllm_gemm_skinny_swiglu(_p(x), _p(w_gate_up), _p(act), rows, inter, k, int(interleaved),
+                                         _stream()), "gemm_skinny_swiglu")
     return act
 
 
-def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
-    """silu(x . Wg^T) * (x . Wu^T) for w_gate_up = [Wg; Wu].  With enough bfloat16 rows the
-    product and the activation are one tcgen05 kernel; otherwise the product is followed by the
-    SwiGLU kernel."""
+def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out_dtype: torch.dtype,
+                  interleaved: bool = False) -> torch.Tensor:
+    """silu(x . Wg^T) * (x . Wu^T) for w_gate_up = [Wg; Wu], or with the rows of Wg and Wu
+    interleaved by eight (``interleave_gate_up``).  With enough bfloat16 rows the product and the
+    activation are one tcgen05 kernel, with few rows and interleaved weights one weight-streaming
+    kernel; otherwise the product is followed by the SwiGLU kernel."""
     rows, k = x.shape
     inter = w_gate_up.shape[0] // 2
-    if x.dtype == w_gate_up.dtype == out_dtype == torch.bfloat16 and x.is_contiguous() \
-            and w_gate_up.is_contiguous() and tcgen05_pays(rows, inter, k, w_gate_up.dtype, col_tile=128):
-        return gemm_tcgen05(x, w_gate_up, swiglu=True)
-    if x.dtype == w_gate_up.dtype == out_dtype == torch.bfloat16 and 0 < rows <= SKINNY_SWIGLU_MAX_ROWS \
-            and k % 8 == 0 and x.is_contiguous() and w_gate_up.is_contiguous():
-        return gemm_skinny_swiglu(x, w_gate_up)
+    plain = x.dtype == w_gate_up.dtype == out_dtype == torch.bfloat16 and x.is_contiguous() \
+        and w_gate_up.is_contiguous()
+    if plain and tcgen05_pays(rows, inter, k, w_gate_up.dtype, col_tile=128):
+        return gemm_tcgen05(x, w_gate_up, swiglu=True, interleaved=interleaved)
+    if plain and 0 < rows <= (SKINNY_MAX_ROWS if interleaved else SKINNY_SWIGLU_MAX_ROWS) and k % 8 == 0:
+        return gemm_skinny_swiglu(x, w_gate_up, interleaved)
     gate_up = linear(x, w_gate_up, out_dtype=out_dtype)
     act = torch.empty((rows, inter), dtype=out_dtype, device=x.device)
-    return swiglu(gate_up, act)
+    return swiglu(gate_up, act, interleaved)
