@@ -220,3 +220,38 @@ def test_toy_parts_and_run_order_need_no_change_to_the_framework(tmp_path):
     another's cache: registered from the tests, built from a folder, stepped in portions
     and mixed with a second request, compared with a plain restatement."""
     run_toy(tmp_path, "cuda:0")
+
+
+@pytest.mark.parametrize("name,dtype", [("B", "float32"), ("E", "bfloat16")])
+def test_repeated_prompt_layouts_replay_as_graphs(folders, name, dtype):
+    """A step layout that comes a second time is captured as a CUDA graph and replayed from the
+    third time on; the logits are those of a runner that launches every kernel itself: equal to
+    the bit for prompt-only steps (the same kernels on the same data), and within rounding where
+    one-token rows run beside a portion (their key splits follow the context bucket)."""
+    from tiny_llm_infer_b200.cache import CacheManager
+    from tiny_llm_infer_b200.engine import DTYPES, ModelRunner, StepEntry, load_model
+    tiny = TINIES[name]
+    model, cfg = load_model(str(folders[name]), DTYPES[dtype], "cuda:0")
+    runners = []
+    for graphs in (True, False):
+        cache = CacheManager(model.cache_needs(), tiny["page_size"], 160, 8, 512, DTYPES[dtype], "cuda:0")
+        runners.append(ModelRunner(model, cache, max_batch_tokens=512, use_graphs=graphs))
+    with_graphs, plain_runner = runners
+    vocab = cfg.vocab_size
+    for i in range(5):                                   # five prompts of 200 tokens, each in one step
+        toks = prompt(50 + i, 200, vocab)
+        got = [r.step([StepEntry(f"p{i}", toks, [0, 199])]).clone() for r in runners]
+        assert torch.equal(got[0], got[1]), i
+        if i >= 2:
+            for r in runners:
+                r.release(f"p{i - 2}")
+    assert len(with_graphs._prompt_graphs) == 1 and not plain_runner._prompt_graphs
+    for i in range(4):                                   # two live requests decode beside a portion of a new one
+        toks = prompt(70 + i, 150, vocab)
+        entries = [StepEntry("p3", [i + 1], [0]), StepEntry("p4", [i + 2], [0]), StepEntry(f"q{i}", toks, [149])]
+        got = [r.step(entries).clone() for r in runners]
+        assert (got[0] - got[1]).abs().max() < (1e-4 if dtype == "float32" else 0.05), i
+        for r in runners:
+            r.release(f"q{i}")
+    assert len(with_graphs._prompt_graphs) == 2
+    with_graphs.check_kernels()
