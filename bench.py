@@ -40,8 +40,11 @@ def peaks():
     if path.is_file():
         try:
             raw = json.loads(path.read_text())
-            return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]),
-                    "source": "measured"}
+            out = {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]),
+                   "source": "measured"}
+            if raw.get("bf16_tflops_sustained"):          # a seconds-long loop under the power cap
+                out["bf16_tflops_sustained"] = float(raw["bf16_tflops_sustained"])
+            return out
         except (KeyError, ValueError, TypeError):
             pass
     return dict(FALLBACK_PEAKS)
@@ -180,6 +183,8 @@ def main() -> int:
         prefill = {"value": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "tokens": PREFILL_TOKENS,
                    "ms": round(prefill_ms, 3),
                    "frac": round(prefill_flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+        if pk.get("bf16_tflops_sustained"):
+            prefill["frac_sustained"] = round(prefill_flops / (prefill_ms / 1e3) / (pk["bf16_tflops_sustained"] * 1e12), 4)
         print(f"[bench] prefill {prefill}", file=sys.stderr, flush=True)
 
     # ---------------------------------------------------------------- decode, timed on the device
