@@ -355,6 +355,10 @@ class CacheManager:
         self._tokens[slot] = tokens[:hits * ps]
         self._hashed[slot], self._chain[slot] = hits, chain
 
+    def _covered(self, slot: int) -> int:
+        """Tokens [0, n) that the slot's pages cover in every group."""
+        return min(g.end_page[slot] for g in self.groups.values()) * self.page_size if self.groups else 0
+
     def pages_needed(self, request: Hashable, new_len: int) -> Dict[Optional[int], int]:
         """Pages each group must still hand out so that tokens [0, new_len) are covered."""
         slot = self._slot_of[request]
@@ -363,6 +367,8 @@ class CacheManager:
                 for k, g in self.groups.items()}
 
     def can_reserve(self, request: Hashable, new_len: int) -> bool:
+        if new_len <= self._covered(self._slot_of[request]):
+            return new_len <= self.max_seq_len   # the pages are there already (most decode steps)
         if new_len > self.max_seq_len:
             return False
         need = self.pages_needed(request, new_len)
@@ -370,6 +376,11 @@ class CacheManager:
 
     def reserve(self, request: Hashable, new_len: int) -> None:
         """Cover tokens [0, new_len) with pages in every group, or change nothing."""
+        slot = self._slot_of[request]
+        if new_len <= self._covered(slot) and new_len <= self.max_seq_len:
+            if new_len > self._reserved[slot]:
+                self._reserved[slot] = new_len
+            return
         if new_len > self.max_seq_len:
             raise CacheError(f"{new_len} tokens exceed the maximum sequence length {self.max_seq_len}")
         if not self.can_reserve(request, new_len):

@@ -180,7 +180,8 @@ class ModelRunner:
         self.cache.sync()
         if self.is_cuda:
             self._dev[:used].copy_(self._host[:used], non_blocking=True)
-            self._uploaded = torch.cuda.Event()
+            if self._uploaded is None:
+                self._uploaded = torch.cuda.Event()
             self._uploaded.record()
         else:
             self._dev[:used].copy_(self._host[:used])
@@ -324,7 +325,8 @@ class ModelRunner:
             ctx_bucket *= 2
         self.cache.sync()
         self._dev[:4 * bucket].copy_(self._host[:4 * bucket], non_blocking=True)
-        self._uploaded = torch.cuda.Event()
+        if self._uploaded is None:
+            self._uploaded = torch.cuda.Event()
         self._uploaded.record()
         key = (bucket, ctx_bucket)
         if key not in self._graphs:
