@@ -193,7 +193,7 @@ def run_toy(tmp_path, device):
     model, cfg = load_model(folder, torch.float32, device)
     needs = model.cache_needs()
     assert sum(1 for c, s in needs.values() if s is not None) == 2        # two visits of the stateful layer
-    assert sum(1 for c, s in needs.values() if c is not None) == 2        # cache 10 is shared, one more
+    assert sum(1 for c, s in needs.values() if c is not None) == 3        # cache 10 is shared, two more
     cache = CacheManager(needs, 8, 24, 3, 128, torch.float32, device)
     runner = ModelRunner(model, cache, 256)
     a, b = prompt(1, 50, 160), prompt(2, 37, 160)
@@ -216,7 +216,8 @@ def run_toy(tmp_path, device):
 
 
 def test_toy_parts_and_run_order_need_no_change_to_the_framework(tmp_path):
-    """A stateful mixer, a partial rotary encoding, a layer run twice and a layer reading
+    """A stateful mixer, a feed-forward with a router over experts, a position encoding the
+    kernels do not know (and a partial rotary one), a layer run twice and a layer reading
     another's cache: registered from the tests, built from a folder, stepped in portions
     and mixed with a second request, compared with a plain restatement."""
     run_toy(tmp_path, "cuda:0")

@@ -1,6 +1,7 @@
 """Parts and an architecture that exist only in the tests: a mixer with state of its own
-(a running mean), a partial rotary encoding, a run order that names a layer twice and lets
-a layer read another layer's cache.  They are registered through the package's public
+(a running mean), a feed-forward with a router over two experts, a position encoding that is
+no rotation (and a partial rotary one), a run order that names a layer twice and lets a
+layer read another layer's cache.  They are registered through the package's public
 registries, without a change to its files, and restated with the plain implementation's
 functions."""
 from dataclasses import dataclass
@@ -49,6 +50,58 @@ def register_toys():
                 st[self.h] += seg.length
             return ops.linear(out, self.w, out_dtype=self.dtype)
 
+    @register("feed_forward", "toy_routed")
+    class RoutedExperts:
+        """Two SwiGLU experts weighted by a router: delta = sum_e softmax(x Wr^T)_e * expert_e(x),
+        router logits and weights in float32."""
+
+        def __init__(self, hidden_size, intermediate_size, dtype, device):
+            self.h, self.i, self.dtype = hidden_size, intermediate_size, dtype
+            self.router = None
+            self.experts = []
+
+        @classmethod
+        def param_specs(cls, hidden_size, intermediate_size):
+            specs = {"router.weight": ParamSpec((2, hidden_size))}
+            for e in range(2):
+                specs[f"experts.{e}.gate_proj.weight"] = ParamSpec((intermediate_size, hidden_size))
+                specs[f"experts.{e}.up_proj.weight"] = ParamSpec((intermediate_size, hidden_size))
+                specs[f"experts.{e}.down_proj.weight"] = ParamSpec((hidden_size, intermediate_size))
+            return specs
+
+        def load(self, t):
+            self.router = t["router.weight"].float().contiguous()
+            self.experts = [(torch.cat([t[f"experts.{e}.gate_proj.weight"], t[f"experts.{e}.up_proj.weight"]]).contiguous(),
+                             t[f"experts.{e}.down_proj.weight"].contiguous()) for e in range(2)]
+
+        def forward(self, x, ctx):
+            weights = torch.softmax(x.float() @ self.router.T, dim=-1)
+            out = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+            for e, (w_gate_up, w_down) in enumerate(self.experts):
+                act = ops.linear_swiglu(x, w_gate_up, out_dtype=self.dtype)
+                out += weights[:, e:e + 1] * ops.linear(act, w_down, out_dtype=self.dtype).float()
+            return out.to(self.dtype)
+
+    @register("position", "toy_cosine_gate")
+    class CosineGate:
+        """Not a rotation: element i of every query and key head is scaled by cos(pos * (i + 1) / 40).
+        The attention part does not know it and calls ``apply`` between its norm and the cache."""
+
+        def __init__(self, head_dim, dtype, device):
+            self.freq = ((torch.arange(head_dim, dtype=torch.float32) + 1) / 40).to(device)
+
+        @classmethod
+        def param_specs(cls, **params):
+            return {}
+
+        def load(self, tensors):
+            pass
+
+        def apply(self, q, k, positions):
+            gate = torch.cos(positions.float()[:, None] * self.freq[None, :])[:, None, :]
+            q.copy_((q.float() * gate).to(q.dtype))
+            k.copy_((k.float() * gate).to(k.dtype))
+
     @dataclass(frozen=True)
     class ToyConfig(ModelConfig):
         hidden_size: int = 48
@@ -84,12 +137,20 @@ def register_toys():
                 "norm1": PartSpec("rmsnorm", norm, p + "n1."), "mixer": PartSpec(mixer[0], mixer[1], p + "mixer."),
                 "norm2": PartSpec("rmsnorm", norm, p + "n2."),
                 "ffn": PartSpec(ffn.kind, ffn.params, p + "ffn.")})
+        gated = dict(attn, position=PartSpec("toy_cosine_gate", dict(head_dim=16)))
+        routed = PartSpec("toy_routed", dict(hidden_size=H, intermediate_size=40))
+
+        def layer3():
+            p = "layers.3."
+            return LayerSpec("prenorm", {
+                "norm1": PartSpec("rmsnorm", norm, p + "n1."), "mixer": PartSpec("gq_attention", gated, p + "mixer."),
+                "norm2": PartSpec("rmsnorm", norm, p + "n2."), "ffn": PartSpec(routed.kind, routed.params, p + "ffn.")})
         layers = (layer(0, ("toy_running_mean", dict(hidden_size=H))), layer(1, ("gq_attention", attn)),
-                  layer(2, ("gq_attention", attn)))
+                  layer(2, ("gq_attention", attn)), layer3())
         # layer 1 runs twice (second visit with a cache of its own); layer 2 reads the cache
         # that the first visit of layer 1 wrote
         order = (ExecEntry(0), ExecEntry(1, cache=10), ExecEntry(2, cache=10, writes_cache=False),
-                 ExecEntry(1), ExecEntry(0))
+                 ExecEntry(3), ExecEntry(1), ExecEntry(0))
         return ModelDescription(H, cfg.vocab_size, cfg.max_position_embeddings,
                                 PartSpec("token_embedding", dict(vocab_size=cfg.vocab_size, hidden_size=H), "embed."),
                                 layers, order, PartSpec("rmsnorm", norm, "final."),
@@ -134,9 +195,23 @@ def toy_plain(w, ids, eps):
         o = plain.causal_attention(q, k, v).reshape(T, 48) @ w[p + "mixer.o_proj.weight"].T
         return ffn(h + o, p), (k, v)
 
+    def gated_routed_layer(h):
+        p = "layers.3."
+        x = plain.rms_norm(h, w[p + "n1.weight"], eps)
+        gate = torch.cos(pos.to(F)[:, None] * ((torch.arange(16, dtype=F) + 1) / 40)[None, :])[:, None, :]
+        q = plain.rms_norm((x @ w[p + "mixer.q_proj.weight"].T).view(T, 3, 16), w[p + "mixer.q_norm.weight"], eps) * gate
+        k = plain.rms_norm((x @ w[p + "mixer.k_proj.weight"].T).view(T, 1, 16), w[p + "mixer.k_norm.weight"], eps) * gate
+        v = (x @ w[p + "mixer.v_proj.weight"].T).view(T, 1, 16)
+        h = h + plain.causal_attention(q, k, v).reshape(T, 48) @ w[p + "mixer.o_proj.weight"].T
+        x = plain.rms_norm(h, w[p + "n2.weight"], eps)
+        weights = torch.softmax(x @ w[p + "ffn.router.weight"].T, dim=-1)
+        return h + sum(weights[:, e:e + 1] * plain.feed_forward(x, *(w[p + f"ffn.experts.{e}.{n}_proj.weight"]
+                                                                     for n in ("gate", "up", "down"))) for e in range(2))
+
     h = mean_layer(h)
     h, kv1 = attn_layer(h, 1)
     h, _ = attn_layer(h, 2, kv1)
+    h = gated_routed_layer(h)
     h, _ = attn_layer(h, 1)
     h = mean_layer(h)
     return plain.rms_norm(h, w["final.weight"], eps) @ w["head.weight"].T
