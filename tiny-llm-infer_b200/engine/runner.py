@@ -77,6 +77,12 @@ class ModelRunner:
         self.model, self.cache = model, cache
         self.use_graphs = use_graphs
         self._graphs = {}
+        # a step may be captured as a CUDA graph only if every launch of it reads the step's data from
+        # device buffers: mixers say so themselves (graph_safe = True), other parts may say no
+        self._graph_safe = all(
+            getattr(b.mixer, "graph_safe", False)
+            and all(getattr(getattr(b, role, None), "graph_safe", True) for role in getattr(b, "roles", ()) if role != "mixer")
+            for b in model.blocks)
         self._graph_pool = None
         self._prompt_pool = None
         self._prompt_graphs: dict = {}
@@ -229,7 +235,7 @@ class ModelRunner:
     def _prompt_signature(self, ctx: StepContext):
         if not (self.use_graphs and self.is_cuda and ctx.tokens >= self.PROMPT_GRAPH_MIN_TOKENS
                 and ctx.want_rows.shape[0] <= min(self.GRAPH_MAX_ROWS, self.max_batch_tokens)
-                and all(getattr(b.mixer, "graph_safe", False) for b in self.model.blocks)):
+                and self._graph_safe):
             return None
         bucket = 0
         if ctx.n_dec:
@@ -285,7 +291,7 @@ class ModelRunner:
         return (self.is_cuda and 0 < len(entries) <= self.GRAPH_MAX_ROWS
                 and len(entries) <= self.max_batch_tokens
                 and all(len(e.tokens) == 1 for e in entries)
-                and all(getattr(b.mixer, "graph_safe", False) for b in self.model.blocks))
+                and self._graph_safe)
 
     def _step_graph(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         rows = len(entries)
