@@ -221,6 +221,8 @@ class CacheManager:
         self._request_of: Dict[int, Hashable] = {}
         self._reserved = [0] * max_slots       # tokens covered by pages
         self._computed = [0] * max_slots       # tokens whose keys and values are in the cache
+        self._windowed = [g for g in self.groups.values() if g.window is not None]
+        self._one_group = next(iter(self.groups.values())) if len(self.groups) == 1 else None
         self.prefix_active = bool(prefix_cache) and set(self.groups) == {None} \
             and all(state is None for _, state in needs.values())
         self._tokens: List[Optional[List[int]]] = [None] * max_slots   # of the request, while they are known
@@ -357,7 +359,22 @@ class CacheManager:
 
     def _covered(self, slot: int) -> int:
         """Tokens [0, n) that the slot's pages cover in every group."""
+        if self._one_group is not None:
+            return self._one_group.end_page[slot] * self.page_size
         return min(g.end_page[slot] for g in self.groups.values()) * self.page_size if self.groups else 0
+
+    def try_reserve(self, request: Hashable, new_len: int) -> bool:
+        """``reserve`` if it can be done, else nothing and False (one look-up for the common case
+        of a decode step whose page is there already)."""
+        slot = self._slot_of[request]
+        if new_len <= self._covered(slot) and new_len <= self.max_seq_len:
+            if new_len > self._reserved[slot]:
+                self._reserved[slot] = new_len
+            return True
+        if not self.can_reserve(request, new_len):
+            return False
+        self.reserve(request, new_len)
+        return True
 
     def pages_needed(self, request: Hashable, new_len: int) -> Dict[Optional[int], int]:
         """Pages each group must still hand out so that tokens [0, new_len) are covered."""
@@ -405,7 +422,7 @@ class CacheManager:
             raise CacheError("more tokens computed than pages were reserved for")
         before = self._computed[slot]
         self._computed[slot] = computed_len
-        for g in self.groups.values():
+        for g in self._windowed:
             dead = min(g.dead_before(computed_len), g.end_page[slot])
             for p in range(g.first_page[slot], dead):
                 g.drop(int(g.table[slot, p]))

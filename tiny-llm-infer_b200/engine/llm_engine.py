@@ -109,7 +109,7 @@ class LLMEngine:
             entries.append(StepEntry(seq.id, toks, want))
             if item.samples:
                 rows.append((seq.sampling.temperature, seq.sampling.top_p,
-                             draw_key(seq.seed, len(seq.completion))))
+                             draw_key(seq.seed, seq.num_completion_tokens)))
                 row_of.append(len(entries) - 1)
         logits = self.runner.step(entries)
         tokens = self.sampler.sample(logits, rows)

@@ -80,6 +80,10 @@ class Sequence:
     def completion(self) -> List[int]:
         return self.tokens[self.prompt_len:]
 
+    @property
+    def num_completion_tokens(self) -> int:
+        return len(self.tokens) - self.prompt_len
+
 
 @dataclass
 class ScheduledSequence:
@@ -139,10 +143,9 @@ class Scheduler:
             if len(plan.sequences) >= max_seqs or used >= budget:
                 break
             seq = self.running.popleft()
-            if not self.cache.can_reserve(seq.id, len(seq)):
+            if not self.cache.try_reserve(seq.id, len(seq)):
                 self._preempt(seq, plan)
                 continue
-            self.cache.reserve(seq.id, len(seq))
             seq.num_scheduled_tokens = 1
             plan.sequences.append(ScheduledSequence(seq, len(seq) - 1, 1, False, True))
             self.running.append(seq)
@@ -206,7 +209,7 @@ class Scheduler:
                 raise SchedulerError("The model runner did not return a token for a completed step.")
             seq.tokens.append(int(token))
             stop = (not seq.sampling.ignore_eos and is_eos(int(token))) \
-                or len(seq.completion) >= seq.sampling.max_tokens
+                or seq.num_completion_tokens >= seq.sampling.max_tokens
             if stop:
                 seq.status = Status.FINISHED
                 self.cache.release(seq.id)

@@ -97,7 +97,14 @@ def _check(code: int, what: str, kernels: int = 1) -> None:
         raise KernelError(f"{what}: {lib().tllm_last_error().decode(errors='replace')} (code {code})")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """Handle of the current CUDA stream of the current device (the raw getter costs a fraction
+    of a microsecond, the Stream object several)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 

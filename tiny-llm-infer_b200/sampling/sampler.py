@@ -12,6 +12,7 @@ from __future__ import annotations
 
 from typing import List, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from .. import ops
@@ -31,10 +32,6 @@ def draw_key(request_seed: int, output_index: int) -> int:
     return _mix64(_mix64(request_seed) + 0x9E3779B97F4A7C15 * (output_index + 1))
 
 
-def _signed(x: int) -> int:
-    return x - (1 << 64) if x >= (1 << 63) else x
-
-
 class Sampler:
     def __init__(self, device, max_rows: int):
         self.device = device
@@ -44,6 +41,9 @@ class Sampler:
         if cuda:
             self._params_host = self._params_host.pin_memory()
             self._seeds_host = self._seeds_host.pin_memory()
+        # numpy views of the pinned buffers: filled in one go per step, not element by element
+        self._params_np = self._params_host.numpy()
+        self._seeds_np = self._seeds_host.numpy().view(np.uint64)
         self._params = torch.empty((max_rows, 2), dtype=torch.float32, device=device)
         self._seeds = torch.empty(max_rows, dtype=torch.int64, device=device)
         self._out = torch.empty(max_rows, dtype=torch.int32, device=device)
@@ -54,12 +54,13 @@ class Sampler:
         assert logits.shape[0] == n
         if n == 0:
             return []
-        for i, (temp, top_p, key) in enumerate(rows):
-            self._params_host[i, 0] = temp
-            self._params_host[i, 1] = top_p
-            self._seeds_host[i] = _signed(key & _M)
+        temps = [r[0] for r in rows]
+        top_ps = [r[1] for r in rows]
+        self._params_np[:n, 0] = temps
+        self._params_np[:n, 1] = top_ps
+        self._seeds_np[:n] = np.fromiter((r[2] & _M for r in rows), dtype=np.uint64, count=n)
         self._params[:n].copy_(self._params_host[:n], non_blocking=True)
         self._seeds[:n].copy_(self._seeds_host[:n], non_blocking=True)
-        nucleus = any(temp > 1e-6 and top_p < 1.0 for temp, top_p, _ in rows)
+        nucleus = any(t > 1e-6 and p < 1.0 for t, p in zip(temps, top_ps))
         ops.sample(logits, self._params[:n], self._seeds[:n], self._out[:n], any_nucleus=nucleus)
         return self._out[:n].cpu().tolist()
