@@ -260,3 +260,15 @@ def test_random_orders_with_shared_prefixes_keep_every_invariant(seed):
         m.release(rid)
     m.audit()
     assert m.free_pages() == {None: 30} and m.free_slots == 5 and shared_total > 0
+
+
+def test_try_reserve_is_reserve_or_nothing():
+    m = CacheManager(MIXED, page_size=4, num_pages=3, max_slots=2, max_seq_len=64)
+    m.admit("a")
+    assert m.try_reserve("a", 9) and m.pages_of("a")[None] == [0, 1, 2]
+    assert m.try_reserve("a", 12)                       # the pages are there already
+    before = m.free_pages()
+    assert not m.try_reserve("a", 13) and m.free_pages() == before and m.pages_of("a")[None] == [0, 1, 2]
+    assert not m.try_reserve("a", 65)                   # beyond the longest sequence
+    m.commit("a", 12)
+    m.audit()
