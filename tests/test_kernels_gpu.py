@@ -259,6 +259,39 @@ def test_sample_greedy_ties_and_temperature(ops):
     assert abs(ops.uniform_of(12345, 678) - plain.uniform_of(12345, 678)) < 1e-9
 
 
+@pytest.mark.parametrize("V", [151937, 3001])
+def test_sample_nucleus(ops, V):
+    """Top-p over a vocabulary no power of two (the larger is shared by several blocks a row,
+    the smaller takes the one-block kernel), many rows with their own temperature, top_p and
+    seed: the token drawn is the best-scoring one of the plain nucleus.  One row is peaked
+    (a single token holds the mass), one is flat (every key ties, so all are kept)."""
+    rows = 24
+    logits = rnd(rows, V, seed=61, scale=3.0).float()
+    logits[0] = 0.0
+    logits[0, V // 2] = 30.0                             # alone in every nucleus
+    logits[1] = 1.25                                     # all tie
+    gen = np.random.default_rng(5)
+    temps = gen.uniform(0.3, 1.6, rows)
+    tops = gen.uniform(0.02, 0.999, rows)
+    tops[0], tops[1] = 0.9, 0.5
+    params = torch.tensor(np.stack([temps, tops], 1), dtype=torch.float32)
+    seeds = torch.tensor(gen.integers(0, 2 ** 62, rows), dtype=torch.int64)
+    for nucleus in (True, None):
+        out = torch.full((rows,), -1, dtype=torch.int32, device="cuda")
+        ops.sample(dev(logits), dev(params), dev(seeds), out, any_nucleus=nucleus)
+        got = out.cpu().tolist()
+        assert got[0] == V // 2
+        for r in range(1, rows):
+            temp, top_p = params[r].tolist()
+            scores = plain.gumbel_scores(logits[r].numpy(), temp, int(seeds[r]))
+            if r == 1:
+                assert scores[got[r]] >= scores.max() - 1e-4
+                continue
+            keep = plain.nucleus(logits[r].numpy(), temp, top_p)
+            assert got[r] in set(keep.tolist()), (r, temp, top_p, len(keep))
+            assert scores[got[r]] >= max(scores[keep]) - 1e-4, (r, temp, top_p, len(keep))
+
+
 def test_sample_distribution(ops):
     """Frequencies of many seeds follow softmax(logits / T)."""
     V, n, temp = 11, 4000, 0.8

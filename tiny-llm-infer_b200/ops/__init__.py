@@ -67,7 +67,7 @@ def _declare(h) -> None:
         "tllm_paged_attention_general": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32,
                                          i32, f32, vp, vp],
         "tllm_sample": [vp, i32, i32, i64, vp, vp, vp, vp],
-        "tllm_sample_split": [vp, i32, i32, i64, vp, vp, vp, vp, i32, i32, vp],
+        "tllm_sample_split": [vp, i32, i32, i64, vp, vp, vp, vp, i32, vp, vp],
         "tllm_gemm_skinny": [vp, vp, vp, i32, i32, i32, i32, vp],
         "tllm_gemm_tcgen05": [vp, vp, vp, i32, i32, i32, i32, vp, vp],
         "tllm_gemm_skinny_swiglu": [vp, vp, vp, i32, i32, i32, i32, vp],
@@ -83,6 +83,8 @@ def _declare(h) -> None:
         fn.restype = i32
     h.tllm_paged_attention_prefill_tc_rows.argtypes = [i32, i32]
     h.tllm_paged_attention_prefill_tc_rows.restype = i32
+    h.tllm_sample_nucleus_scratch_bytes.argtypes = [i32]
+    h.tllm_sample_nucleus_scratch_bytes.restype = i64
     h.tllm_uniform_of.argtypes = [ctypes.c_ulonglong, i32]
     h.tllm_uniform_of.restype = f32
 
@@ -337,6 +339,9 @@ def paged_attention(q: torch.Tensor, cache: torch.Tensor, positions, token_slot,
     return out
 
 
+SAMPLE_BLOCKS = 1024     # blocks over all rows beyond which a row's vocabulary is cut less finely
+
+
 def sample(logits: torch.Tensor, params: torch.Tensor, seeds: torch.Tensor,
            out: torch.Tensor, any_nucleus: Optional[bool] = None) -> torch.Tensor:
     """Token per row of float32 ``logits`` [S, V]: params[s] = (temperature, top_p), seeds[s]
@@ -347,13 +352,16 @@ def sample(logits: torch.Tensor, params: torch.Tensor, seeds: torch.Tensor,
     assert seeds.dtype == torch.int64 and out.dtype == torch.int32
     rows, vocab = logits.shape
     if vocab >= 4096 and rows > 0:
-        # a row's vocabulary shared by several blocks; rows with top-p take the one-block kernel
-        blocks = min(64, -(-vocab // 2048))
+        # a row's vocabulary shared by several blocks; rows with top-p take four more passes
+        blocks = min(64, -(-vocab // 2048), max(8, SAMPLE_BLOCKS // rows))
         partial = torch.empty((rows, blocks, 2), dtype=torch.float32, device=logits.device)
-        nucleus = 1 if any_nucleus is None else int(any_nucleus)
+        scratch = None
+        if any_nucleus is None or any_nucleus:
+            size = lib().tllm_sample_nucleus_scratch_bytes(rows)
+            scratch = torch.empty(size // 8, dtype=torch.int64, device=logits.device)
         _check(lib().tllm_sample_split(_p(logits), rows, vocab, logits.stride(0), _p(params), _p(seeds),
-                                       _p(out), _p(partial), blocks, nucleus, _stream()), "sample",
-               kernels=2 + nucleus)
+                                       _p(out), _p(partial), blocks, _p(scratch), _stream()), "sample",
+               kernels=2 if scratch is None else 7)
         return out
     _check(lib().tllm_sample(_p(logits), rows, vocab, logits.stride(0), _p(params), _p(seeds),
                              _p(out), _stream()), "sample")
