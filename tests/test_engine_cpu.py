@@ -64,3 +64,35 @@ def test_prefix_cache_changes_no_token(tmp_path, cpu_ops):
         assert llm.cache.free_pages() == {None: 24}
         # stem[:37] shares 2 pages, stem[:32] one (its last page is computed), stem + 3 two
         assert llm.engine.counters.prefix_cached_tokens == (16 * (2 + 1 + 2) if on else 0)
+
+
+@pytest.mark.parametrize("blocks,budget", [(32, 64), (6, 8)])
+def test_overlapped_scheduling_changes_no_token(tmp_path, cpu_ops, blocks, budget):
+    """With the next step scheduled and laid out while the present one runs, requests that
+    end on an end-of-sequence token have a row in a step made before that was known: the
+    tokens, the finished requests and the pages given back are the same as without."""
+    from tiny_llm_infer_b200 import LLM, SamplingParams
+    folder = make_folder(TINIES["A"], tmp_path / "m")
+    prompts = [prompt(i, n, 256) for i, n in enumerate((5, 17, 33, 9, 21))]
+    params = [SamplingParams(max_tokens=14, temperature=0.9, seed=11 + i) for i in range(5)]
+
+    def run(overlap, eos):
+        llm = LLM(str(folder), dtype="float32", max_model_len=64, num_kv_blocks=blocks, block_size=16,
+                  max_num_batched_tokens=budget, max_num_seqs=3, device="cpu", overlap_scheduling=overlap)
+        llm.engine.eos = frozenset(eos)
+        outs = [o.token_ids for o in llm.generate(prompts, params)]
+        llm.cache.audit()
+        assert llm.cache.free_pages() == {None: blocks} and llm.cache.free_slots == 3
+        assert llm.engine._ahead is None and llm.engine.is_finished()
+        return outs, llm.engine.counters
+
+    free_run, _ = run(False, ())
+    # tokens that end some requests early: the third token of one, the last-but-one of another
+    eos = {free_run[0][2], free_run[3][12]}
+    plain_outs, plain_counters = run(False, eos)
+    ahead_outs, ahead_counters = run(True, eos)
+    assert any(len(o) < 14 for o in plain_outs)
+    for o, full in zip(plain_outs, free_run):
+        assert o == full[:len(o)] and (len(o) == 14 or o[-1] in eos)
+    assert ahead_outs == plain_outs
+    assert ahead_counters.generated_tokens == plain_counters.generated_tokens == sum(map(len, plain_outs))

@@ -161,3 +161,43 @@ def test_prefix_cache_starts_a_prompt_behind_what_is_shared():
     plan, done = step()
     assert shape(plan) == [(2, 20, 1, False)] and [d.id for d in done] == [2]
     assert cache.free_pages() == {None: 16} and cache.prefix_hit_pages == 3
+
+
+def test_a_plan_made_ahead_of_the_tokens():
+    """advance() at the launch of a step, the next plan made before its tokens are known,
+    resolve() when they are: lengths count the PENDING token, a request at its max_tokens
+    is out of the next plan and its pages are free for it, and one that ends on an
+    end-of-sequence token keeps what the next plan holds for it until that plan is launched."""
+    from tiny_llm_infer_b200.engine.scheduler import PENDING
+    sched, cache = make(pages=8, budget=32, page=8)
+    a = Sequence(1, list(range(5)), SamplingParams(max_tokens=2, ignore_eos=True))
+    b = Sequence(2, list(range(7)), SamplingParams(max_tokens=50))
+    sched.add(a)
+    sched.add(b)
+
+    def launch(plan):
+        for item in plan.sequences:
+            cache.reserve(item.sequence.id, item.token_start + item.token_count)
+            cache.commit(item.sequence.id, item.token_start + item.token_count)
+        sched.advance(plan)
+
+    first = sched.schedule()
+    launch(first)
+    assert a.tokens[-1] == PENDING and a.pending and len(a) == 6 and a.num_cached_tokens == 5
+    second = sched.schedule()                        # made while `first` runs
+    assert shape(second) == [(1, 5, 1, False), (2, 7, 1, False)]
+    assert sched.resolve(first, [11, 12], lambda t: t == 99, held={1, 2}) == []
+    assert a.tokens[-1] == 11 and b.tokens[-1] == 12 and not a.pending
+    launch(second)                                   # a reaches max_tokens: over, pages back at once
+    assert a.status is Status.FINISHED and not cache.has(1) and cache.has(2)
+    third = sched.schedule()
+    assert shape(third) == [(2, 8, 1, False)]
+    done = sched.resolve(second, [13, 99], lambda t: t == 99, held={2})
+    assert [s.id for s in done] == [1, 2] and a.completion == [11, 13] and b.completion == [12, 99]
+    assert b.status is Status.FINISHED and cache.has(2)          # the third plan still holds it
+    assert sched.is_finished()
+    launch(third)                                    # its row runs for nothing; pages back now
+    assert not cache.has(2) and len(b) == 9 and not b.pending
+    assert sched.resolve(third, [5], lambda t: False) == []
+    cache.audit()
+    assert cache.free_pages() == {None: 8}

@@ -51,6 +51,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-prefix-caching", action="store_true",
                     help="compute every prompt in full (the reference always shares hashed pages)")
+    ap.add_argument("--no-overlap-scheduling", action="store_true",
+                    help="schedule a step only after the one before it has finished on the GPU")
     ap.add_argument("--num-seqs", type=int, default=8)
     ap.add_argument("--min-input-len", type=int, default=64)
     ap.add_argument("--max-input-len", type=int, default=128)
@@ -119,7 +121,8 @@ def main(argv=None) -> int:
                   block_size=16, max_num_batched_tokens=min(max_seq_len, 256),
                   max_num_seqs=min(16, len(prompts)),
                   gpu_memory_utilization=args.gpu_memory_utilization or 0.9, device=device,
-                  tokenizer=args.tokenizer, enable_prefix_caching=not args.no_prefix_caching)
+                  tokenizer=args.tokenizer, enable_prefix_caching=not args.no_prefix_caching,
+                  overlap_scheduling=not args.no_overlap_scheduling)
         params = SamplingParams(max_tokens=args.max_new_tokens, temperature=args.temperature,
                                 top_p=args.top_p, seed=args.seed)
         for result in llm.generate(prompts, params):
@@ -134,7 +137,8 @@ def main(argv=None) -> int:
     llm = LLM(args.model, dtype=args.dtype, max_model_len=max_seq_len, num_kv_blocks=args.num_kv_blocks,
               block_size=16, max_num_batched_tokens=min(max_seq_len, 256), max_num_seqs=min(16, args.num_seqs),
               gpu_memory_utilization=args.gpu_memory_utilization or 0.7, device=device,
-              enable_prefix_caching=not args.no_prefix_caching)
+              enable_prefix_caching=not args.no_prefix_caching,
+              overlap_scheduling=not args.no_overlap_scheduling)
     vocab = llm.runner.vocab
     import torch
 

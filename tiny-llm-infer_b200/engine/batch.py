@@ -21,6 +21,9 @@ class StepEntry:
     request: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = ()
+    # index among ``tokens`` of one token that is not known yet when the step is prepared (the
+    # token a step still running will sample); its value is given when the step is run
+    late: Optional[int] = None
 
 
 @dataclass

@@ -19,7 +19,7 @@ from ..cache.manager import CacheManager
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler, draw_key
 from .batch import StepEntry
-from .runner import DTYPES, ModelRunner, load_model
+from .runner import DTYPES, ModelRunner, PreparedStep, load_model
 from .scheduler import BatchPlan, Scheduler, SchedulerConfig, Sequence, Status
 
 
@@ -49,9 +49,17 @@ class EngineCounters:
     prefix_cached_tokens: int = 0      # prompt tokens found in the cache instead of computed
 
 
+@dataclass
+class _PreparedPlan:
+    plan: BatchPlan
+    step: PreparedStep
+    rows: List[tuple]          # (temperature, top_p, draw key) per sampled row
+    row_of: List[int]          # the plan's sequence of each sampled row
+
+
 class LLMEngine:
     def __init__(self, runner: ModelRunner, config: EngineConfig, eos_token_ids: Seq[int] = (),
-                 detokenize=None):
+                 detokenize=None, overlap: bool = True):
         if config.max_model_len <= 0:
             raise ValueError("max_model_len must be positive")
         config.scheduler.validate()
@@ -63,6 +71,9 @@ class LLMEngine:
         self.counters = EngineCounters()
         self._next_id = 1
         self._lock = threading.Lock()      # add_request may come from another thread
+        self.overlap = overlap
+        self._ahead: Optional[_PreparedPlan] = None      # the next step, laid out while this one ran
+        self._deferred: Optional[Exception] = None
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt_tokens: Seq[int], sampling: Optional[SamplingParams] = None) -> int:
@@ -89,39 +100,87 @@ class LLMEngine:
 
     def is_finished(self) -> bool:
         with self._lock:
-            return self.scheduler.is_finished()
+            done = self.scheduler.is_finished()
+        if done and self._ahead is not None:       # made ahead for requests that have ended since
+            self._discard(self._ahead)
+            self._ahead = None
+        return done
 
     @property
     def total_generated_tokens(self) -> int:
         return self.counters.generated_tokens
 
     # ------------------------------------------------------------------ one step
-    def step(self) -> List[GenerationResult]:
+    def _prepare(self) -> Optional["_PreparedPlan"]:
+        """Ask the scheduler for a plan, flatten it and let the runner lay it out.  A request
+        whose last token is still being sampled brings it as a late token."""
         with self._lock:
             plan = self.scheduler.schedule()
         if not plan.sequences:
-            return []
+            return None
         entries, rows, row_of = [], [], []
         for item in plan.sequences:
             seq = item.sequence
-            toks = seq.tokens[item.token_start:item.token_start + item.token_count]
+            end = item.token_start + item.token_count
+            late = item.token_count - 1 if seq.pending and end == len(seq) else None
             want = [item.token_count - 1] if item.samples else []
-            entries.append(StepEntry(seq.id, toks, want))
+            entries.append(StepEntry(seq.id, seq.tokens[item.token_start:end], want, late))
             if item.samples:
                 rows.append((seq.sampling.temperature, seq.sampling.top_p,
                              draw_key(seq.seed, seq.num_completion_tokens)))
                 row_of.append(len(entries) - 1)
-        logits = self.runner.step(entries)
-        tokens = self.sampler.sample(logits, rows)
+        return _PreparedPlan(plan, self.runner.prepare(entries), rows, row_of)
+
+    def _discard(self, ahead: "_PreparedPlan") -> None:
+        """A plan made ahead that is not going to run: every request in it has ended."""
+        self.runner.abandon(ahead.step)
+        with self._lock:
+            for item in ahead.plan.sequences:
+                if self.runner.cache.has(item.sequence.id):
+                    self.runner.cache.release(item.sequence.id)
+
+    def step(self) -> List[GenerationResult]:
+        """One step: launch it, and while the GPU runs it, schedule and lay out the next
+        (``overlap``), whose only open values are the tokens this step samples; then read
+        the tokens and book them."""
+        if self._deferred is not None:
+            error, self._deferred = self._deferred, None
+            raise error
+        current, self._ahead = self._ahead, None
+        if current is not None and all(i.sequence.status is Status.FINISHED for i in current.plan.sequences):
+            self._discard(current)
+            current = None
+        if current is None:
+            current = self._prepare()
+            if current is None:
+                return []
+        plan = current.plan
+        late = []
+        for index, _ in current.step.late:
+            item = plan.sequences[index]
+            late.append(item.sequence.tokens[item.token_start + current.step.entries[index].late])
+        logits = self.runner.run(current.step, late)
+        self.sampler.launch(logits, current.rows)
+        with self._lock:
+            self.scheduler.advance(plan)
+        if self.overlap:
+            try:
+                self._ahead = self._prepare()
+            except Exception as error:             # belongs to the next step: raised when it is asked for
+                self._deferred = error
+        tokens = self.sampler.fetch()
         self.runner.check_kernels()
         sampled = [-1] * len(plan.sequences)
-        for idx, tok in zip(row_of, tokens):
+        generated = 0
+        for idx, tok in zip(current.row_of, tokens):
             sampled[idx] = tok
+            generated += plan.sequences[idx].sequence.pending
+        held = () if self._ahead is None else {i.sequence.id for i in self._ahead.plan.sequences}
         with self._lock:
-            finished = self.scheduler.postprocess(plan, sampled, lambda t: t in self.eos)
+            finished = self.scheduler.resolve(plan, sampled, lambda t: t in self.eos, held)
         c = self.counters
         c.steps += 1
-        c.generated_tokens += len(tokens)
+        c.generated_tokens += generated
         c.preemptions = self.scheduler.num_preemptions
         cache = self.runner.cache
         c.prefix_cached_tokens = cache.prefix_hit_pages * cache.page_size
@@ -192,13 +251,15 @@ class LLM:
     ``max_num_seqs`` 16.  ``enable_prefix_caching`` (on, as in the reference, whose block
     manager always shares hashed pages): prompts that begin like an earlier one reuse its
     full pages; it stays off by itself for models with windows or per-request state.
+    ``overlap_scheduling`` (on): the host schedules and lays out a step while the GPU runs
+    the one before it; the tokens are the same either way.
     """
 
     def __init__(self, model: str, dtype: str = "bfloat16", max_model_len: int = 2048,
                  num_kv_blocks: int = 0, block_size: int = 16, max_num_batched_tokens: Optional[int] = None,
                  max_num_seqs: int = 16, gpu_memory_utilization: float = 0.9, device: str = "cuda:0",
                  tokenizer: Optional[str] = None, loaded=None, use_cuda_graphs: bool = True,
-                 enable_prefix_caching: bool = True):
+                 enable_prefix_caching: bool = True, overlap_scheduling: bool = True):
         if device.startswith("cuda") and not torch.cuda.is_available():
             raise RuntimeError("no CUDA device; this engine has no CPU path")
         torch_dtype = DTYPES[dtype] if isinstance(dtype, str) else dtype
@@ -225,7 +286,8 @@ class LLM:
         cfg = EngineConfig(SchedulerConfig(max_num_seqs, max_num_batched_tokens, block_size, num_kv_blocks),
                            max_model_len)
         self.engine = LLMEngine(self.runner, cfg, eos,
-                                (lambda ids: self.tokenizer.decode(ids)) if self.tokenizer else None)
+                                (lambda ids: self.tokenizer.decode(ids)) if self.tokenizer else None,
+                                overlap=overlap_scheduling)
 
     def encode(self, text: str) -> List[int]:
         if self.tokenizer is None:

@@ -11,6 +11,7 @@ Reference counterpart: ``Qwen3Model::forward_paged_batch`` and the adapter in fr
 from __future__ import annotations
 
 import contextlib
+from dataclasses import dataclass
 
 from pathlib import Path
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
@@ -73,6 +74,20 @@ def random_model(config: ModelConfig, seed: int, dtype: torch.dtype, device, std
     return model
 
 
+@dataclass
+class PreparedStep:
+    """A step whose pages are reserved and whose rows lie in the runner's host buffer, not yet
+    uploaded or launched.  ``late`` lists (entry, place in the host buffer) of tokens that are
+    given only when it runs."""
+    entries: Sequence[StepEntry]
+    commits: List[Tuple[Hashable, int, Sequence[int]]]
+    upload: int                                   # int32 words of the host buffer to send
+    late: List[Tuple[int, int]]
+    ctx: Optional[StepContext] = None             # the general path's context
+    graph_key: Optional[Tuple[int, int]] = None   # (rows bucket, context bucket) of a one-token step
+    wanted: Optional[List[int]] = None            # rows wanted of a one-token step
+
+
 class ModelRunner:
     def __init__(self, model: Model, cache: CacheManager, max_batch_tokens: int = 8192,
                  use_graphs: bool = True):
@@ -104,6 +119,7 @@ class ModelRunner:
             self._host = self._host.pin_memory()
         self._dev = torch.empty(12 * n + 64, dtype=torch.int32, device=self.device)
         self._uploaded: Optional[torch.cuda.Event] = None
+        self._prepared: Optional[PreparedStep] = None      # the host buffer holds this step
 
     def check_kernels(self) -> None:
         """Raise if a kernel with bounded waits gave up since the last check (reads a device
@@ -118,11 +134,10 @@ class ModelRunner:
             self.cache.release(request)
 
     # ------------------------------------------------------------------ the step
-    def build_context(self, entries: Sequence[StepEntry]) -> Tuple[StepContext, List[Tuple[Hashable, int, Sequence[int]]]]:
-        """Reserve pages, lay the rows out, upload them.  Returns the context and, per
-        entry, (request, length after this step, its tokens) to commit once the step has run."""
-        if not entries:
-            raise StepError("a step needs at least one entry")
+    def _prepare_general(self, entries: Sequence[StepEntry]) -> PreparedStep:
+        """Reserve pages and lay the rows out in the host buffer.  The prepared step holds the
+        context and, per entry, (request, length after this step, its tokens) to commit once
+        the step has run."""
         seen = set()
         total = wanted = 0
         for e in entries:
@@ -145,11 +160,17 @@ class ModelRunner:
             self._uploaded.synchronize()
         segments: List[Segment] = []
         commits: List[Tuple[Hashable, int, Sequence[int]]] = []
+        late: List[Tuple[int, int]] = []
         row = n_want = max_ctx = max_seg = 0
-        for e in entries:
+        for index, e in enumerate(entries):
             if not self.cache.has(e.request):
                 self.cache.admit(e.request)
-            toks = np.asarray(e.tokens, dtype=np.int64)
+            toks = np.array(e.tokens, dtype=np.int64)
+            if e.late is not None:
+                if not 0 <= e.late < len(toks):
+                    raise StepError(f"request {e.request!r}: late token {e.late} outside its {len(toks)} tokens")
+                toks[e.late] = 0
+                late.append((index, o_ids + row + e.late))
             if toks.min() < 0 or toks.max() >= self.vocab:
                 raise StepError(f"request {e.request!r}: token id outside [0, {self.vocab})")
             n = len(toks)
@@ -187,13 +208,6 @@ class ModelRunner:
         for i, (s, off, _) in enumerate(tiles):
             host[o_tiles + 2 * i], host[o_tiles + 2 * i + 1] = s, off
         self.cache.sync()
-        if self.is_cuda:
-            self._dev[:used].copy_(self._host[:used], non_blocking=True)
-            if self._uploaded is None:
-                self._uploaded = torch.cuda.Event()
-            self._uploaded.record()
-        else:
-            self._dev[:used].copy_(self._host[:used])
         d = self._dev
         ctx = StepContext(
             tokens=row, token_ids=d[o_ids:o_ids + row], positions=d[o_pos:o_pos + row],
@@ -202,24 +216,70 @@ class ModelRunner:
             dec_rows=None if n_dec == row else d[o_dec:o_tiles], n_dec=n_dec,
             pf_tiles=d[o_tiles:used].view(-1, 2), n_tiles=n_tiles, n_tiles128=n_tiles128, n_tiles256=n_tiles256,
             decode_only=(max_seg == 1), max_context=max_ctx, max_segment=max_seg)
-        return ctx, commits
+        return PreparedStep(entries, commits, used, late, ctx=ctx)
 
-    @torch.no_grad()
+    def _upload(self, words: int) -> None:
+        if self.is_cuda:
+            self._dev[:words].copy_(self._host[:words], non_blocking=True)
+            if self._uploaded is None:
+                self._uploaded = torch.cuda.Event()
+            self._uploaded.record()
+        else:
+            self._dev[:words].copy_(self._host[:words])
+
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Run one batch; logits [wanted, vocab] float32 on the device, in the order of
         the entries and of their ``want`` lists.  The tensor may be reused by the next
         step: read it (or sample from it) before stepping again."""
+        return self.run(self.prepare(entries))
+
+    def prepare(self, entries: Sequence[StepEntry]) -> PreparedStep:
+        """The host's share of a step, which may be done while the step before it still runs on
+        the GPU: checks, pages, the layout of rows, the block tables.  A token marked ``late``
+        in its entry is left open.  One prepared step at a time: ``run`` it before the next."""
+        if self._prepared is not None:
+            raise StepError("a prepared step has not been run yet")
+        if not entries:
+            raise StepError("a step needs at least one entry")
         if self.use_graphs and self._graphable(entries):
-            return self._step_graph(entries)
-        ctx, commits = self.build_context(entries)
-        signature = self._prompt_signature(ctx)
-        if signature is None:
-            logits = self.model.forward(ctx, self.cache)
+            prepared = self._prepare_graph(entries)
         else:
-            logits = self._step_prompt_graph(signature, ctx)
-        for request, length, tokens in commits:
+            prepared = self._prepare_general(entries)
+        self._prepared = prepared
+        return prepared
+
+    @torch.no_grad()
+    def run(self, prepared: PreparedStep, late_tokens: Sequence[int] = ()) -> torch.Tensor:
+        """Upload and launch a prepared step; ``late_tokens`` in the order of ``prepared.late``."""
+        if prepared is not self._prepared:
+            raise StepError("run() takes the step that prepare() returned last")
+        if len(late_tokens) != len(prepared.late):
+            raise StepError(f"{len(prepared.late)} late tokens are open, {len(late_tokens)} were given")
+        host = self._host.numpy()
+        for (index, place), token in zip(prepared.late, late_tokens):
+            e = prepared.entries[index]
+            if not 0 <= int(token) < self.vocab:
+                raise StepError(f"request {e.request!r}: token id outside [0, {self.vocab})")
+            host[place] = int(token)
+            e.tokens[e.late] = int(token)          # what commit() hashes
+        self._prepared = None
+        self._upload(prepared.upload)
+        if prepared.graph_key is not None:
+            logits = self._run_graph(prepared)
+        else:
+            signature = self._prompt_signature(prepared.ctx)
+            if signature is None:
+                logits = self.model.forward(prepared.ctx, self.cache)
+            else:
+                logits = self._step_prompt_graph(signature, prepared.ctx)
+        for request, length, tokens in prepared.commits:
             self.cache.commit(request, length, tokens)
         return logits
+
+    def abandon(self, prepared: PreparedStep) -> None:
+        """Drop a prepared step without running it (pages it reserved stay with their requests)."""
+        if prepared is self._prepared:
+            self._prepared = None
 
     # ------------------------------------------------------------------ repeated prompt steps as CUDA graphs
     # A step with prompt portions launches fewer, longer kernels, and the host is far ahead of
@@ -296,7 +356,7 @@ class ModelRunner:
                 and all(len(e.tokens) == 1 for e in entries)
                 and self._graph_safe)
 
-    def _step_graph(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def _prepare_graph(self, entries: Sequence[StepEntry]) -> PreparedStep:
         rows = len(entries)
         bucket = 1
         while bucket < rows:
@@ -310,12 +370,18 @@ class ModelRunner:
         host[bucket:2 * bucket] = 0
         host[2 * bucket:3 * bucket] = -1
         host[3 * bucket:4 * bucket] = np.arange(bucket)
-        commits, wanted, max_ctx = [], [], 0
+        commits, wanted, late, max_ctx = [], [], [], 0
         for i, e in enumerate(entries):
             if e.request in seen:
                 raise StepError(f"request {e.request!r} appears twice in one step")
             seen.add(e.request)
-            tok = int(e.tokens[0])
+            if e.late is not None:
+                if e.late != 0:
+                    raise StepError(f"request {e.request!r}: late token {e.late} outside its 1 token")
+                tok = 0
+                late.append((i, i))
+            else:
+                tok = int(e.tokens[0])
             if not 0 <= tok < self.vocab:
                 raise StepError(f"request {e.request!r}: token id outside [0, {self.vocab})")
             if not self.cache.has(e.request):
@@ -333,19 +399,16 @@ class ModelRunner:
         while ctx_bucket < max_ctx:
             ctx_bucket *= 2
         self.cache.sync()
-        self._dev[:4 * bucket].copy_(self._host[:4 * bucket], non_blocking=True)
-        if self._uploaded is None:
-            self._uploaded = torch.cuda.Event()
-        self._uploaded.record()
-        key = (bucket, ctx_bucket)
+        return PreparedStep(entries, commits, 4 * bucket, late, graph_key=(bucket, ctx_bucket), wanted=wanted)
+
+    def _run_graph(self, prepared: PreparedStep) -> torch.Tensor:
+        key, rows, wanted = prepared.graph_key, len(prepared.entries), prepared.wanted
         if key not in self._graphs:
             self._capture(key)
         graph, kernels = self._graphs[key]
         graph.replay()
         ops.launches += kernels                      # the replay launches what the capture recorded
         logits = self._graph_logits
-        for request, length, tokens in commits:
-            self.cache.commit(request, length, tokens)
         if wanted == list(range(rows)):
             return logits[:rows]
         if not wanted:

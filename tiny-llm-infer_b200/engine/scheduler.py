@@ -38,6 +38,11 @@ class SchedulerError(RuntimeError):
     pass
 
 
+# Stands in a request's tokens for the one that a launched step will sample: its place is
+# known (lengths, pages and the next step's layout depend on it), its value is not yet.
+PENDING = -1
+
+
 class Status(enum.Enum):
     WAITING = "waiting"
     RUNNING = "running"
@@ -72,6 +77,7 @@ class Sequence:
         self.num_cached_tokens = 0
         self.num_scheduled_tokens = 0
         self.preemptions = 0
+        self.pending = False          # the last of ``tokens`` is PENDING
 
     def __len__(self) -> int:
         return len(self.tokens)
@@ -198,21 +204,61 @@ class Scheduler:
         sampled nothing).  Returns the requests that finished."""
         if len(sampled) != len(plan.sequences):
             raise SchedulerError("The model runner returned the wrong number of sampled tokens.")
-        finished = []
-        for item, token in zip(plan.sequences, sampled):
+        self.advance(plan)
+        return self.resolve(plan, sampled, is_eos)
+
+    # The booking in two halves, so that the next step can be scheduled and laid out while this
+    # one still runs: what a step changes is known when it is launched, but for the values of
+    # the tokens it samples and whether one of them ends its request.
+
+    def advance(self, plan: BatchPlan) -> None:
+        """The step has been launched: its tokens count as computed, every request that
+        samples grows by a PENDING token, and one that reaches its ``max_tokens`` with it is
+        over (its pages are free for the next plan; work already launched comes before
+        anything later on the stream).  A request that ended after this plan was made (see
+        ``resolve``) gives back here what the plan held for it."""
+        for item in plan.sequences:
             seq = item.sequence
+            if seq.status is Status.FINISHED:
+                if self.cache.has(seq.id):
+                    self.cache.release(seq.id)
+                continue
             seq.num_cached_tokens += seq.num_scheduled_tokens
             seq.num_scheduled_tokens = 0
-            if item.is_prefill and seq.num_cached_tokens < len(seq):
+            if not item.samples:
                 continue
-            if token < 0:
-                raise SchedulerError("The model runner did not return a token for a completed step.")
-            seq.tokens.append(int(token))
-            stop = (not seq.sampling.ignore_eos and is_eos(int(token))) \
-                or seq.num_completion_tokens >= seq.sampling.max_tokens
-            if stop:
+            seq.tokens.append(PENDING)
+            seq.pending = True
+            if seq.num_completion_tokens >= seq.sampling.max_tokens:
                 seq.status = Status.FINISHED
                 self.cache.release(seq.id)
                 self.running.remove(seq)
+
+    def resolve(self, plan: BatchPlan, sampled: Seq[int], is_eos: Callable[[int], bool],
+                held: Seq[Hashable] = ()) -> List[Sequence]:
+        """The step's tokens are here: ``sampled[i]`` is the token of ``plan.sequences[i]``
+        (ignored where it sampled nothing).  Returns the requests that finished.  A request
+        that ends on an end-of-sequence token may already stand in a plan made meanwhile
+        (its id in ``held``): then it keeps its pages until that plan is launched, where its
+        row runs for nothing and ``advance`` frees them."""
+        if len(sampled) != len(plan.sequences):
+            raise SchedulerError("The model runner returned the wrong number of sampled tokens.")
+        finished = []
+        for item, token in zip(plan.sequences, sampled):
+            seq = item.sequence
+            if not (item.samples and seq.pending):
+                continue
+            if token < 0:
+                raise SchedulerError("The model runner did not return a token for a completed step.")
+            seq.tokens[-1] = int(token)
+            seq.pending = False
+            if seq.status is Status.FINISHED:          # by its length, in advance()
+                finished.append(seq)
+            elif not seq.sampling.ignore_eos and is_eos(int(token)):
+                # RUNNING, or WAITING again if the plan made meanwhile preempted it
+                (self.running if seq.status is Status.RUNNING else self.waiting).remove(seq)
+                seq.status = Status.FINISHED
+                if seq.id not in held and self.cache.has(seq.id):
+                    self.cache.release(seq.id)
                 finished.append(seq)
         return finished

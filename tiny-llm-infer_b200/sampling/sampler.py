@@ -47,13 +47,26 @@ class Sampler:
         self._params = torch.empty((max_rows, 2), dtype=torch.float32, device=device)
         self._seeds = torch.empty(max_rows, dtype=torch.int64, device=device)
         self._out = torch.empty(max_rows, dtype=torch.int32, device=device)
+        self._out_host = torch.empty(max_rows, dtype=torch.int32)
+        self._done = None
+        if cuda:
+            self._out_host = self._out_host.pin_memory()
+            self._done = torch.cuda.Event()
+        self._launched = 0
 
     def sample(self, logits: torch.Tensor, rows: Sequence[Tuple[float, float, int]]) -> List[int]:
         """``rows[i]`` = (temperature, top_p, draw key) for ``logits[i]``; token ids on the host."""
+        self.launch(logits, rows)
+        return self.fetch()
+
+    def launch(self, logits: torch.Tensor, rows: Sequence[Tuple[float, float, int]]) -> None:
+        """Start the draw and the copy of its result to the host; ``fetch`` waits for it.  The
+        host is free in between (the engine prepares its next step there)."""
         n = len(rows)
         assert logits.shape[0] == n
+        self._launched = n
         if n == 0:
-            return []
+            return
         temps = [r[0] for r in rows]
         top_ps = [r[1] for r in rows]
         self._params_np[:n, 0] = temps
@@ -63,4 +76,17 @@ class Sampler:
         self._seeds[:n].copy_(self._seeds_host[:n], non_blocking=True)
         nucleus = any(t > 1e-6 and p < 1.0 for t, p in zip(temps, top_ps))
         ops.sample(logits, self._params[:n], self._seeds[:n], self._out[:n], any_nucleus=nucleus)
-        return self._out[:n].cpu().tolist()
+        if self._done is None:
+            self._out_host = self._out.cpu()           # no stream to wait for
+        else:
+            self._out_host[:n].copy_(self._out[:n], non_blocking=True)
+            self._done.record()
+
+    def fetch(self) -> List[int]:
+        """Token ids of the draw that ``launch`` started."""
+        n = self._launched
+        if n == 0:
+            return []
+        if self._done is not None:
+            self._done.synchronize()
+        return self._out_host[:n].tolist()
