@@ -99,6 +99,34 @@ def test_long_prompts_head_width_128(folders, budget):
         assert ok, info
 
 
+def test_short_portions_of_a_long_prompt_share_out_their_keys(tmp_path, monkeypatch):
+    """A prompt of 1500 tokens under a budget of 128: a step then has three blocks of query rows
+    and up to 24 tiles of keys, so the full-attention layer cuts every block's keys into runs
+    for several blocks and combines them (the windowed layer never sees enough keys).  The steps
+    repeat their layout and are replayed as graphs, the context bucket deciding the number of
+    runs.  Generated tokens against the plain implementation on the same prefix."""
+    import dataclasses
+    from tiny_llm_infer_b200 import LLM, SamplingParams, ops
+    tiny = dict(TINIES["E"])
+    tiny["cfg"] = dataclasses.replace(tiny["cfg"], max_position_embeddings=2048)
+    folder = make_folder(tiny, tmp_path / "long")
+    cfg, w = plain.read_model(folder)
+    seen = []
+    inner = ops.paged_attention_prefill_tcgen05
+
+    def spy(*args, **kwargs):
+        seen.append(args[13] if len(args) > 13 else kwargs.get("splits", 1))
+        return inner(*args, **kwargs)
+    monkeypatch.setattr(ops, "paged_attention_prefill_tcgen05", spy)
+    p = prompt(77, 1500, cfg["vocab_size"])
+    llm = LLM(str(folder), dtype="bfloat16", max_model_len=1600, num_kv_blocks=60, block_size=tiny["page_size"],
+              max_num_batched_tokens=128, max_num_seqs=2)
+    out = llm.generate([p], SamplingParams(max_tokens=12, ignore_eos=True))[0]
+    assert 2 in seen and 1 in seen, sorted(set(seen))
+    ok, info = teacher_forced_ok(cfg, w, p, out.token_ids, 0.08)
+    assert ok, info
+
+
 def test_prefix_cache_on_the_gpu(folders):
     """Shared beginnings: the pages of an earlier prompt are read instead of computed again, by
     live requests and after the earlier one has ended; float32 tokens equal the plain

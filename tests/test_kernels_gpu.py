@@ -431,16 +431,20 @@ def test_prefill_kernel_segments(ops, nh, nkv, hd, ps, window):
         assert err < tol(torch.bfloat16, want.abs().max().item()), (s, p0, n, err)
 
 
+@pytest.mark.parametrize("splits", [1, 2, 3, 16])
 @pytest.mark.parametrize("nh,nkv,ps,window", [(8, 2, 16, None), (3, 3, 32, None), (6, 1, 16, 70), (2, 1, 64, 9),
                                               (4, 2, 48, 200), (5, 1, 16, None), (3, 1, 32, 130)])
-def test_prefill_tcgen05_kernel_segments(ops, nh, nkv, ps, window):
+def test_prefill_tcgen05_kernel_segments(ops, nh, nkv, ps, window, splits):
     """The tcgen05 kernel (head width 128; a thread block takes two heads at 128 positions where
     the group is even, else 256 positions of one head) on segments that start inside a
     request, are shorter and longer than a block, start and end off the edges of key tiles
     and pages; each row's query points at one key (the window's first, the row's own, the
     last of the tile before, the one before its own), so that a key that is missed, masked
     wrongly or read from the wrong page changes the result; every other four rows have no such
-    key, so that a tile whose share is lost or counted twice shows as well."""
+    key, so that a tile whose share is lost or counted twice shows as well.  With ``splits``
+    every block's key tiles go to that many blocks in equal runs (16: more runs than most blocks
+    have tiles, so some are empty, and with 256-row blocks the earlier 128 rows have no key in
+    the later runs) and a second kernel combines them."""
     hd = 128
     lens = [600, 128, 259, 5]
     max_pages = -(-600 // ps) + 1
@@ -470,7 +474,7 @@ def test_prefill_tcgen05_kernel_segments(ops, nh, nkv, ps, window):
     ops.paged_attention_prefill_tcgen05(dev(q.reshape(T, -1).to(torch.bfloat16)), cache,
                                         dev(torch.tensor(seg_info, dtype=torch.int32)),
                                         dev(torch.tensor(tiles, dtype=torch.int32)), len(tiles), dev(table), ps,
-                                        nh, nkv, hd, window, 1 / math.sqrt(hd), out)
+                                        nh, nkv, hd, window, 1 / math.sqrt(hd), out, splits)
     ops.check_error_word(torch.device("cuda"))
     got = out.cpu().double().view(T, nh, hd)
     for (s, r0, n, p0) in seg_info:
@@ -480,8 +484,15 @@ def test_prefill_tcgen05_kernel_segments(ops, nh, nkv, ps, window):
         assert err < tol(torch.bfloat16, want.abs().max().item()), (s, p0, n, err)
 
 
+def test_prefill_splits_rule(ops):
+    assert ops.prefill_splits(32, 256) == 1 and ops.prefill_splits(32, 1024) == 2
+    assert ops.prefill_splits(32, 4096) == 4 and ops.prefill_splits(16, 8192) == 8
+    assert ops.prefill_splits(64, 4096) == 2 and ops.prefill_splits(128, 65536) == 1
+
+
+@pytest.mark.parametrize("splits", [1, 4])
 @pytest.mark.parametrize("nh,nkv,window", [(4, 2, None), (3, 1, None), (2, 1, 1000)])
-def test_prefill_tcgen05_long_request(ops, nh, nkv, window):
+def test_prefill_tcgen05_long_request(ops, nh, nkv, window, splits):
     """One portion of 3000 tokens behind 1100 that are already in the cache: some 65 key tiles per
     block, so the rings of key and value tiles, the S buffers and every barrier's parity wrap
     many times.  Checked against float64 attention on sampled rows of every block."""
@@ -497,7 +508,7 @@ def test_prefill_tcgen05_long_request(ops, nh, nkv, window):
     out = torch.zeros_like(q)
     ops.paged_attention_prefill_tcgen05(q, cache, dev(torch.tensor([[0, 0, new, have]], dtype=torch.int32)),
                                         dev(tiles), len(tiles), dev(table), ps, nh, nkv, hd, window,
-                                        1 / math.sqrt(hd), out)
+                                        1 / math.sqrt(hd), out, splits)
     ops.check_error_word(torch.device("cuda"))
     # keys and values of the request in position order, float64
     kv = cache[table[0].long().cuda()].double()                       # [pages, 2, nkv, ps, hd]

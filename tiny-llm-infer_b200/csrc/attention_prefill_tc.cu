@@ -37,6 +37,7 @@
 // One block per SM (224 KB of shared memory, all 512 TMEM columns).  Every mbarrier wait is
 // bounded; on a timeout the block sets the caller's error word, stops, waits (bounded) for
 // copies and MMAs in flight, frees its tensor memory and returns.
+#include <climits>
 #include <cuda.h>
 
 #include "common.cuh"
@@ -186,7 +187,8 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
                                   const int* __restrict__ seg_info, const int* __restrict__ tiles,
                                   const int* __restrict__ block_table, int max_pages, int page_size, int q_heads,
                                   int kv_heads, int window, float scale_log2e, int pair_heads,
-                                  bf16* __restrict__ out, int* __restrict__ error_word) {
+                                  bf16* __restrict__ out, int splits, float* __restrict__ part_o,
+                                  float* __restrict__ part_ml, int* __restrict__ error_word) {
     extern __shared__ __align__(1024) unsigned char smem[];
     Barriers* bars = reinterpret_cast<Barriers*>(smem + kTilesBytes);
     volatile int* aborted = &bars->abort_flag;
@@ -211,11 +213,51 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
         t.n = t.rows > 0 ? t.last_pos / kBN - t.kt_first + 1 : 0;
     }
     const int g = qt[0].head / (q_heads / kv_heads);           // both tiles read this key/value head
-    const bool two = qt[1].n > 0;
-    const int kt_lo = two ? min(qt[0].kt_first, qt[1].kt_first) : qt[0].kt_first;
-    const int kt_hi = two ? max(qt[0].kt_first + qt[0].n, qt[1].kt_first + qt[1].n) - 1 : qt[0].kt_first + qt[0].n - 1;
-    const int n_tiles = kt_hi - kt_lo + 1;
-    const int last_pos = two ? max(qt[0].last_pos, qt[1].last_pos) : qt[0].last_pos;
+    const int last_pos = max(qt[0].last_pos, qt[1].rows > 0 ? qt[1].last_pos : 0);
+    // the key tiles some query tile of the block reads: [kt_lo, kt_lo + n_tiles)
+    auto block_range = [&](int& lo, int& end) {
+        lo = INT_MAX, end = 0;
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+            if (qt[x].n > 0) {
+                lo = min(lo, qt[x].kt_first);
+                end = max(end, qt[x].kt_first + qt[x].n);
+            }
+        }
+    };
+    int kt_lo, kt_end;
+    block_range(kt_lo, kt_end);
+    if (splits > 1) {
+        // this block takes the blockIdx.z-th of `splits` equal runs of those tiles and leaves
+        // unnormalised partial results; a query tile may have nothing in the run
+        const int part = (kt_end - kt_lo + splits - 1) / splits;
+        const int a = kt_lo + (int)blockIdx.z * part, b = min(kt_end, a + part);
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+            QTile& t = qt[x];
+            if (t.n > 0) {
+                const int na = max(t.kt_first, a), nb = min(t.kt_first + t.n, b);
+                t.kt_first = na;
+                t.n = max(0, nb - na);
+            }
+        }
+        block_range(kt_lo, kt_end);
+    }
+    const int n_tiles = kt_end > kt_lo ? kt_end - kt_lo : 0;
+    // partial results of row r of query tile t: O at part_o + index * kHD, (reference maximum, sum) at part_ml + index * 2
+    auto part_index = [&](const QTile& t, int r) -> size_t {
+        return ((size_t)(start + t.q_off + r) * q_heads + t.head) * splits + blockIdx.z;
+    };
+    if (splits > 1 && warp >= 4) {                            // a tile with no key in this run says so
+        const QTile& t = qt[(warp - 4) >> 2];
+        const int r = (warp & 3) * 32 + lane;
+        if (t.n == 0 && r < t.rows) {
+            float* ml = part_ml + part_index(t, r) * 2;
+            ml[0] = -INFINITY;
+            ml[1] = 0.0f;
+        }
+    }
+    if (n_tiles == 0) return;                                 // (only with splits) nothing for either tile
 
     if (threadIdx.x == 0) {
         if (q_s & 1023) atomicExch(error_word, 9);         // operand tiles need a 1024-byte aligned window
@@ -259,7 +301,7 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
         const int x = warp == 1 ? 0 : 1;
         const QTile t = x ? qt[1] : qt[0];
         if (warp == 0 && lane == 0 && !*aborted) {           // query tiles, by TMA, once
-            mbar_expect_tx(&bars->q_full, two ? 2 * kQBytes : kQBytes);
+            mbar_expect_tx(&bars->q_full, ((qt[0].n > 0) + (qt[1].n > 0)) * kQBytes);
 #pragma unroll
             for (int y = 0; y < 2; ++y) {
                 if (qt[y].n == 0) continue;
@@ -493,7 +535,27 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
             if (x == 0) asm volatile("bar.sync 1, 128;\n" ::: "memory");
             else asm volatile("bar.sync 2, 128;\n" ::: "memory");
         }
-        if (alive && !__any_sync(0xffffffffu, *aborted != 0)) {
+        const bool finish = alive && !__any_sync(0xffffffffu, *aborted != 0);
+        if (finish && splits > 1) {
+            // ---- one of several runs of keys: O as it stands, its reference maximum and its sum
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const size_t index = part_index(t, r);
+#pragma unroll 1
+            for (int c = 0; c < kHD; c += 32) {
+                uint32_t o[32];
+                tmem_ld32(tmem_ox + c, o);
+                tmem_ld_wait();
+                if (r < t.rows) {
+                    uint4* dst = reinterpret_cast<uint4*>(part_o + index * kHD + c);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) dst[e] = make_uint4(o[4 * e], o[4 * e + 1], o[4 * e + 2], o[4 * e + 3]);
+                }
+            }
+            if (r < t.rows) {
+                part_ml[index * 2] = m_ref;
+                part_ml[index * 2 + 1] = l_run;
+            }
+        } else if (finish) {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const float inv = 1.0f / l_run;
             const uint32_t stage = q_s + x * kQBytes, stage_row = stage + r * 256;
@@ -533,6 +595,34 @@ paged_attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
+// out[row, head, :] = sum_z O_z 2^(m_z - M) / sum_z l_z 2^(m_z - M) over the runs of keys, in
+// index order; a run that held no key for the row has m = -inf and is passed over.  A block
+// takes kCombineRows rows of one entry of the tile list and one head.
+constexpr int kCombineRows = 8;
+__global__ void paged_attention_prefill_combine_kernel(const float* part_o, const float* part_ml,
+                                                       const int* __restrict__ seg_info,
+                                                       const int* __restrict__ tiles, int rows_per_tile,
+                                                       int q_heads, int splits, bf16* __restrict__ out) {
+    const int seg = tiles[2 * blockIdx.x], q_off = tiles[2 * blockIdx.x + 1], head = blockIdx.y, d = threadIdx.x;
+    const int start = seg_info[4 * seg + 1], len = seg_info[4 * seg + 2];
+    for (int i = 0; i < kCombineRows; ++i) {
+        const int r = q_off + blockIdx.z * kCombineRows + i;
+        if (r >= len || r >= q_off + rows_per_tile) return;
+        const size_t base = ((size_t)(start + r) * q_heads + head) * splits;
+        float mm = -INFINITY;
+        for (int z = 0; z < splits; ++z) mm = fmaxf(mm, part_ml[(base + z) * 2]);
+        float total = 0.0f, acc = 0.0f;
+        for (int z = 0; z < splits; ++z) {
+            const float mz = part_ml[(base + z) * 2];
+            if (mz == -INFINITY) continue;
+            const float f = exp2f(mz - mm);
+            total += part_ml[(base + z) * 2 + 1] * f;
+            acc += part_o[(base + z) * kHD + d] * f;
+        }
+        out[((size_t)(start + r) * q_heads + head) * kHD + d] = __float2bfloat16_rn(acc / total);
     }
 }
 
@@ -579,10 +669,14 @@ extern "C" int tllm_paged_attention_prefill_tc_rows(int q_heads, int kv_heads) {
 // tiles: int[n_tiles][2] = segment, offset of the block's first query row; the offsets are the
 // multiples of tllm_paged_attention_prefill_tc_rows() below the segment's length.
 // q [tokens, q_heads * 128], cache [num_pages, 2, kv_heads, page_size, 128], both bfloat16.
+// splits > 1: the keys of every block go to that many blocks in equal runs (for steps with few
+// query rows and many keys, which would leave most of the GPU idle), their partial results to
+// part_o float[tokens * q_heads * splits * 128] and part_ml float[tokens * q_heads * splits * 2],
+// and a second kernel combines them.
 extern "C" int tllm_paged_attention_prefill_tc(
     const void* q, int tokens, const void* cache, int num_pages, const int* seg_info, const int* tiles, int n_tiles,
     const int* block_table, int max_pages, int page_size, int q_heads, int kv_heads, int head_dim, int window,
-    float scale, void* out, int* error_word, cudaStream_t stream) {
+    float scale, void* out, int splits, float* part_o, float* part_ml, int* error_word, cudaStream_t stream) {
     TLLM_REQUIRE(head_dim == 128, "paged_attention_prefill_tc: head_dim %d is not 128", head_dim);
     TLLM_REQUIRE(q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0 && q_heads <= 65535,
                  "paged_attention_prefill_tc: %d query heads over %d key/value heads", q_heads, kv_heads);
@@ -590,12 +684,14 @@ extern "C" int tllm_paged_attention_prefill_tc(
                  page_size);
     TLLM_REQUIRE(error_word != nullptr && n_tiles >= 0 && n_tiles <= 65535 && tokens > 0,
                  "paged_attention_prefill_tc: bad arguments (at most 65535 blocks of query rows)");
+    TLLM_REQUIRE(splits >= 1 && splits <= 64 && (splits == 1 || (part_o != nullptr && part_ml != nullptr)),
+                 "paged_attention_prefill_tc: %d splits (1 to 64; more than one needs scratch)", splits);
     const long long kv_rows = (long long)num_pages * 2 * kv_heads * page_size;
     TLLM_REQUIRE(kv_rows < (1ll << 31), "paged_attention_prefill_tc: a cache of %lld rows exceeds the kernel's 32-bit row index",
                  kv_rows);
     if (n_tiles == 0) return 0;
     TLLM_REQUIRE((reinterpret_cast<uintptr_t>(cache) & 15u) == 0 && (reinterpret_cast<uintptr_t>(q) & 15u) == 0 &&
-                     (reinterpret_cast<uintptr_t>(out) & 15u) == 0,
+                     (reinterpret_cast<uintptr_t>(out) & 15u) == 0 && (reinterpret_cast<uintptr_t>(part_o) & 15u) == 0,
                  "paged_attention_prefill_tc: pointers must be 16-byte aligned");
     CUtensorMap mq;
     TLLM_REQUIRE(pftc::make_map(&mq, q, tokens, (long long)q_heads * 128, 128),
@@ -607,10 +703,15 @@ extern "C" int tllm_paged_attention_prefill_tc(
         if (e != cudaSuccess) { set_error("paged_attention_prefill_tc: %s", cudaGetErrorString(e)); return (int)e; }
         configured = true;
     }
-    const int pair_heads = tllm_paged_attention_prefill_tc_rows(q_heads, kv_heads) == 128;
-    pftc::paged_attention_prefill_tc_kernel<<<dim3(pair_heads ? q_heads / 2 : q_heads, n_tiles), pftc::kThreads,
+    const int rows_per_tile = tllm_paged_attention_prefill_tc_rows(q_heads, kv_heads);
+    const int pair_heads = rows_per_tile == 128;
+    pftc::paged_attention_prefill_tc_kernel<<<dim3(pair_heads ? q_heads / 2 : q_heads, n_tiles, splits), pftc::kThreads,
                                               pftc::kSmemBytes, stream>>>(
         mq, (const bf16*)cache, seg_info, tiles, block_table, max_pages, page_size, q_heads, kv_heads, window,
-        scale * 1.4426950408889634f, pair_heads, (bf16*)out, error_word);
-    return finish_launch("paged_attention_prefill_tc");
+        scale * 1.4426950408889634f, pair_heads, (bf16*)out, splits, part_o, part_ml, error_word);
+    int rc = finish_launch("paged_attention_prefill_tc");
+    if (rc != 0 || splits == 1) return rc;
+    pftc::paged_attention_prefill_combine_kernel<<<dim3(n_tiles, q_heads, rows_per_tile / pftc::kCombineRows), 128, 0, stream>>>(
+        part_o, part_ml, seg_info, tiles, rows_per_tile, q_heads, splits, (bf16*)out);
+    return finish_launch("paged_attention_prefill_combine");
 }

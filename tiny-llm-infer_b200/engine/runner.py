@@ -289,7 +289,7 @@ class ModelRunner:
     # comes again and again (a full portion of one prompt, or the same number of decode rows
     # beside one portion), so a layout seen a second time is captured and replayed from then
     # on.  The layout is everything that sizes a grid or places a buffer: tokens, wanted rows,
-    # entries, one-token rows, attention blocks, and the context bucket of the one-token rows;
+    # entries, one-token rows, attention blocks, and the context rounded up to a power of two;
     # the values (ids, positions, slots, segments, block tables) are read from the runner's
     # fixed device buffers at replay.
     PROMPT_GRAPHS = 8
@@ -300,12 +300,10 @@ class ModelRunner:
                 and ctx.want_rows.shape[0] <= min(self.GRAPH_MAX_ROWS, self.max_batch_tokens)
                 and self._graph_safe):
             return None
-        bucket = 0
-        if ctx.n_dec:
-            bucket = 256
-            while bucket < ctx.max_context:
-                bucket *= 2
-            ctx.max_context = bucket                  # grids of the one-token rows are sized for the bucket
+        bucket = 256
+        while bucket < ctx.max_context:
+            bucket *= 2
+        ctx.max_context = bucket       # grids that go with the context (key splits) are sized for the bucket
         return (ctx.tokens, int(ctx.want_rows.shape[0]), len(ctx.segments), ctx.n_dec, ctx.n_tiles,
                 ctx.n_tiles128, ctx.n_tiles256, bucket)
 

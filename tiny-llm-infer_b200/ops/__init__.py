@@ -75,7 +75,7 @@ def _declare(h) -> None:
                                         i32, vp, vp, vp, vp],
         "tllm_paged_attention_prefill": [vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32, vp, vp],
         "tllm_paged_attention_prefill_tc": [vp, i32, vp, i32, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32,
-                                            vp, vp, vp],
+                                            vp, i32, vp, vp, vp, vp],
     }
     for name, args in sigs.items():
         fn = getattr(h, name)
@@ -288,20 +288,40 @@ def prefill_tcgen05_block_rows(q_heads: int, kv_heads: int) -> int:
     return int(lib().tllm_paged_attention_prefill_tc_rows(q_heads, kv_heads))
 
 
+def prefill_splits(blocks: int, max_context: int) -> int:
+    """Runs of keys per block of query rows in ``paged_attention_prefill_tcgen05``: 1, 2, 4 or 8.
+    A step with few query rows (a short portion of a prompt) has few blocks, each walking all keys
+    of its request; cutting the keys fills the GPU (148 SMs, one block each), as long as a run
+    keeps eight tiles of 64 keys, below which a block's start and end outweigh its work."""
+    fit = min(SM_COUNT // max(blocks, 1), -(-max_context // 64) // 8)
+    splits = 1
+    while splits * 2 <= min(fit, 8):
+        splits *= 2
+    return splits
+
+
+
 def paged_attention_prefill_tcgen05(q, cache, seg_info, tiles, n_tiles, block_table, page_size, q_heads,
-                                    kv_heads, head_dim, window, scale, out):
+                                    kv_heads, head_dim, window, scale, out, splits=1):
     """As ``paged_attention_prefill`` on tcgen05 tensor cores with TMA loads: bfloat16, head width
-    128, ``tiles`` at multiples of ``prefill_tcgen05_block_rows`` rows.  The kernel's waits are
-    bounded; what they report is read by ``check_error_word``."""
+    128, ``tiles`` at multiples of ``prefill_tcgen05_block_rows`` rows.  With ``splits`` > 1 every
+    block's keys are shared by that many blocks and a second kernel combines what they leave.
+    The kernel's waits are bounded; what they report is read by ``check_error_word``."""
     _cuda(q, cache, seg_info, tiles, block_table, out)
     assert q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
     assert q.shape[1] == q_heads * head_dim and tuple(out.shape) == tuple(q.shape)
     global tcgen05_calls
     tcgen05_calls += 1
+    part_o = part_ml = None
+    if splits > 1:
+        n = q.shape[0] * q_heads * splits
+        ws = workspace(q.device, n * (head_dim + 2))
+        part_o, part_ml = ws[:n * head_dim], ws[n * head_dim:n * (head_dim + 2)]
     _check(lib().tllm_paged_attention_prefill_tc(
         _p(q), q.shape[0], _p(cache), cache.shape[0], _p(seg_info), _p(tiles), n_tiles, _p(block_table),
         block_table.shape[1], page_size, q_heads, kv_heads, head_dim, int(window or 0), float(scale),
-        _p(out), _p(error_word(q.device)), _stream()), "paged_attention_prefill_tc")
+        _p(out), splits, _p(part_o), _p(part_ml), _p(error_word(q.device)), _stream()), "paged_attention_prefill_tc",
+        kernels=2 if splits > 1 else 1)
     return out
 
 
@@ -324,10 +344,13 @@ def paged_attention(q: torch.Tensor, cache: torch.Tensor, positions, token_slot,
                                    ctx.max_context)
         if ctx.n_tiles:
             if PREFILL_TCGEN05 and head_dim == 128 and getattr(ctx, "n_tiles256", 0):
-                blocks = ctx.n_tiles128 if prefill_tcgen05_block_rows(q_heads, kv_heads) == 128 else ctx.n_tiles256
+                pairs = prefill_tcgen05_block_rows(q_heads, kv_heads) == 128
+                blocks = ctx.n_tiles128 if pairs else ctx.n_tiles256
+                keys = ctx.max_context if not window else min(ctx.max_context, window + 256)
+                splits = prefill_splits(blocks * (q_heads // 2 if pairs else q_heads), keys)
                 paged_attention_prefill_tcgen05(q, cache, ctx.seg_info, ctx.pf_tiles, blocks,
                                                 block_table, page_size, q_heads, kv_heads, head_dim,
-                                                window, scale, out)
+                                                window, scale, out, splits)
             else:
                 paged_attention_prefill(q, cache, ctx.seg_info, ctx.pf_tiles, ctx.n_tiles, block_table,
                                         page_size, q_heads, kv_heads, head_dim, window, scale, out)
