@@ -98,25 +98,29 @@ __global__ void qk_norm_rope_store_kernel(
 // is VEC * 16 elements away, that is, in lane ^ 16.
 template <typename T, int VEC> struct VecIO;
 template <int VEC> struct VecIO<bf16, VEC> {
-    static __device__ __forceinline__ void load(const bf16* p, float (&v)[VEC]) {
+    // what a load leaves in registers until it is needed: half the registers of the float form
+    struct Raw { uint32_t w[VEC / 2]; };
+    static __device__ __forceinline__ Raw load_raw(const bf16* p) {
+        Raw raw;
         if constexpr (VEC == 2) {
-            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
-            v[0] = f.x; v[1] = f.y;
+            raw.w[0] = *reinterpret_cast<const uint32_t*>(p);
         } else if constexpr (VEC == 4) {
-            const uint2 raw = *reinterpret_cast<const uint2*>(p);
-            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-            const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
-            v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+            const uint2 u = *reinterpret_cast<const uint2*>(p);
+            raw.w[0] = u.x; raw.w[1] = u.y;
         } else {
-            const uint4 raw = *reinterpret_cast<const uint4*>(p);
-            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+            const uint4 u = *reinterpret_cast<const uint4*>(p);
+            raw.w[0] = u.x; raw.w[1] = u.y; raw.w[2] = u.z; raw.w[3] = u.w;
+        }
+        return raw;
+    }
+    static __device__ __forceinline__ void unpack(const Raw& raw, float (&v)[VEC]) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float2 f = __bfloat1622float2(h[i]);
-                v[2 * i] = f.x; v[2 * i + 1] = f.y;
-            }
+        for (int i = 0; i < VEC / 2; ++i) {
+            v[2 * i] = __uint_as_float(raw.w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(raw.w[i] & 0xffff0000u);
         }
     }
+    static __device__ __forceinline__ void load(const bf16* p, float (&v)[VEC]) { unpack(load_raw(p), v); }
     static __device__ __forceinline__ void store(bf16* p, const float (&v)[VEC]) {
         if constexpr (VEC == 2) {
             *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v[0], v[1]);
@@ -136,13 +140,21 @@ template <int VEC> struct VecIO<bf16, VEC> {
     }
 };
 template <int VEC> struct VecIO<float, VEC> {
-    static __device__ __forceinline__ void load(const float* p, float (&v)[VEC]) {
+    struct Raw { float v[VEC]; };
+    static __device__ __forceinline__ Raw load_raw(const float* p) {
+        Raw raw;
 #pragma unroll
         for (int i = 0; i < VEC; i += 2) {
             const float2 f = *reinterpret_cast<const float2*>(p + i);
-            v[i] = f.x; v[i + 1] = f.y;
+            raw.v[i] = f.x; raw.v[i + 1] = f.y;
         }
+        return raw;
     }
+    static __device__ __forceinline__ void unpack(const Raw& raw, float (&v)[VEC]) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) v[i] = raw.v[i];
+    }
+    static __device__ __forceinline__ void load(const float* p, float (&v)[VEC]) { unpack(load_raw(p), v); }
     static __device__ __forceinline__ void store(float* p, const float (&v)[VEC]) {
 #pragma unroll
         for (int i = 0; i < VEC; i += 2) *reinterpret_cast<float2*>(p + i) = make_float2(v[i], v[i + 1]);
@@ -150,7 +162,7 @@ template <int VEC> struct VecIO<float, VEC> {
 };
 
 template <typename T, typename TG, int VEC>
-__global__ void qk_norm_rope_store_vec_kernel(
+__global__ void __launch_bounds__(256, (VEC <= 4 && sizeof(T) == 2) ? 4 : 2) qk_norm_rope_store_vec_kernel(
     T* qkv, const TG* __restrict__ q_gain, const TG* __restrict__ k_gain, float eps,
     const float* __restrict__ inv_freq, const int* __restrict__ positions,
     const int* __restrict__ token_slot, const int* __restrict__ block_table, int max_pages,
@@ -164,10 +176,26 @@ __global__ void qk_norm_rope_store_vec_kernel(
     const int pos = positions[t];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     const bool rope = (flags & kFlagRope) != 0;
-    if (rope)
-        for (int i = threadIdx.x; i < HALF; i += blockDim.x) sincosf((float)pos * inv_freq[i], &sn[i], &cs[i]);
     const int heads_total = q_heads + 2 * kv_heads;
     const int e0 = lane * VEC;
+    T* row = qkv + (size_t)t * heads_total * HD;
+    // With few tokens the heads of a token are spread over gridDim.y blocks (one round per warp);
+    // with many a warp takes several heads, and loads kRounds of them before it works on the
+    // first, so that their latencies overlap.  The first loads are issued before the angles are
+    // computed (sincosf of a large argument is slow) and before the page is looked up.
+    constexpr int kRounds = 6;
+    const int stride = warps * gridDim.y;
+    typename VecIO<T, VEC>::Raw xs[kRounds];
+    auto load_heads = [&](int first) {
+#pragma unroll
+        for (int r = 0; r < kRounds; ++r) {
+            const int head = first + r * stride;
+            if (head < heads_total) xs[r] = VecIO<T, VEC>::load_raw(row + (size_t)head * HD + e0);
+        }
+    };
+    load_heads(blockIdx.y * warps + warp);
+    if (rope)
+        for (int i = threadIdx.x; i < HALF; i += blockDim.x) sincosf((float)pos * inv_freq[i], &sn[i], &cs[i]);
     float gq[VEC], gk[VEC];
     if (flags & kFlagNorm) {
 #pragma unroll
@@ -176,24 +204,14 @@ __global__ void qk_norm_rope_store_vec_kernel(
     int page = -1;
     if (flags & kFlagStore) page = block_table[(size_t)slot * max_pages + pos / page_size];
     __syncthreads();
-    T* row = qkv + (size_t)t * heads_total * HD;
-    // With few tokens the heads of a token are spread over gridDim.y blocks (one round per warp);
-    // with many a warp takes several heads, and loads kRounds of them before it works on the
-    // first, so that their latencies overlap.
-    constexpr int kRounds = 6;
-    const int stride = warps * gridDim.y;
     for (int first = blockIdx.y * warps + warp; first < heads_total; first += stride * kRounds) {
-        float xs[kRounds][VEC];
-#pragma unroll
-        for (int r = 0; r < kRounds; ++r) {
-            const int head = first + r * stride;
-            if (head < heads_total) VecIO<T, VEC>::load(row + (size_t)head * HD + e0, xs[r]);
-        }
+        if (first != blockIdx.y * warps + warp) load_heads(first);
 #pragma unroll
         for (int r = 0; r < kRounds; ++r) {
             const int head = first + r * stride;
             if (head >= heads_total) break;
-            float (&x)[VEC] = xs[r];
+            float x[VEC];
+            VecIO<T, VEC>::unpack(xs[r], x);
             const bool is_q = head < q_heads, is_k = !is_q && head < q_heads + kv_heads;
             T* src = row + (size_t)head * HD + e0;
             if ((is_q || is_k) && (flags & kFlagNorm)) {
