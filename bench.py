@@ -81,8 +81,13 @@ class ClockSampler:
                 self.proc.kill()
         mhz, max_mhz, reasons = [], 0, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for a, b, what in windows:                 # per timed region, for the log
+            inside = [int(line.split(",")[0]) for t, line in self.samples if a <= t <= b and line.split(",")[0].strip().isdigit()]
+            if inside:
+                print(f"[bench] clocks during {what}: median {int(statistics.median(inside))} MHz, min {min(inside)}, "
+                      f"{len(inside)} samples", file=sys.stderr, flush=True)
         for t, line in self.samples:
-            if windows and not any(a <= t <= b for a, b in windows):
+            if windows and not any(a <= t <= b for a, b, _ in windows):
                 continue
             parts = [p.strip() for p in line.split(",")]
             try:
@@ -177,7 +182,7 @@ def main() -> int:
             prefill_once()
         w0 = time.perf_counter()
         prefill_ms = statistics.median(prefill_once() for _ in range(5))
-        windows.append((w0, time.perf_counter()))
+        windows.append((w0, time.perf_counter(), "prefill"))
         prefill_flops = 2.0 * PREFILL_TOKENS * args.layers * layer_params \
             + args.layers * 2.0 * PREFILL_TOKENS ** 2 * cfg.q_dim + 2.0 * vocab * cfg.hidden_size
         prefill = {"value": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "tokens": PREFILL_TOKENS,
@@ -218,7 +223,7 @@ def main() -> int:
             if it >= warmup:
                 times.append((start, end))
         torch.cuda.synchronize()
-        windows.append((w_start, time.perf_counter()))
+        windows.append((w_start, time.perf_counter(), f"decode b{batch}"))
         launches = ops.launches - before
         ms = sum(a.elapsed_time(b) for a, b in times) / steps
         for name in names:
@@ -255,7 +260,7 @@ def main() -> int:
             engine.step()
         torch.cuda.synchronize()
         elapsed = time.perf_counter() - t_start
-        windows.append((t_start, t_start + elapsed))
+        windows.append((t_start, t_start + elapsed, f"e2e b{batch}"))
         while not engine.is_finished():
             engine.step()
         bucket = 1

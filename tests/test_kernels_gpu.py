@@ -600,6 +600,51 @@ def test_gemm_tcgen05(ops, M, N, K, swiglu, short_tiles):
     assert (y.cpu().double() - ref).abs().max() < 1.6e-2 * ref.abs().max()
 
 
+@pytest.mark.parametrize("M", [9, 32, 33, 64, 100, 128])
+@pytest.mark.parametrize("N,K,splits", [(256, 64, 1), (304, 328, 2), (1000, 1000, 8), (80, 4104, 5), (4096, 1024, 3),
+                                        (1008, 4096, None)])
+@pytest.mark.parametrize("mode", ["bf16", "f32", "swiglu"])
+def test_gemm_stream_tc(ops, M, N, K, splits, mode):
+    """The weight-streaming tcgen05 product for 9 to 128 rows: row counts inside and at the edges
+    of the paddings (32, 64, 128), weight rows that end inside a tile of 128, K that ends inside
+    a stage of 64, one to eight blocks sharing a tile's K (one of them left without a stage
+    when K is short), float32 and bfloat16 results, fused SwiGLU over interleaved rows.  One
+    weight row and one k-column are much larger than the rest."""
+    if mode == "swiglu" and N % 16:
+        pytest.skip("interleaved rows come in sixteens")
+    x = rnd(M, K, seed=420, scale=0.5).to(torch.bfloat16)
+    w = rnd(N, K, seed=421, scale=0.5).to(torch.bfloat16)
+    w[N - 1] *= 8
+    w[:, K - 1] *= 6
+    ref = x.double() @ w.double().T
+    if splits is not None and splits > -(-K // 64):
+        with pytest.raises(ops.KernelError, match="splits"):
+            ops.gemm_stream_tc(dev(x), dev(w), splits=splits)
+        return
+    if mode == "swiglu":
+        ref = plain.silu(ref[:, :N // 2]) * ref[:, N // 2:]
+        y = ops.gemm_stream_tc(dev(x), dev(ops.interleave_gate_up(w[:N // 2], w[N // 2:])), swiglu=True, splits=splits)
+    else:
+        y = ops.gemm_stream_tc(dev(x), dev(w), torch.float32 if mode == "f32" else torch.bfloat16, splits=splits)
+    ops.check_error_word("cuda:0")
+    assert y.shape == ref.shape and y.dtype == (torch.float32 if mode == "f32" else torch.bfloat16)
+    assert (y.cpu().double() - ref).abs().max() < (2e-3 if mode == "f32" else 1.6e-2) * ref.abs().max()
+
+
+def test_gemm_stream_tc_refusals_and_rule(ops):
+    x = torch.zeros((129, 64), dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros((128, 64), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ops.KernelError, match="outside 1..128"):
+        ops.gemm_stream_tc(x, w)
+    with pytest.raises(ops.KernelError, match="multiple of 8"):
+        ops.gemm_stream_tc(x[:16, :60].contiguous(), w[:, :60].contiguous())
+    with pytest.raises(ops.KernelError, match="sixteens"):
+        ops.gemm_stream_tc(x[:16], w[:72], swiglu=True)
+    # Qwen3-8B: q/k/v 48 tiles x 4, o 32 x 8, gate-up 192 x 1, down 32 x 8; 0.6B: q/k/v 32 x 4, head one block each
+    assert [ops.stream_tc_splits(n, k) for n, k in ((6144, 4096), (4096, 4096), (24576, 4096), (4096, 12288),
+                                                     (4096, 1024), (151936, 1024))] == [4, 8, 1, 8, 4, 1]
+
+
 def test_linear_takes_the_tcgen05_path_for_many_rows(ops):
     assert ops.tcgen05_pays(2048, 4096, 4096, torch.bfloat16) and not ops.tcgen05_pays(2048, 6144, 4096, torch.bfloat16)
     assert not ops.tcgen05_pays(64, 4096, 4096, torch.bfloat16) and not ops.tcgen05_pays(2048, 4096, 4096, torch.float32)
@@ -612,15 +657,15 @@ def test_linear_takes_the_tcgen05_path_for_many_rows(ops):
     ref = plain.silu(ref[:, :5376]) * ref[:, 5376:]
     ops.check_error_word("cuda:0")
     assert (act.cpu().double() - ref).abs().max() < 1.6e-2 * ref.abs().max()
-    small = ops.linear_swiglu(dev(x[:9]), dev(w), torch.bfloat16)           # few rows: two kernels, same values
-    assert ops.tcgen05_calls == before + 1
+    small = ops.linear_swiglu(dev(x[:9]), dev(w), torch.bfloat16)           # few rows, stacked: the streaming
+    assert ops.tcgen05_calls == before + 2                                   # product and the SwiGLU kernel
     assert (small.cpu().double() - ref[:9]).abs().max() < 1.6e-2 * ref.abs().max()
     wi = dev(ops.interleave_gate_up(w[:5376], w[5376:]))                     # the layout the feed-forward part stores
     for rows in (600, 9, 40):
         act = ops.linear_swiglu(dev(x[:rows]), wi, torch.bfloat16, interleaved=True)
         ops.check_error_word("cuda:0")
         assert (act.cpu().double() - ref[:rows]).abs().max() < 1.6e-2 * ref.abs().max()
-    assert ops.tcgen05_calls == before + 2
+    assert ops.tcgen05_calls == before + 5                                   # one fused kernel each
 
 
 @pytest.mark.parametrize("M", [1, 5, 8])

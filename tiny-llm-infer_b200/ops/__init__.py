@@ -71,6 +71,7 @@ def _declare(h) -> None:
         "tllm_gemm_skinny": [vp, vp, vp, i32, i32, i32, i32, vp],
         "tllm_gemm_tcgen05": [vp, vp, vp, i32, i32, i32, i32, vp, vp],
         "tllm_gemm_skinny_swiglu": [vp, vp, vp, i32, i32, i32, i32, vp],
+        "tllm_gemm_stream_tc": [vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp],
         "tllm_paged_attention_decode": [vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32,
                                         i32, vp, vp, vp, vp],
         "tllm_paged_attention_prefill": [vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32, vp, vp],
@@ -474,6 +475,52 @@ def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, swiglu: bool = False, sh
     return y
 
 
+# Above SKINNY_MAX_ROWS and up to this many rows the weight-streaming tcgen05 product is used (the
+# kernel takes up to 128).  Measured at Qwen3-8B sizes against the library, per layer (q/k/v, o,
+# gate-up + SwiGLU, down): 16 rows 13.0 + 12.9 + 39.1 + 20.5 against 18.0 + 17.0 + 43 + 23.8 µs,
+# 64 rows 15.0 + 12.0 + 42.3 + 22.5 against 17.6 + 13.2 + 45 + 24.5, 128 rows 17.8 + 14.9 + 47.3 + 26.5
+# against 14.5 + 12.5 + 46 + 25.5; inside a decode step the two are level (batch 16: 5.42 against
+# 5.47 ms, batch 64: 9.92 against 9.86 ms).
+STREAM_TC_MAX_ROWS = 64
+
+
+def stream_tc_splits(out_rows: int, k: int) -> int:
+    """Blocks (1, 2, 4 or 8, one cluster) that share the K of a tile of 128 weight rows in
+    ``gemm_stream_tc``: the most that still run all at once (clusters do not pack the last
+    slots of the GPU, so 260 of its 296 count), each with four stages of 64 or more.  Measured
+    at Qwen3-8B sizes, 64 rows: q/k/v (48 tiles) 27.6, 18.2, 15.0, 20.7 µs for 1, 2, 4, 8 blocks,
+    o (32 tiles) 27.2, 17.7, 12.8, 12.0, gate-up (192 tiles) 42.3, 46.1, 48.0, 62.0."""
+    tiles = -(-out_rows // 128)
+    splits = 1
+    while splits < 8 and tiles * splits * 2 <= 260 and -(-k // 64) // (splits * 2) >= 4:
+        splits *= 2
+    return splits
+
+
+def gemm_stream_tc(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
+                   swiglu: bool = False, splits: Optional[int] = None) -> torch.Tensor:
+    """y = x . weight^T for up to 128 bfloat16 rows on tcgen05 with the roles swapped (128 weight
+    rows fill the tensor core's rows, the rows of x its columns; csrc/gemm_stream_tc.cu): the
+    weights stream once from HBM, ``splits`` blocks of a cluster share a tile's K and add their
+    partial sums through distributed shared memory.  ``swiglu``: gate and up rows interleaved by
+    eight, the result is silu(x . gate^T) * (x . up^T)."""
+    _cuda(x, weight)
+    rows, k = x.shape
+    n = weight.shape[0]
+    assert weight.shape[1] == k and x.dtype == weight.dtype == torch.bfloat16
+    y = torch.empty((rows, n // 2 if swiglu else n), dtype=out_dtype, device=x.device)
+    if rows == 0:
+        return y
+    if splits is None:
+        splits = stream_tc_splits(n, k)
+    global tcgen05_calls
+    tcgen05_calls += 1
+    _check(lib().tllm_gemm_stream_tc(_p(x), _p(weight), _p(y), rows, n, k, int(swiglu),
+                                     int(out_dtype == torch.float32), splits, _p(error_word(x.device)), _stream()),
+           "gemm_stream_tc")
+    return y
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """y[T, N] = x[T, K] . weight[N, K]^T with float32 accumulation.  A weight kept in
     float32 is multiplied in float32 whatever the activations are stored in."""
@@ -491,6 +538,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     if weight.dtype == torch.bfloat16 and 0 < rows <= SKINNY_MAX_ROWS and k % 8 == 0 \
             and x.is_contiguous() and weight.is_contiguous() and want in _DT:
         return gemm_skinny(x, weight, want)
+    if weight.dtype == torch.bfloat16 and SKINNY_MAX_ROWS < rows <= STREAM_TC_MAX_ROWS and k % 8 == 0 \
+            and x.is_contiguous() and weight.is_contiguous() and want in _DT:
+        return gemm_stream_tc(x, weight, want)
     if want == torch.bfloat16 and tcgen05_pays(rows, weight.shape[0], k, weight.dtype) \
             and x.is_contiguous() and weight.is_contiguous():
         return gemm_tcgen05(x, weight)
@@ -524,6 +574,8 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out_dtype: torch.dty
         return gemm_tcgen05(x, w_gate_up, swiglu=True, interleaved=interleaved)
     if plain and 0 < rows <= (SKINNY_MAX_ROWS if interleaved else SKINNY_SWIGLU_MAX_ROWS) and k % 8 == 0:
         return gemm_skinny_swiglu(x, w_gate_up, interleaved)
+    if plain and interleaved and SKINNY_MAX_ROWS < rows <= STREAM_TC_MAX_ROWS and k % 8 == 0:
+        return gemm_stream_tc(x, w_gate_up, torch.bfloat16, swiglu=True)
     gate_up = linear(x, w_gate_up, out_dtype=out_dtype)
     act = torch.empty((rows, inter), dtype=out_dtype, device=x.device)
     return swiglu(gate_up, act, interleaved)
