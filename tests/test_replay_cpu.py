@@ -50,3 +50,41 @@ def test_replay_modes_cpu(name, tmp_path, cpu_ops, monkeypatch, capsys):
     worst, where = replay.compare(tmp_path / "out", tb, want, cfg["vocab_size"])
     assert set(worst) == {"w", "t", "p", "m"}
     assert max(worst.values()) < 2e-4, (worst, where)
+
+
+def test_a_step_prepared_ahead_with_a_late_token(tmp_path, cpu_ops):
+    """prepare() lays a step out before one of its tokens is known, run() fills it in: the
+    logits are those of the same step made in one go; a second prepare() before run(), a
+    missing late token and one outside the vocabulary are refused, and the runner can go on."""
+    from tiny_llm_infer_b200.cache import CacheManager
+    from tiny_llm_infer_b200.engine import ModelRunner, StepEntry, load_model
+    from tiny_llm_infer_b200.engine.runner import StepError
+    tiny = TINIES["A"]
+    folder = make_folder(tiny, tmp_path / "model")
+    model, _ = load_model(str(folder), torch.float32, "cpu")
+    toks = requests_for(tiny, (20, 9))
+
+    def fresh():
+        cache = CacheManager(model.cache_needs(), tiny["page_size"], 16, max_slots=4, max_seq_len=128,
+                             dtype=torch.float32, device="cpu")
+        return ModelRunner(model, cache, max_batch_tokens=64)
+
+    a, b = toks["0"], toks["1"]
+    plain_runner, runner = fresh(), fresh()
+    for r in (plain_runner, runner):
+        r.step([StepEntry("a", a[:12], []), StepEntry("b", b[:8], [])])
+    want = plain_runner.step([StepEntry("a", a[12:], [7]), StepEntry("b", b[8:9], [0])]).clone()
+    late = [StepEntry("a", a[12:19] + [-1], [7], late=7), StepEntry("b", [-1], [0], late=0)]
+    prepared = runner.prepare(late)
+    assert [i for i, _ in prepared.late] == [0, 1]
+    with pytest.raises(StepError, match="has not been run"):
+        runner.prepare([StepEntry("c", [1, 2], [])])
+    with pytest.raises(StepError, match="late tokens"):
+        runner.run(prepared, [a[19]])
+    prepared = runner.prepare(late)                     # the refusal freed the runner; pages are already reserved
+    with pytest.raises(StepError, match="outside"):
+        runner.run(prepared, [a[19], 10 ** 6])
+    got = runner.run(runner.prepare(late), [a[19], b[8]])
+    assert torch.equal(got, want)
+    assert late[0].tokens[7] == a[19] and runner.cache.computed("a") == 20 and runner.cache.computed("b") == 9
+    runner.cache.audit()

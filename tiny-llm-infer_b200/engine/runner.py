@@ -253,6 +253,7 @@ class ModelRunner:
         """Upload and launch a prepared step; ``late_tokens`` in the order of ``prepared.late``."""
         if prepared is not self._prepared:
             raise StepError("run() takes the step that prepare() returned last")
+        self._prepared = None                      # whatever happens below, the host buffer is free again
         if len(late_tokens) != len(prepared.late):
             raise StepError(f"{len(prepared.late)} late tokens are open, {len(late_tokens)} were given")
         host = self._host.numpy()
@@ -262,7 +263,6 @@ class ModelRunner:
                 raise StepError(f"request {e.request!r}: token id outside [0, {self.vocab})")
             host[place] = int(token)
             e.tokens[e.late] = int(token)          # what commit() hashes
-        self._prepared = None
         self._upload(prepared.upload)
         if prepared.graph_key is not None:
             logits = self._run_graph(prepared)
