@@ -3,8 +3,10 @@
 Mirrors the reference's engine (engine/include/llm_engine.h:14-56,
 engine/src/llm_engine.cpp:29-323): requests are validated on entry, a step asks the
 scheduler for a plan, flattens it into one batch (decode tokens first, then portions of
-prompts), runs the step function, samples on the device and books the result.  Prompts
-are token ids; text in and out is an optional extra through a ``tokenizers`` tokenizer.
+prompts), runs the step function, samples on the device and books the result; while the
+GPU runs a step, the next one is already scheduled and laid out (its sampled tokens are
+filled in when they arrive).  Prompts are token ids; text in and out is an optional extra
+through a ``tokenizers`` tokenizer.
 """
 from __future__ import annotations
 

@@ -22,7 +22,10 @@ Differences: pages are asked of the cache manager (several groups, windows) inst
 a block manager of the scheduler's own; ``max_num_seqs`` bounds the requests that hold a
 slot at any time (the reference bounds the requests in one step); the prefix cache
 (engine/src/block_manager.cpp:97-125: a prompt's full pages that are already in the cache
-are shared, and its first portion starts behind them) lives in the cache manager too.
+are shared, and its first portion starts behind them) lives in the cache manager too;
+the booking of a step comes in two halves (``advance`` when it is launched, ``resolve`` when
+its tokens are known, ``postprocess`` = both), so that the engine can make the next plan
+while the step still runs.
 """
 from __future__ import annotations
 
