@@ -53,7 +53,7 @@ def peaks():
 class ClockSampler:
     """Samples nvidia-smi clocks and throttle reasons while the timed regions run."""
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap,clocks.mem,power.draw")
 
     def __init__(self):
         self.samples, self.proc, self.thread = [], None, None
@@ -82,10 +82,14 @@ class ClockSampler:
         mhz, max_mhz, reasons = [], 0, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for a, b, what in windows:                 # per timed region, for the log
-            inside = [int(line.split(",")[0]) for t, line in self.samples if a <= t <= b and line.split(",")[0].strip().isdigit()]
+            lines = [[p.strip() for p in line.split(",")] for t, line in self.samples if a <= t <= b]
+            inside = [int(p[0]) for p in lines if p[0].isdigit()]
             if inside:
-                print(f"[bench] clocks during {what}: median {int(statistics.median(inside))} MHz, min {min(inside)}, "
-                      f"{len(inside)} samples", file=sys.stderr, flush=True)
+                mem = sorted({p[6] for p in lines if len(p) > 7})
+                watts = [float(p[7]) for p in lines if len(p) > 7 and p[7].replace(".", "", 1).isdigit()]
+                print(f"[bench] clocks during {what}: SM median {int(statistics.median(inside))} MHz, min {min(inside)}; "
+                      f"memory {'/'.join(mem)} MHz; {int(statistics.median(watts)) if watts else '?'} W; {len(inside)} samples",
+                      file=sys.stderr, flush=True)
         for t, line in self.samples:
             if windows and not any(a <= t <= b for a, b, _ in windows):
                 continue
