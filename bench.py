@@ -2,7 +2,7 @@
 """Benchmark of the engine on one B200: decode and prefill throughput of a Qwen3-8B-shaped
 model with random weights, in bfloat16.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference] [--model 8b|0.6b|32b] [--mixed]
 
 A "step" is one decode step of a batch of 8 requests.  The headline ``value`` is decoded
 tokens per second timed on the device (CUDA events around each step); ``e2e`` is the same
@@ -29,6 +29,15 @@ sys.path.insert(0, str(ROOT))
 QWEN3_8B = dict(hidden_size=4096, intermediate_size=12288, num_hidden_layers=36, num_attention_heads=32,
                 num_key_value_heads=8, head_dim=128, vocab_size=151936, max_position_embeddings=40960,
                 rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False)
+# configs[3] and configs[4]: the 0.6B shape (tied head) and the 32B shape (--model)
+QWEN3_06B = dict(hidden_size=1024, intermediate_size=3072, num_hidden_layers=28, num_attention_heads=16,
+                 num_key_value_heads=8, head_dim=128, vocab_size=151936, max_position_embeddings=40960,
+                 rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=True)
+QWEN3_32B = dict(hidden_size=5120, intermediate_size=25600, num_hidden_layers=64, num_attention_heads=64,
+                 num_key_value_heads=8, head_dim=128, vocab_size=151936, max_position_embeddings=40960,
+                 rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False)
+MODELS = {"8b": ("Qwen3-8B shape", QWEN3_8B), "0.6b": ("Qwen3-0.6B shape", QWEN3_06B),
+          "32b": ("Qwen3-32B shape", QWEN3_32B)}
 CONTEXT = 4096
 PAGE = 16
 PREFILL_TOKENS = 2048
@@ -113,12 +122,22 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"],
+    ap.add_argument("--model", default="8b", choices=sorted(MODELS),
+                    help="the sizes: 8b is the benchmark configuration, 0.6b and 32b the other two of the baseline")
+    ap.add_argument("--layers", type=int, default=None,
                     help="fewer layers than the model has (named in the record) if memory or time needs it")
+    ap.add_argument("--mixed", action="store_true",
+                    help="also the mixed run of the baseline's 0.6B configuration: 64 requests, prompts of 16 to "
+                         "1024 tokens, 256 outputs each at temperature 0.6, budget 2048, through LLM.generate")
     ap.add_argument("--skip-points", action="store_true", help="leave out the batch 1 and 64 points")
-    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "e2e"],
+    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "e2e", "mixed"],
                     help="run one phase only (for profiling a small case); the record then lacks the others")
     args = ap.parse_args()
+    model_name, model_sizes = MODELS[args.model]
+    if args.layers is None:
+        args.layers = model_sizes["num_hidden_layers"]
+    if args.only == "mixed":
+        args.mixed = True
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -140,7 +159,7 @@ def main() -> int:
     assert torch.cuda.is_available(), "bench.py needs a CUDA device"
     device = "cuda:0"
     pk = peaks()
-    sizes = dict(QWEN3_8B, num_hidden_layers=args.layers)
+    sizes = dict(model_sizes, num_hidden_layers=args.layers)
     cfg = Qwen3Config(layer_types=("full_attention",) * args.layers, **sizes)
     ops.lib()
     t0 = time.perf_counter()
@@ -148,7 +167,7 @@ def main() -> int:
     torch.cuda.synchronize()
     print(f"[bench] model built in {time.perf_counter() - t0:.1f} s", file=sys.stderr, flush=True)
 
-    max_batch = 64 if not args.skip_points else max(args.batch, 1)
+    max_batch = 64 if (not args.skip_points or args.mixed) else max(args.batch, 1)
     pages = max_batch * (CONTEXT // PAGE) + 2 * (PREFILL_TOKENS // PAGE) + 64
     llm = LLM(None, dtype="bfloat16", max_model_len=CONTEXT, num_kv_blocks=pages, block_size=PAGE,
               max_num_batched_tokens=PREFILL_TOKENS, max_num_seqs=max_batch, device=device, loaded=(model, cfg))
@@ -287,21 +306,42 @@ def main() -> int:
             bw = (weight_bytes + b * ctx_b * kv_bytes_per_token) / (ms_b / 1e3) / 1e9
             print(f"[bench] decode b{b}: {v:.1f} tok/s, {ms_b:.3f} ms/step, {bw:.0f} GB/s", file=sys.stderr, flush=True)
 
+    mixed = None
+    if args.mixed:
+        g2 = torch.Generator().manual_seed(1)
+
+        def workload():
+            lens = torch.randint(16, 1025, (64,), generator=g2).tolist()
+            return ([torch.randint(0, vocab, (n,), generator=g2).tolist() for n in lens],
+                    [SamplingParams(max_tokens=256, temperature=0.6, ignore_eos=True, seed=i + 1) for i in range(64)])
+        llm.generate(*workload())                               # first run: graphs are captured
+        prompts, params = workload()
+        torch.cuda.synchronize()
+        t_start = time.perf_counter()
+        outs = llm.generate(prompts, params)
+        torch.cuda.synchronize()
+        elapsed = time.perf_counter() - t_start
+        windows.append((t_start, t_start + elapsed, "mixed run"))
+        made = sum(len(o.token_ids) for o in outs)
+        mixed = {"value": round(made / elapsed, 1), "unit": "generated tokens/s", "requests": 64,
+                 "prompt_tokens": sum(map(len, prompts)), "generated_tokens": made, "seconds": round(elapsed, 3)}
+        print(f"[bench] mixed run: {mixed}", file=sys.stderr, flush=True)
+
     record = {
-        "metric": "decode tok/s @ batch 8 (Qwen3-8B shape, context 4096, 1 B200)",
+        "metric": f"decode tok/s @ batch {args.batch} ({model_name}, context 4096, 1 B200)",
         "value": None if value is None else round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": None if ms_per_step is None else round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (random weights N(0,0.02), uniform random token ids)",
-        "config": {"model": "Qwen3-8B shape", "global_batch": args.batch, "seq_len": CONTEXT,
-                   "parallelism": "single GPU", "layers": args.layers, "layers_of_model": QWEN3_8B["num_hidden_layers"],
+        "config": {"model": model_name, "global_batch": args.batch, "seq_len": CONTEXT,
+                   "parallelism": "single GPU", "layers": args.layers, "layers_of_model": model_sizes["num_hidden_layers"],
                    "hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size,
                    "q_heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
                    "vocab_size": vocab, "page_size": PAGE, "decode_context": None if mean_ctx is None else round(mean_ctx, 1),
-                   "prefill_tokens": PREFILL_TOKENS, "l2": "inputs larger than L2 (16 GB of weights per step)",
+                   "prefill_tokens": PREFILL_TOKENS, "l2": f"inputs larger than L2 ({weight_bytes / 1e9:.1f} GB of weights per step)",
                    "peaks": pk["source"]},
         "e2e": e2e,
         "gpu_launches": launches,
-        "prefill": prefill, "roofline": roofline, "points": points,
+        "prefill": prefill, "roofline": roofline, "points": points, "mixed": mixed,
         "clocks": clocks.stop(windows),
     }
     print(json.dumps(record))
