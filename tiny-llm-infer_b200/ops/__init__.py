@@ -3,8 +3,12 @@ product.  Every function here works on CUDA tensors on the current stream and ha
 other implementation: if the kernel library cannot be built or loaded, the first call
 raises ``KernelLibraryError``.
 
-The matrix product is the library's (cuBLAS through ``torch.mm``), as in the reference,
-which calls ``cublasHgemm`` for every projection with more than one row
+The matrix product (``linear``, ``linear_swiglu``) has three kernels of this package for
+bfloat16, chosen by the number of rows: up to 8 the weight-streaming mma.sync product
+(``gemm_skinny``), 9 to 64 the weight-streaming tcgen05 product (``gemm_stream_tc``), from 256
+on, where the tiles fill the GPU, the TMA + tcgen05 product (``gemm_tcgen05``).  Everything
+else is the library's (cuBLAS through ``torch.mm``), as in the reference, which calls
+``cublasHgemm`` for every projection with more than one row
 (kernels/src/matmul_kernel_cuda.cu:83-91); in float32 mode it runs with the
 reduced-precision matrix modes switched off.
 """
