@@ -73,8 +73,9 @@ def test_overlapped_scheduling_changes_no_token(tmp_path, cpu_ops, blocks, budge
     tokens, the finished requests and the pages given back are the same as without."""
     from tiny_llm_infer_b200 import LLM, SamplingParams
     folder = make_folder(TINIES["A"], tmp_path / "m")
-    prompts = [prompt(i, n, 256) for i, n in enumerate((5, 17, 33, 9, 21))]
-    params = [SamplingParams(max_tokens=14, temperature=0.9, seed=11 + i) for i in range(5)]
+    stem = prompt(9, 35, 256)                      # two prompts begin alike: pages are shared while both live
+    prompts = [prompt(i, n, 256) for i, n in enumerate((5, 17, 33, 9))] + [stem, stem[:33] + prompt(8, 4, 256)]
+    params = [SamplingParams(max_tokens=14, temperature=0.9, seed=11 + i) for i in range(6)]
 
     def run(overlap, eos):
         llm = LLM(str(folder), dtype="float32", max_model_len=64, num_kv_blocks=blocks, block_size=16,
