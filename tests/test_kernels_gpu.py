@@ -645,7 +645,7 @@ def test_gemm_stream_tc_refusals_and_rule(ops):
                                                      (4096, 1024), (151936, 1024))] == [4, 8, 1, 8, 4, 1]
 
 
-def test_linear_takes_the_tcgen05_path_for_many_rows(ops):
+def test_linear_takes_the_tcgen05_path_for_many_rows(ops, monkeypatch):
     assert ops.tcgen05_pays(2048, 4096, 4096, torch.bfloat16) and not ops.tcgen05_pays(2048, 6144, 4096, torch.bfloat16)
     assert not ops.tcgen05_pays(64, 4096, 4096, torch.bfloat16) and not ops.tcgen05_pays(2048, 4096, 4096, torch.float32)
     x = rnd(600, 136, seed=410).to(torch.bfloat16)
@@ -657,15 +657,25 @@ def test_linear_takes_the_tcgen05_path_for_many_rows(ops):
     ref = plain.silu(ref[:, :5376]) * ref[:, 5376:]
     ops.check_error_word("cuda:0")
     assert (act.cpu().double() - ref).abs().max() < 1.6e-2 * ref.abs().max()
-    small = ops.linear_swiglu(dev(x[:9]), dev(w), torch.bfloat16)           # few rows, stacked: the streaming
-    assert ops.tcgen05_calls == before + 2                                   # product and the SwiGLU kernel
+    small = ops.linear_swiglu(dev(x[:9]), dev(w), torch.bfloat16)           # few rows: two kernels, same values
+    assert ops.tcgen05_calls == before + 1
     assert (small.cpu().double() - ref[:9]).abs().max() < 1.6e-2 * ref.abs().max()
     wi = dev(ops.interleave_gate_up(w[:5376], w[5376:]))                     # the layout the feed-forward part stores
     for rows in (600, 9, 40):
         act = ops.linear_swiglu(dev(x[:rows]), wi, torch.bfloat16, interleaved=True)
         ops.check_error_word("cuda:0")
         assert (act.cpu().double() - ref[:rows]).abs().max() < 1.6e-2 * ref.abs().max()
-    assert ops.tcgen05_calls == before + 5                                   # one fused kernel each
+    assert ops.tcgen05_calls == before + 2
+    # with the weight-streaming tcgen05 product switched on, 9 to 64 rows take it, fused with SwiGLU
+    monkeypatch.setattr(ops, "STREAM_TC_MAX_ROWS", 64)
+    for rows in (9, 40):
+        act = ops.linear_swiglu(dev(x[:rows]), wi, torch.bfloat16, interleaved=True)
+        y = ops.linear(dev(x[:rows]), dev(w))
+        ops.check_error_word("cuda:0")
+        assert (act.cpu().double() - ref[:rows]).abs().max() < 1.6e-2 * ref.abs().max()
+        full = x[:rows].double() @ w.double().T
+        assert (y.cpu().double() - full).abs().max() < 1.6e-2 * full.abs().max()
+    assert ops.tcgen05_calls == before + 6
 
 
 @pytest.mark.parametrize("M", [1, 5, 8])

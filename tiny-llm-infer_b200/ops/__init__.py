@@ -5,9 +5,10 @@ raises ``KernelLibraryError``.
 
 The matrix product (``linear``, ``linear_swiglu``) has three kernels of this package for
 bfloat16, chosen by the number of rows: up to 8 the weight-streaming mma.sync product
-(``gemm_skinny``), 9 to 64 the weight-streaming tcgen05 product (``gemm_stream_tc``), from 256
-on, where the tiles fill the GPU, the TMA + tcgen05 product (``gemm_tcgen05``).  Everything
-else is the library's (cuBLAS through ``torch.mm``), as in the reference, which calls
+(``gemm_skinny``), from 256 on, where the tiles fill the GPU, the TMA + tcgen05 product
+(``gemm_tcgen05``); a weight-streaming tcgen05 product for 9 to 128 rows (``gemm_stream_tc``) is
+there and tested but equals the library at best, so ``STREAM_TC_MAX_ROWS`` keeps it off.
+Everything else is the library's (cuBLAS through ``torch.mm``), as in the reference, which calls
 ``cublasHgemm`` for every projection with more than one row
 (kernels/src/matmul_kernel_cuda.cu:83-91); in float32 mode it runs with the
 reduced-precision matrix modes switched off.
@@ -15,6 +16,7 @@ reduced-precision matrix modes switched off.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -479,13 +481,17 @@ def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, swiglu: bool = False, sh
     return y
 
 
-# Above SKINNY_MAX_ROWS and up to this many rows the weight-streaming tcgen05 product is used (the
-# kernel takes up to 128).  Measured at Qwen3-8B sizes against the library, per layer (q/k/v, o,
-# gate-up + SwiGLU, down): 16 rows 13.0 + 12.9 + 39.1 + 20.5 against 18.0 + 17.0 + 43 + 23.8 µs,
-# 64 rows 15.0 + 12.0 + 42.3 + 22.5 against 17.6 + 13.2 + 45 + 24.5, 128 rows 17.8 + 14.9 + 47.3 + 26.5
-# against 14.5 + 12.5 + 46 + 25.5; inside a decode step the two are level (batch 16: 5.42 against
-# 5.47 ms, batch 64: 9.92 against 9.86 ms).
-STREAM_TC_MAX_ROWS = 64
+# Above SKINNY_MAX_ROWS and up to this many rows ``linear`` takes the weight-streaming tcgen05
+# product (the kernel takes up to 128).  0: never, the library's product runs instead; that is the
+# setting, because the kernel equals the library where it is best and loses elsewhere.  Measured
+# per layer (q/k/v, o, gate-up + SwiGLU, down) with weights that do not stay in L2, at Qwen3-8B
+# sizes: 16 rows 13.0 + 12.9 + 39.1 + 20.5 against the library's 18.0 + 17.0 + 43 + 23.8 µs, 64 rows
+# 15.0 + 12.0 + 42.3 + 22.5 against 17.6 + 13.2 + 45 + 24.5, 128 rows 17.8 + 14.9 + 47.3 + 26.5 against
+# 14.5 + 12.5 + 46 + 25.5; but inside a decode step the two are level (batch 16: 5.42 against 5.47 ms,
+# batch 64: 9.92 against 9.86 ms), at Qwen3-0.6B sizes a step of 64 rows takes 2.19 ms with it and
+# 2.11 without (the head, 151936 x 1024: 74 against 60 µs), and at Qwen3-32B sizes with 64 rows it
+# trails (q/k/v 24.8 against 21.8 µs, o 20.7 against 19.6, down 52.3 against 52.0).
+STREAM_TC_MAX_ROWS = int(os.environ.get("TLLM_STREAM_TC_ROWS", "0"))     # the variable: for measurements
 
 
 def stream_tc_splits(out_rows: int, k: int) -> int:
