@@ -120,7 +120,7 @@ def test_short_portions_of_a_long_prompt_share_out_their_keys(tmp_path, monkeypa
     monkeypatch.setattr(ops, "paged_attention_prefill_tcgen05", spy)
     p = prompt(77, 1500, cfg["vocab_size"])
     llm = LLM(str(folder), dtype="bfloat16", max_model_len=1600, num_kv_blocks=60, block_size=tiny["page_size"],
-              max_num_batched_tokens=128, max_num_seqs=2)
+              max_num_batched_tokens=128, max_num_seqs=2, prompt_graphs=True)
     out = llm.generate([p], SamplingParams(max_tokens=12, ignore_eos=True))[0]
     assert 2 in seen and 1 in seen, sorted(set(seen))
     ok, info = teacher_forced_ok(cfg, w, p, out.token_ids, 0.08)
@@ -264,7 +264,7 @@ def test_repeated_prompt_layouts_replay_as_graphs(folders, name, dtype):
     runners = []
     for graphs in (True, False):
         cache = CacheManager(model.cache_needs(), tiny["page_size"], 160, 8, 512, DTYPES[dtype], "cuda:0")
-        runners.append(ModelRunner(model, cache, max_batch_tokens=512, use_graphs=graphs))
+        runners.append(ModelRunner(model, cache, max_batch_tokens=512, use_graphs=graphs, prompt_graphs=graphs))
     with_graphs, plain_runner = runners
     vocab = cfg.vocab_size
     for i in range(5):                                   # five prompts of 200 tokens, each in one step

@@ -51,6 +51,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-prefix-caching", action="store_true",
                     help="compute every prompt in full (the reference always shares hashed pages)")
+    ap.add_argument("--prompt-graphs", action="store_true",
+                    help="replay prompt steps whose layout repeats as CUDA graphs too")
     ap.add_argument("--no-overlap-scheduling", action="store_true",
                     help="schedule a step only after the one before it has finished on the GPU")
     ap.add_argument("--num-seqs", type=int, default=8)
@@ -122,7 +124,7 @@ def main(argv=None) -> int:
                   max_num_seqs=min(16, len(prompts)),
                   gpu_memory_utilization=args.gpu_memory_utilization or 0.9, device=device,
                   tokenizer=args.tokenizer, enable_prefix_caching=not args.no_prefix_caching,
-                  overlap_scheduling=not args.no_overlap_scheduling)
+                  overlap_scheduling=not args.no_overlap_scheduling, prompt_graphs=args.prompt_graphs)
         params = SamplingParams(max_tokens=args.max_new_tokens, temperature=args.temperature,
                                 top_p=args.top_p, seed=args.seed)
         for result in llm.generate(prompts, params):
@@ -138,7 +140,7 @@ def main(argv=None) -> int:
               block_size=16, max_num_batched_tokens=min(max_seq_len, 256), max_num_seqs=min(16, args.num_seqs),
               gpu_memory_utilization=args.gpu_memory_utilization or 0.7, device=device,
               enable_prefix_caching=not args.no_prefix_caching,
-              overlap_scheduling=not args.no_overlap_scheduling)
+              overlap_scheduling=not args.no_overlap_scheduling, prompt_graphs=args.prompt_graphs)
     vocab = llm.runner.vocab
     import torch
 

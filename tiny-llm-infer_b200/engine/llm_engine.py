@@ -254,14 +254,17 @@ class LLM:
     manager always shares hashed pages): prompts that begin like an earlier one reuse its
     full pages; it stays off by itself for models with windows or per-request state.
     ``overlap_scheduling`` (on): the host schedules and lays out a step while the GPU runs
-    the one before it; the tokens are the same either way.
+    the one before it; the tokens are the same either way.  ``use_cuda_graphs`` (on): steps of
+    one-token rows are replayed as CUDA graphs; ``prompt_graphs`` (off): steps with prompt
+    portions whose layout repeats too (faster prompts, slightly slower decoding afterwards).
     """
 
     def __init__(self, model: str, dtype: str = "bfloat16", max_model_len: int = 2048,
                  num_kv_blocks: int = 0, block_size: int = 16, max_num_batched_tokens: Optional[int] = None,
                  max_num_seqs: int = 16, gpu_memory_utilization: float = 0.9, device: str = "cuda:0",
                  tokenizer: Optional[str] = None, loaded=None, use_cuda_graphs: bool = True,
-                 enable_prefix_caching: bool = True, overlap_scheduling: bool = True):
+                 enable_prefix_caching: bool = True, overlap_scheduling: bool = True,
+                 prompt_graphs: bool = False):
         if device.startswith("cuda") and not torch.cuda.is_available():
             raise RuntimeError("no CUDA device; this engine has no CPU path")
         torch_dtype = DTYPES[dtype] if isinstance(dtype, str) else dtype
@@ -279,7 +282,8 @@ class LLM:
                 raise RuntimeError("no memory left for the key/value cache")
         self.cache = CacheManager(self.model.cache_needs(), block_size, num_kv_blocks, max_num_seqs,
                                   max_model_len, torch_dtype, device, prefix_cache=enable_prefix_caching)
-        self.runner = ModelRunner(self.model, self.cache, max_num_batched_tokens, use_graphs=use_cuda_graphs)
+        self.runner = ModelRunner(self.model, self.cache, max_num_batched_tokens, use_graphs=use_cuda_graphs,
+                                  prompt_graphs=prompt_graphs)
         self.tokenizer = None
         if tokenizer:
             from tokenizers import Tokenizer     # optional; text is outside the engine proper

@@ -90,9 +90,10 @@ class PreparedStep:
 
 class ModelRunner:
     def __init__(self, model: Model, cache: CacheManager, max_batch_tokens: int = 8192,
-                 use_graphs: bool = True):
+                 use_graphs: bool = True, prompt_graphs: bool = False):
         self.model, self.cache = model, cache
         self.use_graphs = use_graphs
+        self.prompt_graphs = prompt_graphs and use_graphs
         self._graphs = {}
         # a step may be captured as a CUDA graph only if every launch of it reads the step's data from
         # device buffers: mixers say so themselves (graph_safe = True), other parts may say no
@@ -282,21 +283,26 @@ class ModelRunner:
             self._prepared = None
 
     # ------------------------------------------------------------------ repeated prompt steps as CUDA graphs
-    # A step with prompt portions launches fewer, longer kernels, and the host is far ahead of
-    # the GPU; still every launch from a stream costs a few microseconds between dependent
-    # kernels that a graph node does not (2048 tokens of a Qwen3-8B-sized model: 26.7 ms
-    # launched one by one, 25.5 ms replayed).  Under a token budget the same layout of a step
-    # comes again and again (a full portion of one prompt, or the same number of decode rows
-    # beside one portion), so a layout seen a second time is captured and replayed from then
-    # on.  The layout is everything that sizes a grid or places a buffer: tokens, wanted rows,
-    # entries, one-token rows, attention blocks, and the context rounded up to a power of two;
-    # the values (ids, positions, slots, segments, block tables) are read from the runner's
-    # fixed device buffers at replay.
-    PROMPT_GRAPHS = 8
+    # (``prompt_graphs=True``; off unless asked for.)  A step with prompt portions launches fewer,
+    # longer kernels, and the host is far ahead of the GPU; still every launch from a stream costs
+    # a few microseconds between dependent kernels that a graph node does not (2048 tokens of a
+    # Qwen3-8B-sized model: 26.5 ms launched one by one, 25.85 ms replayed).  Under a token budget
+    # the same layout of a step comes again and again (a full portion of one prompt, or the same
+    # number of decode rows beside one portion), so a layout seen a second time is captured and
+    # replayed from then on.  The layout is everything that sizes a grid or places a buffer:
+    # tokens, wanted rows, entries, one-token rows, attention blocks, and the context rounded up
+    # to a power of two; the values (ids, positions, slots, segments, block tables) are read from
+    # the runner's fixed device buffers at replay.
+    # Why it is off: in a process that has captured three or more such graphs, decode graphs
+    # captured afterwards replay 2% slower (Qwen3-8B sizes, batch 8: 4.19 to 4.22 ms per step
+    # instead of 4.10 to 4.12; one or two prompt graphs, or any number of decode graphs, do not do
+    # it; whether the prompt graphs still exist makes no difference).  The cause was not found,
+    # and decode steps are where a running engine spends its time.
+    PROMPT_GRAPHS = 8            # at least two: the pool of the graphs is never left without one
     PROMPT_GRAPH_MIN_TOKENS = 128
 
     def _prompt_signature(self, ctx: StepContext):
-        if not (self.use_graphs and self.is_cuda and ctx.tokens >= self.PROMPT_GRAPH_MIN_TOKENS
+        if not (self.prompt_graphs and self.is_cuda and ctx.tokens >= self.PROMPT_GRAPH_MIN_TOKENS
                 and ctx.want_rows.shape[0] <= min(self.GRAPH_MAX_ROWS, self.max_batch_tokens)
                 and self._graph_safe):
             return None
