@@ -334,7 +334,7 @@ class ModelRunner:
         if self._graph_logits is None:
             rows = min(self.GRAPH_MAX_ROWS, self.max_batch_tokens)
             self._graph_logits = torch.empty((rows, self.vocab), dtype=torch.float32, device=self.device)
-        while len(self._prompt_graphs) >= self.PROMPT_GRAPHS:
+        while len(self._prompt_graphs) >= max(2, self.PROMPT_GRAPHS):
             self._prompt_graphs.pop(next(iter(self._prompt_graphs)))      # the oldest
         graph = torch.cuda.CUDAGraph()
         launches, tc_calls = ops.launches, ops.tcgen05_calls
