@@ -99,12 +99,14 @@ def test_long_prompts_head_width_128(folders, budget):
         assert ok, info
 
 
-def test_short_portions_of_a_long_prompt_share_out_their_keys(tmp_path, monkeypatch):
+@pytest.mark.parametrize("prompt_graphs", [False, True])
+def test_short_portions_of_a_long_prompt_share_out_their_keys(tmp_path, monkeypatch, prompt_graphs):
     """A prompt of 1500 tokens under a budget of 128: a step then has three blocks of query rows
     and up to 24 tiles of keys, so the full-attention layer cuts every block's keys into runs
-    for several blocks and combines them (the windowed layer never sees enough keys).  The steps
-    repeat their layout and are replayed as graphs, the context bucket deciding the number of
-    runs.  Generated tokens against the plain implementation on the same prefix."""
+    for several blocks and combines them (the windowed layer never sees enough keys).  With
+    ``prompt_graphs`` the steps, which repeat their layout, are replayed as graphs, the context
+    bucket deciding the number of runs.  Generated tokens against the plain implementation on
+    the same prefix."""
     import dataclasses
     from tiny_llm_infer_b200 import LLM, SamplingParams, ops
     tiny = dict(TINIES["E"])
@@ -120,7 +122,7 @@ def test_short_portions_of_a_long_prompt_share_out_their_keys(tmp_path, monkeypa
     monkeypatch.setattr(ops, "paged_attention_prefill_tcgen05", spy)
     p = prompt(77, 1500, cfg["vocab_size"])
     llm = LLM(str(folder), dtype="bfloat16", max_model_len=1600, num_kv_blocks=60, block_size=tiny["page_size"],
-              max_num_batched_tokens=128, max_num_seqs=2, prompt_graphs=True)
+              max_num_batched_tokens=128, max_num_seqs=2, prompt_graphs=prompt_graphs)
     out = llm.generate([p], SamplingParams(max_tokens=12, ignore_eos=True))[0]
     assert 2 in seen and 1 in seen, sorted(set(seen))
     ok, info = teacher_forced_ok(cfg, w, p, out.token_ids, 0.08)
