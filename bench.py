@@ -7,8 +7,8 @@ model with random weights, in bfloat16.
 A "step" is one decode step of a batch of 8 requests.  The headline ``value`` is decoded
 tokens per second timed on the device (CUDA events around each step); ``e2e`` is the same
 through the Python entry point (``LLMEngine.step``), host token ids in and out, timed by
-the wall clock.  One JSON line is printed.  The sizes are those of BASELINE.json
-``configs[2]``; every request stands at a context of about 4096 tokens while it decodes
+the wall clock.  One JSON line is printed.  The sizes are those of Qwen3-8B
+(the benchmark configuration); every request stands at a context of about 4096 tokens while it decodes
 (the prompts are really prefilled, in portions of 2048 tokens, outside the timed region).
 
 For more than one GPU this engine has nothing to run: it prints one line and exits 2.
@@ -25,11 +25,11 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-# BASELINE.json configs[2]: Qwen3-8B shape, random weights N(0, 0.02), untied head, page 16
+# the benchmark configuration: Qwen3-8B shape, random weights N(0, 0.02), untied head, page 16
 QWEN3_8B = dict(hidden_size=4096, intermediate_size=12288, num_hidden_layers=36, num_attention_heads=32,
                 num_key_value_heads=8, head_dim=128, vocab_size=151936, max_position_embeddings=40960,
                 rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False)
-# configs[3] and configs[4]: the 0.6B shape (tied head) and the 32B shape (--model)
+# the two other sizes the reference is quoted on: the 0.6B shape (tied head) and the 32B shape (--model)
 QWEN3_06B = dict(hidden_size=1024, intermediate_size=3072, num_hidden_layers=28, num_attention_heads=16,
                  num_key_value_heads=8, head_dim=128, vocab_size=151936, max_position_embeddings=40960,
                  rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=True)
@@ -123,11 +123,11 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--model", default="8b", choices=sorted(MODELS),
-                    help="the sizes: 8b is the benchmark configuration, 0.6b and 32b the other two of the baseline")
+                    help="the sizes: 8b is the benchmark configuration, 0.6b and 32b the other two the reference is quoted on")
     ap.add_argument("--layers", type=int, default=None,
                     help="fewer layers than the model has (named in the record) if memory or time needs it")
     ap.add_argument("--mixed", action="store_true",
-                    help="also the mixed run of the baseline's 0.6B configuration: 64 requests, prompts of 16 to "
+                    help="also the mixed run that goes with the 0.6B sizes: 64 requests, prompts of 16 to "
                          "1024 tokens, 256 outputs each at temperature 0.6, budget 2048, through LLM.generate")
     ap.add_argument("--skip-points", action="store_true", help="leave out the batch 1 and 64 points")
     ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "e2e", "mixed"],
