@@ -97,3 +97,46 @@ def test_overlapped_scheduling_changes_no_token(tmp_path, cpu_ops, blocks, budge
         assert o == full[:len(o)] and (len(o) == 14 or o[-1] in eos)
     assert ahead_outs == plain_outs
     assert ahead_counters.generated_tokens == plain_counters.generated_tokens == sum(map(len, plain_outs))
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2, 3, 8])
+def test_overlapped_scheduling_under_random_workloads(tmp_path, cpu_ops, seed):
+    """Random prompts, lengths, limits, pool sizes, budgets and end-of-sequence tokens: the
+    engine that schedules ahead gives the tokens of the one that does not and gives every page
+    back.  (A request that ends on an end-of-sequence token holds its pages one step longer, so
+    the order in which the others are admitted and finish may differ.)"""
+    import random
+    from tiny_llm_infer_b200 import LLM, SamplingParams
+    rng = random.Random(seed)
+    folder = make_folder(TINIES["A"], tmp_path / "m")
+    n = rng.randint(3, 7)
+    prompts = [prompt(100 * seed + i, rng.randint(1, 40), 256) for i in range(n)]
+    if rng.random() < 0.5:
+        prompts[-1] = prompts[0][:rng.randint(1, len(prompts[0]))] + prompts[-1][:5]     # a shared beginning
+    params = [SamplingParams(max_tokens=rng.randint(1, 16), temperature=rng.choice([0.0, 0.8]),
+                             top_p=rng.choice([1.0, 0.7]), seed=rng.randint(1, 10 ** 6)) for _ in range(n)]
+    blocks, budget, seqs = rng.randint(5, 12), rng.choice([4, 16, 64]), rng.randint(1, 4)
+    eos = frozenset(rng.sample(range(256), rng.randint(0, 60)))
+
+    def run(overlap):
+        llm = LLM(str(folder), dtype="float32", max_model_len=64, num_kv_blocks=blocks, block_size=16,
+                  max_num_batched_tokens=budget, max_num_seqs=seqs, device="cpu", overlap_scheduling=overlap)
+        llm.engine.eos = eos
+        ids = [llm.engine.add_request(p, s) for p, s in zip(prompts, params)]
+        order, results = [], {}
+        while not llm.engine.is_finished():
+            for r in llm.engine.step():
+                order.append(r.request_id)
+                results[r.request_id] = r.token_ids
+        llm.cache.audit()
+        assert llm.cache.free_pages() == {None: blocks} and llm.cache.free_slots == seqs
+        assert llm.engine._ahead is None
+        for i, s in zip(ids, params):
+            out = results[i]
+            assert 1 <= len(out) <= s.max_tokens and all(0 <= t < 256 for t in out)
+            assert len(out) == s.max_tokens or out[-1] in eos
+            assert not any(t in eos for t in out[:-1])
+        return [results[i] for i in ids], order, llm.engine.counters.steps
+
+    ahead, plain_run = run(True), run(False)
+    assert ahead[0] == plain_run[0] and sorted(ahead[1]) == sorted(plain_run[1])
