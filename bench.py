@@ -289,7 +289,8 @@ def main() -> int:
         bucket = 1
         while bucket < batch:
             bucket *= 2
-        h2d = 4 * bucket * 4 + batch * 8 + batch * 8         # rows' ids/positions/slots/wanted, sampling params, keys
+        # rows' ids/positions/slots/wanted, where the tokens sampled by the step before go, sampling params, keys
+        h2d = (4 * bucket + 2 * batch) * 4 + batch * 8 + batch * 8
         return batch * steps / elapsed, h2d, batch * 4
 
     e2e = None

@@ -14,7 +14,7 @@ import torch
 from tiny_llm_infer_b200 import ops
 
 NAMES = ["embedding", "add_rmsnorm", "swiglu", "cast", "qk_norm_rope_store", "paged_attention",
-         "sample", "linear", "linear_swiglu", "interleave_gate_up"]
+         "sample", "linear", "linear_swiglu", "interleave_gate_up", "feed_tokens"]
 
 
 def install(monkeypatch):
@@ -53,6 +53,10 @@ def swiglu(gate_up, out, interleaved=False):
 
 def cast(src, dtype):
     return src.to(dtype)
+
+
+def feed_tokens(ids, places, rows, sampled):
+    ids[places.long()] = sampled[rows.long()]
 
 
 def linear(x, weight, out_dtype=None):

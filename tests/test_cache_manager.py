@@ -272,3 +272,31 @@ def test_try_reserve_is_reserve_or_nothing():
     assert not m.try_reserve("a", 65)                   # beyond the longest sequence
     m.commit("a", 12)
     m.audit()
+
+
+def test_a_page_with_a_token_still_to_be_told_waits_for_its_hash():
+    """commit() with a negative token (computed on the device, not yet known on the host): the
+    page is not hashed, so nobody can share it; fill_token() tells it, and the chain goes on
+    through every page that was waiting behind it."""
+    cm = prefix_manager(pages=16)
+    stem = [5, 6, 7, 8, 9, 10, 11]
+    cm.admit("a", stem)
+    cm.reserve("a", 7)
+    cm.commit("a", 7, stem)                               # one full page hashed, three tokens of the next
+    cm.reserve("a", 9)
+    cm.commit("a", 9, [-1, 13])                           # position 7 unknown: page 1 is full but waits
+    cm.admit("b", stem + [12, 13, 1])
+    assert cm.computed("b") == 4                          # only page 0 is found
+    cm.release("b")
+    cm.reserve("a", 12)
+    cm.commit("a", 12, [14, 15, 16])                      # page 2 is full too, behind the waiting one
+    cm.fill_token("a", 7, 12)
+    cm.admit("c", stem + [12, 13, 14, 15, 16, 2])
+    assert cm.computed("c") == 12                         # pages 0, 1 and 2
+    cm.fill_token("a", 7, 99)                             # told once: a second telling changes nothing
+    cm.fill_token("gone", 0, 1)                           # nor does one for a request that is not there
+    cm.audit()
+    for r in ("a", "c"):
+        cm.release(r)
+    cm.audit()
+    assert cm.free_pages() == {None: 16}

@@ -84,7 +84,7 @@ def test_overlapped_scheduling_changes_no_token(tmp_path, cpu_ops, blocks, budge
         outs = [o.token_ids for o in llm.generate(prompts, params)]
         llm.cache.audit()
         assert llm.cache.free_pages() == {None: blocks} and llm.cache.free_slots == 3
-        assert llm.engine._ahead is None and llm.engine.is_finished()
+        assert not llm.engine._flying and llm.engine.is_finished()
         return outs, llm.engine.counters
 
     free_run, _ = run(False, ())
@@ -130,7 +130,7 @@ def test_overlapped_scheduling_under_random_workloads(tmp_path, cpu_ops, seed):
                 results[r.request_id] = r.token_ids
         llm.cache.audit()
         assert llm.cache.free_pages() == {None: blocks} and llm.cache.free_slots == seqs
-        assert llm.engine._ahead is None
+        assert not llm.engine._flying
         for i, s in zip(ids, params):
             out = results[i]
             assert 1 <= len(out) <= s.max_tokens and all(0 <= t < 256 for t in out)

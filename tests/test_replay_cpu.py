@@ -88,3 +88,13 @@ def test_a_step_prepared_ahead_with_a_late_token(tmp_path, cpu_ops):
     assert torch.equal(got, want)
     assert late[0].tokens[7] == a[19] and runner.cache.computed("a") == 20 and runner.cache.computed("b") == 9
     runner.cache.audit()
+    # the same with the tokens still on the device, as rows of what a step before has sampled
+    third = fresh()
+    third.step([StepEntry("a", a[:12], []), StepEntry("b", b[:8], [])])
+    late = [StepEntry("a", a[12:19] + [-1], [7], late=7), StepEntry("b", [-1], [0], late=0)]
+    sampled = torch.tensor([77, b[8], 5, a[19]], dtype=torch.int32)
+    with pytest.raises(StepError, match="rows were named"):
+        third.run(third.prepare(late), late_source=(sampled, [3]))
+    got = third.run(third.prepare(late), late_source=(sampled, [3, 1]))
+    assert torch.equal(got, want)
+    assert late[0].tokens[7] == -1 and third.cache.computed("a") == 20       # the host has not seen them

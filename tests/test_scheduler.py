@@ -163,14 +163,15 @@ def test_prefix_cache_starts_a_prompt_behind_what_is_shared():
     assert cache.free_pages() == {None: 16} and cache.prefix_hit_pages == 3
 
 
-def test_a_plan_made_ahead_of_the_tokens():
-    """advance() at the launch of a step, the next plan made before its tokens are known,
-    resolve() when they are: lengths count the PENDING token, a request at its max_tokens
-    is out of the next plan and its pages are free for it, and one that ends on an
-    end-of-sequence token keeps what the next plan holds for it until that plan is launched."""
+def test_steps_launched_ahead_of_their_tokens():
+    """advance() at the launch of a step, the next step planned and launched before the first
+    one's tokens are known, resolve() in the order of the launches: lengths count the PENDING
+    tokens (two per request for a while), a request at its max_tokens is out of the next plan,
+    and one that ends on an end-of-sequence token drops the PENDING token of the step launched
+    meanwhile, whose row has run for nothing."""
     from tiny_llm_infer_b200.engine.scheduler import PENDING
     sched, cache = make(pages=8, budget=32, page=8)
-    a = Sequence(1, list(range(5)), SamplingParams(max_tokens=2, ignore_eos=True))
+    a = Sequence(1, list(range(5)), SamplingParams(max_tokens=3, ignore_eos=True))
     b = Sequence(2, list(range(7)), SamplingParams(max_tokens=50))
     sched.add(a)
     sched.add(b)
@@ -183,21 +184,20 @@ def test_a_plan_made_ahead_of_the_tokens():
 
     first = sched.schedule()
     launch(first)
-    assert a.tokens[-1] == PENDING and a.pending and len(a) == 6 and a.num_cached_tokens == 5
-    second = sched.schedule()                        # made while `first` runs
+    assert a.tokens[-1] == PENDING and a.pending == 1 and len(a) == 6 and a.num_cached_tokens == 5
+    second = sched.schedule()                        # made and launched while `first` runs
     assert shape(second) == [(1, 5, 1, False), (2, 7, 1, False)]
-    assert sched.resolve(first, [11, 12], lambda t: t == 99, held={1, 2}) == []
-    assert a.tokens[-1] == 11 and b.tokens[-1] == 12 and not a.pending
-    launch(second)                                   # a reaches max_tokens: over, pages back at once
-    assert a.status is Status.FINISHED and not cache.has(1) and cache.has(2)
+    launch(second)
+    assert a.pending == 2 and a.tokens[-2:] == [PENDING, PENDING] and len(b) == 9
+    assert sched.resolve(first, [11, 12], lambda t: t == 99) == []
+    assert a.tokens[-2:] == [11, PENDING] and b.tokens[-2:] == [12, PENDING] and a.pending == 1
     third = sched.schedule()
-    assert shape(third) == [(2, 8, 1, False)]
-    done = sched.resolve(second, [13, 99], lambda t: t == 99, held={2})
-    assert [s.id for s in done] == [1, 2] and a.completion == [11, 13] and b.completion == [12, 99]
-    assert b.status is Status.FINISHED and cache.has(2)          # the third plan still holds it
-    assert sched.is_finished()
-    launch(third)                                    # its row runs for nothing; pages back now
-    assert not cache.has(2) and len(b) == 9 and not b.pending
-    assert sched.resolve(third, [5], lambda t: False) == []
+    launch(third)                                    # a reaches max_tokens with it: over, pages back at once
+    assert a.status is Status.FINISHED and not cache.has(1) and cache.has(2) and a.pending == 2
+    done = sched.resolve(second, [13, 99], lambda t: t == 99)     # b ends here, with `third` under way
+    assert [s.id for s in done] == [2] and b.completion == [12, 99] and b.pending == 0
+    assert b.status is Status.FINISHED and not cache.has(2) and sched.is_finished()
+    done = sched.resolve(third, [14, 5], lambda t: t == 99)       # b's row ran for nothing
+    assert [s.id for s in done] == [1] and a.completion == [11, 13, 14] and b.completion == [12, 99]
     cache.audit()
     assert cache.free_pages() == {None: 8}

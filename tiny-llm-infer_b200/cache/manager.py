@@ -416,7 +416,9 @@ class CacheManager:
     def commit(self, request: Hashable, computed_len: int, tokens: Optional[Sequence[int]] = None) -> None:
         """Tokens [0, computed_len) are now in the cache.  Windowed groups give back the
         pages that no later query can read.  ``tokens``: the ones this step added, for the
-        prefix cache (a request whose tokens are not told stops being hashed)."""
+        prefix cache (a request whose tokens are not told stops being hashed); a negative one
+        stands for a token that is computed but not known on the host yet: its page waits for
+        ``fill_token`` before it gets a hash."""
         slot = self._slot_of[request]
         if computed_len > self._reserved[slot]:
             raise CacheError("more tokens computed than pages were reserved for")
@@ -441,6 +443,8 @@ class CacheManager:
         while (self._hashed[slot] + 1) * ps <= len(known):
             i = self._hashed[slot]
             page_tokens = tuple(known[i * ps:(i + 1) * ps])
+            if min(page_tokens) < 0:           # a token of this page is still to be told
+                break
             h = self._page_hash(self._chain[slot], page_tokens)
             page = int(g.table[slot, i])
             if h not in g.by_hash:             # the first page with this content stands for it
@@ -448,6 +452,16 @@ class CacheManager:
                 g.hash_of[page], g.tokens_of[page] = h, page_tokens
                 g.by_hash[h] = page
             self._hashed[slot], self._chain[slot] = i + 1, h
+
+    def fill_token(self, request: Hashable, position: int, token: int) -> None:
+        """The token at ``position`` of the request, committed as unknown, is ``token``."""
+        slot = self._slot_of.get(request)
+        if slot is None or not self.prefix_active:
+            return
+        known = self._tokens[slot]
+        if known is not None and position < len(known) and known[position] < 0:
+            known[position] = int(token)
+            self._hash_full_pages(slot)
 
     def release(self, request: Hashable) -> None:
         """The request has ended (or is preempted): all it holds is given back."""

@@ -239,6 +239,11 @@ __global__ void swiglu_vec_kernel(const T* gu, T* out, int inter, int interleave
     }
 }
 
+__global__ void feed_tokens_kernel(int* ids, const int* places, const int* rows, const int* sampled, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) ids[places[i]] = sampled[rows[i]];
+}
+
 template <typename TS, typename TD>
 __global__ void cast_kernel(const TS* __restrict__ src, TD* __restrict__ dst, size_t n) {
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -350,6 +355,15 @@ int tllm_swiglu(const void* gate_up, void* out, int dtype, int tokens, int inter
             launch_pdl(kPdlSwiglu, swiglu_kernel<float>, dim3(grid), dim3(block), 0, stream, (const float*)gate_up, (float*)out, inter, interleaved, total);
     }
     return finish_launch("swiglu");
+}
+
+// ids[places[i]] = sampled[rows[i]] for i < n: tokens that a step still being sampled from gives
+// the next step, without the host in between.  All four are device arrays of int32.
+int tllm_feed_tokens(int* ids, const int* places, const int* rows, const int* sampled, int n, cudaStream_t stream) {
+    TLLM_REQUIRE(n >= 0 && ids && places && rows && sampled, "feed_tokens: bad arguments");
+    if (n == 0) return 0;
+    feed_tokens_kernel<<<(n + 127) / 128, 128, 0, stream>>>(ids, places, rows, sampled, n);
+    return finish_launch("feed_tokens");
 }
 
 int tllm_cast(const void* src, int src_dtype, void* dst, int dst_dtype, long long n,

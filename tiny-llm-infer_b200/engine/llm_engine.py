@@ -52,11 +52,13 @@ class EngineCounters:
 
 
 @dataclass
-class _PreparedPlan:
+class _Step:
     plan: BatchPlan
     step: PreparedStep
     rows: List[tuple]          # (temperature, top_p, draw key) per sampled row
     row_of: List[int]          # the plan's sequence of each sampled row
+    late_of: List[int]         # per late token of the prepared step, the request it belongs to
+    ticket: int = -1           # of the sampler, once launched
 
 
 class LLMEngine:
@@ -74,7 +76,7 @@ class LLMEngine:
         self._next_id = 1
         self._lock = threading.Lock()      # add_request may come from another thread
         self.overlap = overlap
-        self._ahead: Optional[_PreparedPlan] = None      # the next step, laid out while this one ran
+        self._flying: List[_Step] = []                 # launched, tokens not read yet (at most two)
         self._deferred: Optional[Exception] = None
 
     # ------------------------------------------------------------------ requests
@@ -102,25 +104,21 @@ class LLMEngine:
 
     def is_finished(self) -> bool:
         with self._lock:
-            done = self.scheduler.is_finished()
-        if done and self._ahead is not None:       # made ahead for requests that have ended since
-            self._discard(self._ahead)
-            self._ahead = None
-        return done
+            return self.scheduler.is_finished() and not self._flying
 
     @property
     def total_generated_tokens(self) -> int:
         return self.counters.generated_tokens
 
     # ------------------------------------------------------------------ one step
-    def _prepare(self) -> Optional["_PreparedPlan"]:
+    def _prepare(self) -> Optional["_Step"]:
         """Ask the scheduler for a plan, flatten it and let the runner lay it out.  A request
         whose last token is still being sampled brings it as a late token."""
         with self._lock:
             plan = self.scheduler.schedule()
         if not plan.sequences:
             return None
-        entries, rows, row_of = [], [], []
+        entries, rows, row_of, late_of = [], [], [], []
         for item in plan.sequences:
             seq = item.sequence
             end = item.token_start + item.token_count
@@ -131,55 +129,58 @@ class LLMEngine:
                 rows.append((seq.sampling.temperature, seq.sampling.top_p,
                              draw_key(seq.seed, seq.num_completion_tokens)))
                 row_of.append(len(entries) - 1)
-        return _PreparedPlan(plan, self.runner.prepare(entries), rows, row_of)
+        step = self.runner.prepare(entries)
+        for index, _ in step.late:                   # whose token each late place waits for
+            late_of.append(plan.sequences[index].sequence.id)
+        return _Step(plan, step, rows, row_of, late_of)
 
-    def _discard(self, ahead: "_PreparedPlan") -> None:
-        """A plan made ahead that is not going to run: every request in it has ended."""
-        self.runner.abandon(ahead.step)
+    def _launch(self, step: "_Step", before: Optional["_Step"]) -> None:
+        """Upload and launch; the late tokens are rows of what ``before``, the step launched
+        last and not read yet, samples: they stay on the device."""
+        if step.late_of:
+            row = {before.plan.sequences[i].sequence.id: r for r, i in enumerate(before.row_of)}
+            source = (self.sampler.device_tokens(before.ticket), [row[request] for request in step.late_of])
+            logits = self.runner.run(step.step, late_source=source)
+        else:
+            logits = self.runner.run(step.step)
+        step.ticket = self.sampler.launch(logits, step.rows)
         with self._lock:
-            for item in ahead.plan.sequences:
-                if self.runner.cache.has(item.sequence.id):
-                    self.runner.cache.release(item.sequence.id)
+            self.scheduler.advance(step.plan)
+        self._flying.append(step)
 
     def step(self) -> List[GenerationResult]:
-        """One step: launch it, and while the GPU runs it, schedule and lay out the next
-        (``overlap``), whose only open values are the tokens this step samples; then read
-        the tokens and book them."""
+        """One step's results.  The steps form a short queue on the GPU: before the tokens of
+        the oldest launched step are read, the next one is scheduled, laid out and launched
+        too (``overlap``), with the tokens it needs from the step before taken on the device;
+        then the oldest step's tokens are read and booked.  So the GPU goes from one step to
+        the next without waiting for the host, and the host learns every token one step late."""
         if self._deferred is not None:
             error, self._deferred = self._deferred, None
             raise error
-        current, self._ahead = self._ahead, None
-        if current is not None and all(i.sequence.status is Status.FINISHED for i in current.plan.sequences):
-            self._discard(current)
-            current = None
-        if current is None:
-            current = self._prepare()
-            if current is None:
+        if not self._flying:
+            first = self._prepare()
+            if first is None:
                 return []
-        plan = current.plan
-        late = []
-        for index, _ in current.step.late:
-            item = plan.sequences[index]
-            late.append(item.sequence.tokens[item.token_start + current.step.entries[index].late])
-        logits = self.runner.run(current.step, late)
-        self.sampler.launch(logits, current.rows)
-        with self._lock:
-            self.scheduler.advance(plan)
-        if self.overlap:
+            self._launch(first, None)
+        if self.overlap and len(self._flying) == 1:
             try:
-                self._ahead = self._prepare()
+                ahead = self._prepare()
+                if ahead is not None:
+                    self._launch(ahead, self._flying[-1])
             except Exception as error:             # belongs to the next step: raised when it is asked for
                 self._deferred = error
-        tokens = self.sampler.fetch()
+        current = self._flying.pop(0)
+        plan = current.plan
+        tokens = self.sampler.fetch(current.ticket)
         self.runner.check_kernels()
         sampled = [-1] * len(plan.sequences)
         generated = 0
         for idx, tok in zip(current.row_of, tokens):
             sampled[idx] = tok
-            generated += plan.sequences[idx].sequence.pending
-        held = () if self._ahead is None else {i.sequence.id for i in self._ahead.plan.sequences}
+            item = plan.sequences[idx]
+            generated += item.pending_index is not None and item.pending_index < len(item.sequence.tokens)
         with self._lock:
-            finished = self.scheduler.resolve(plan, sampled, lambda t: t in self.eos, held)
+            finished = self.scheduler.resolve(plan, sampled, lambda t: t in self.eos)
         c = self.counters
         c.steps += 1
         c.generated_tokens += generated

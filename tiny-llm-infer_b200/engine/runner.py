@@ -250,21 +250,41 @@ class ModelRunner:
         return prepared
 
     @torch.no_grad()
-    def run(self, prepared: PreparedStep, late_tokens: Sequence[int] = ()) -> torch.Tensor:
-        """Upload and launch a prepared step; ``late_tokens`` in the order of ``prepared.late``."""
+    def run(self, prepared: PreparedStep, late_tokens: Sequence[int] = (),
+            late_source: Optional[Tuple[torch.Tensor, Sequence[int]]] = None) -> torch.Tensor:
+        """Upload and launch a prepared step.  Its late tokens are given either as values
+        (``late_tokens``, in the order of ``prepared.late``) or, still being sampled by the step
+        before, as ``late_source`` = (int32 device tensor of that step's sampled tokens, the row
+        of it that each late token is): then they go from there into this step's token ids on
+        the device, the host never waits for them, and the entries keep a negative token in
+        their place."""
         if prepared is not self._prepared:
             raise StepError("run() takes the step that prepare() returned last")
         self._prepared = None                      # whatever happens below, the host buffer is free again
-        if len(late_tokens) != len(prepared.late):
-            raise StepError(f"{len(prepared.late)} late tokens are open, {len(late_tokens)} were given")
         host = self._host.numpy()
-        for (index, place), token in zip(prepared.late, late_tokens):
-            e = prepared.entries[index]
-            if not 0 <= int(token) < self.vocab:
-                raise StepError(f"request {e.request!r}: token id outside [0, {self.vocab})")
-            host[place] = int(token)
-            e.tokens[e.late] = int(token)          # what commit() hashes
-        self._upload(prepared.upload)
+        n_late, words = len(prepared.late), prepared.upload
+        if late_source is not None:
+            sampled, rows = late_source
+            if len(rows) != n_late:
+                raise StepError(f"{n_late} late tokens are open, {len(rows)} rows were named")
+            if words + 2 * n_late > host.shape[0]:
+                raise StepError("no room for the late tokens' places in the step's buffer")
+            host[words:words + n_late] = [place for _, place in prepared.late]
+            host[words + n_late:words + 2 * n_late] = rows
+            words += 2 * n_late
+        else:
+            if len(late_tokens) != n_late:
+                raise StepError(f"{n_late} late tokens are open, {len(late_tokens)} were given")
+            for (index, place), token in zip(prepared.late, late_tokens):
+                e = prepared.entries[index]
+                if not 0 <= int(token) < self.vocab:
+                    raise StepError(f"request {e.request!r}: token id outside [0, {self.vocab})")
+                host[place] = int(token)
+                e.tokens[e.late] = int(token)          # what commit() hashes
+        self._upload(words)
+        if late_source is not None and n_late:
+            d, at = self._dev, prepared.upload
+            ops.feed_tokens(d, d[at:at + n_late], d[at + n_late:at + 2 * n_late], late_source[0])
         if prepared.graph_key is not None:
             logits = self._run_graph(prepared)
         else:

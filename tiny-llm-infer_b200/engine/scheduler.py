@@ -24,8 +24,8 @@ slot at any time (the reference bounds the requests in one step); the prefix cac
 (engine/src/block_manager.cpp:97-125: a prompt's full pages that are already in the cache
 are shared, and its first portion starts behind them) lives in the cache manager too;
 the booking of a step comes in two halves (``advance`` when it is launched, ``resolve`` when
-its tokens are known, ``postprocess`` = both), so that the engine can make the next plan
-while the step still runs.
+its tokens are known, ``postprocess`` = both), so that the engine can make and launch the
+next step while this one still runs.
 """
 from __future__ import annotations
 
@@ -80,7 +80,7 @@ class Sequence:
         self.num_cached_tokens = 0
         self.num_scheduled_tokens = 0
         self.preemptions = 0
-        self.pending = False          # the last of ``tokens`` is PENDING
+        self.pending = 0              # how many of the last ``tokens`` are PENDING
 
     def __len__(self) -> int:
         return len(self.tokens)
@@ -103,6 +103,8 @@ class ScheduledSequence:
     # a row is sampled for a decode token and for the portion that ends the sequence
     # (engine/src/llm_engine.cpp:178-182); fixed when the plan is made
     samples: bool = False
+    # where in the request's tokens the sampled token goes (set when the step is launched)
+    pending_index: Optional[int] = None
 
 
 @dataclass
@@ -210,58 +212,61 @@ class Scheduler:
         self.advance(plan)
         return self.resolve(plan, sampled, is_eos)
 
-    # The booking in two halves, so that the next step can be scheduled and laid out while this
-    # one still runs: what a step changes is known when it is launched, but for the values of
-    # the tokens it samples and whether one of them ends its request.
+    # The booking in two halves, so that the next step can be scheduled, laid out and even
+    # launched while this one still runs: what a step changes is known when it is launched, but
+    # for the values of the tokens it samples and whether one of them ends its request.
 
     def advance(self, plan: BatchPlan) -> None:
         """The step has been launched: its tokens count as computed, every request that
         samples grows by a PENDING token, and one that reaches its ``max_tokens`` with it is
         over (its pages are free for the next plan; work already launched comes before
-        anything later on the stream).  A request that ended after this plan was made (see
-        ``resolve``) gives back here what the plan held for it."""
+        anything later on the stream)."""
         for item in plan.sequences:
             seq = item.sequence
-            if seq.status is Status.FINISHED:
-                if self.cache.has(seq.id):
-                    self.cache.release(seq.id)
-                continue
             seq.num_cached_tokens += seq.num_scheduled_tokens
             seq.num_scheduled_tokens = 0
             if not item.samples:
                 continue
             seq.tokens.append(PENDING)
-            seq.pending = True
+            seq.pending += 1
+            item.pending_index = len(seq.tokens) - 1
             if seq.num_completion_tokens >= seq.sampling.max_tokens:
                 seq.status = Status.FINISHED
                 self.cache.release(seq.id)
                 self.running.remove(seq)
 
-    def resolve(self, plan: BatchPlan, sampled: Seq[int], is_eos: Callable[[int], bool],
-                held: Seq[Hashable] = ()) -> List[Sequence]:
+    def resolve(self, plan: BatchPlan, sampled: Seq[int], is_eos: Callable[[int], bool]) -> List[Sequence]:
         """The step's tokens are here: ``sampled[i]`` is the token of ``plan.sequences[i]``
-        (ignored where it sampled nothing).  Returns the requests that finished.  A request
-        that ends on an end-of-sequence token may already stand in a plan made meanwhile
-        (its id in ``held``): then it keeps its pages until that plan is launched, where its
-        row runs for nothing and ``advance`` frees them."""
+        (ignored where it sampled nothing).  Returns the requests that are finished with it.
+        Steps are resolved in the order of their launch.  A request that ends on an
+        end-of-sequence token may have a row in a step launched meanwhile: that row has run
+        for nothing, its PENDING token is dropped here and its result is passed over when that
+        step is resolved; the pages can go back at once, since whatever is launched later
+        comes later on the stream."""
         if len(sampled) != len(plan.sequences):
             raise SchedulerError("The model runner returned the wrong number of sampled tokens.")
         finished = []
         for item, token in zip(plan.sequences, sampled):
-            seq = item.sequence
-            if not (item.samples and seq.pending):
+            seq, index = item.sequence, item.pending_index
+            if index is None:
+                continue
+            item.pending_index = None
+            if index >= len(seq.tokens):               # the request ended on an earlier token
                 continue
             if token < 0:
                 raise SchedulerError("The model runner did not return a token for a completed step.")
-            seq.tokens[-1] = int(token)
-            seq.pending = False
-            if seq.status is Status.FINISHED:          # by its length, in advance()
-                finished.append(seq)
-            elif not seq.sampling.ignore_eos and is_eos(int(token)):
-                # RUNNING, or WAITING again if the plan made meanwhile preempted it
-                (self.running if seq.status is Status.RUNNING else self.waiting).remove(seq)
-                seq.status = Status.FINISHED
-                if seq.id not in held and self.cache.has(seq.id):
+            seq.tokens[index] = int(token)
+            seq.pending -= 1
+            self.cache.fill_token(seq.id, index, int(token))
+            if not seq.sampling.ignore_eos and is_eos(int(token)):
+                del seq.tokens[index + 1:]             # PENDING tokens of steps launched since
+                seq.pending = 0
+                if seq.status is not Status.FINISHED:  # RUNNING, or WAITING again after a preemption
+                    (self.running if seq.status is Status.RUNNING else self.waiting).remove(seq)
+                    seq.status = Status.FINISHED
+                if self.cache.has(seq.id):
                     self.cache.release(seq.id)
+                finished.append(seq)
+            elif seq.status is Status.FINISHED and seq.pending == 0:     # by its length, in advance()
                 finished.append(seq)
         return finished

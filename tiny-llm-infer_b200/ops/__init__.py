@@ -68,6 +68,7 @@ def _declare(h) -> None:
         "tllm_add_rmsnorm": [vp, vp, vp, i32, f32, vp, i32, vp, i32, i32, vp],
         "tllm_swiglu": [vp, vp, i32, i32, i32, i32, vp],
         "tllm_cast": [vp, i32, vp, i32, i64, vp],
+        "tllm_feed_tokens": [vp, vp, vp, vp, i32, vp],
         "tllm_qk_norm_rope_store": [vp, vp, vp, i32, f32, vp, i32, vp, vp, vp, i32, vp, i32, vp,
                                     i32, i32, i32, i32, i32, i32, vp],
         "tllm_paged_attention_general": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32,
@@ -187,6 +188,14 @@ def cast(src: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     dst = torch.empty_like(src, dtype=dtype)
     _check(lib().tllm_cast(_p(src), _dt(src), _p(dst), _dt(dst), src.numel(), _stream()), "cast")
     return dst
+
+
+def feed_tokens(ids: torch.Tensor, places: torch.Tensor, rows: torch.Tensor, sampled: torch.Tensor) -> None:
+    """ids[places[i]] = sampled[rows[i]] (all int32, on the device): the tokens that the step before
+    is still sampling go into this step's token ids without passing through the host."""
+    _cuda(ids, places, rows, sampled)
+    assert ids.dtype == places.dtype == rows.dtype == sampled.dtype == torch.int32 and places.numel() == rows.numel()
+    _check(lib().tllm_feed_tokens(_p(ids), _p(places), _p(rows), _p(sampled), places.numel(), _stream()), "feed_tokens")
 
 
 def qk_norm_rope_store(qkv: torch.Tensor, q_gain, k_gain, eps: float, inv_freq, rotary_dim: int,

@@ -33,60 +33,75 @@ def draw_key(request_seed: int, output_index: int) -> int:
 
 
 class Sampler:
+    """Two sets of buffers take turns, so that a draw can be started while the one before it has
+    not been read yet (the engine launches a step before it fetches the tokens of the last)."""
+
     def __init__(self, device, max_rows: int):
         self.device = device
         cuda = torch.device(device).type == "cuda"
-        self._params_host = torch.empty((max_rows, 2), dtype=torch.float32)
-        self._seeds_host = torch.empty(max_rows, dtype=torch.int64)
+        self._sets = [self._buffers(device, max_rows, cuda) for _ in range(2)]
+        self._turn = 0
+
+    @staticmethod
+    def _buffers(device, max_rows: int, cuda: bool) -> dict:
+        b = {"params_host": torch.empty((max_rows, 2), dtype=torch.float32),
+             "seeds_host": torch.empty(max_rows, dtype=torch.int64),
+             "out_host": torch.empty(max_rows, dtype=torch.int32)}
         if cuda:
-            self._params_host = self._params_host.pin_memory()
-            self._seeds_host = self._seeds_host.pin_memory()
+            for key in ("params_host", "seeds_host", "out_host"):
+                b[key] = b[key].pin_memory()
         # numpy views of the pinned buffers: filled in one go per step, not element by element
-        self._params_np = self._params_host.numpy()
-        self._seeds_np = self._seeds_host.numpy().view(np.uint64)
-        self._params = torch.empty((max_rows, 2), dtype=torch.float32, device=device)
-        self._seeds = torch.empty(max_rows, dtype=torch.int64, device=device)
-        self._out = torch.empty(max_rows, dtype=torch.int32, device=device)
-        self._out_host = torch.empty(max_rows, dtype=torch.int32)
-        self._done = None
-        if cuda:
-            self._out_host = self._out_host.pin_memory()
-            self._done = torch.cuda.Event()
-        self._launched = 0
+        b["params_np"] = b["params_host"].numpy()
+        b["seeds_np"] = b["seeds_host"].numpy().view(np.uint64)
+        b["params"] = torch.empty((max_rows, 2), dtype=torch.float32, device=device)
+        b["seeds"] = torch.empty(max_rows, dtype=torch.int64, device=device)
+        b["out"] = torch.empty(max_rows, dtype=torch.int32, device=device)
+        b["done"] = torch.cuda.Event() if cuda else None
+        b["rows"] = 0
+        return b
 
     def sample(self, logits: torch.Tensor, rows: Sequence[Tuple[float, float, int]]) -> List[int]:
         """``rows[i]`` = (temperature, top_p, draw key) for ``logits[i]``; token ids on the host."""
-        self.launch(logits, rows)
-        return self.fetch()
+        return self.fetch(self.launch(logits, rows))
 
-    def launch(self, logits: torch.Tensor, rows: Sequence[Tuple[float, float, int]]) -> None:
-        """Start the draw and the copy of its result to the host; ``fetch`` waits for it.  The
-        host is free in between (the engine prepares its next step there)."""
+    def launch(self, logits: torch.Tensor, rows: Sequence[Tuple[float, float, int]]) -> int:
+        """Start the draw and the copy of its result to the host; returns the ticket that
+        ``fetch`` and ``device_tokens`` take.  A ticket is good until the draw after the next."""
         n = len(rows)
         assert logits.shape[0] == n
-        self._launched = n
+        ticket = self._turn
+        self._turn ^= 1
+        b = self._sets[ticket]
+        b["rows"] = n
         if n == 0:
-            return
+            return ticket
         temps = [r[0] for r in rows]
         top_ps = [r[1] for r in rows]
-        self._params_np[:n, 0] = temps
-        self._params_np[:n, 1] = top_ps
-        self._seeds_np[:n] = np.fromiter((r[2] & _M for r in rows), dtype=np.uint64, count=n)
-        self._params[:n].copy_(self._params_host[:n], non_blocking=True)
-        self._seeds[:n].copy_(self._seeds_host[:n], non_blocking=True)
+        b["params_np"][:n, 0] = temps
+        b["params_np"][:n, 1] = top_ps
+        b["seeds_np"][:n] = np.fromiter((r[2] & _M for r in rows), dtype=np.uint64, count=n)
+        b["params"][:n].copy_(b["params_host"][:n], non_blocking=True)
+        b["seeds"][:n].copy_(b["seeds_host"][:n], non_blocking=True)
         nucleus = any(t > 1e-6 and p < 1.0 for t, p in zip(temps, top_ps))
-        ops.sample(logits, self._params[:n], self._seeds[:n], self._out[:n], any_nucleus=nucleus)
-        if self._done is None:
-            self._out_host = self._out.cpu()           # no stream to wait for
+        ops.sample(logits, b["params"][:n], b["seeds"][:n], b["out"][:n], any_nucleus=nucleus)
+        if b["done"] is None:
+            b["out_host"][:n].copy_(b["out"][:n])       # no stream to wait for
         else:
-            self._out_host[:n].copy_(self._out[:n], non_blocking=True)
-            self._done.record()
+            b["out_host"][:n].copy_(b["out"][:n], non_blocking=True)
+            b["done"].record()
+        return ticket
 
-    def fetch(self) -> List[int]:
+    def device_tokens(self, ticket: int) -> torch.Tensor:
+        """The int32 device tensor that the draw of this ticket writes its tokens to (row i of the
+        draw at index i)."""
+        return self._sets[ticket]["out"]
+
+    def fetch(self, ticket: int) -> List[int]:
         """Token ids of the draw that ``launch`` started."""
-        n = self._launched
+        b = self._sets[ticket]
+        n = b["rows"]
         if n == 0:
             return []
-        if self._done is not None:
-            self._done.synchronize()
-        return self._out_host[:n].tolist()
+        if b["done"] is not None:
+            b["done"].synchronize()
+        return b["out_host"][:n].tolist()
