@@ -1,15 +1,21 @@
-"""Importable name of the package whose sources live in ``tiny-llm-infer_b200/``.
+"""A small, whole, single-GPU inference engine for NVIDIA B200 (sm_100a): model folder in,
+next tokens out.  The importable name of this package is ``tiny_llm_infer_b200``.
 
-A folder name with a hyphen cannot appear in an ``import`` statement, so this
-module points its ``__path__`` at that folder and runs the folder's own
-``__init__.py``.  ``import tiny_llm_infer_b200.engine`` therefore loads
-``tiny-llm-infer_b200/engine/__init__.py``.
+Sub-packages: ``config`` (typed configurations, architecture registry), ``weights``
+(safetensors by name, random-weights mode), ``parts`` (mixers, feed-forwards, norms,
+position encodings, block arrangements), ``models`` (architectures as data, model
+assembly), ``cache`` (paged keys and values, per-request state slots), ``engine`` (step
+function, scheduler, LLMEngine), ``sampling``, ``ops`` and ``csrc`` (the CUDA kernels).
 """
-from pathlib import Path as _Path
+__version__ = "0.1.0"
 
-_SRC = _Path(__file__).resolve().parent.parent / "tiny-llm-infer_b200"
-if not (_SRC / "__init__.py").is_file():
-    raise ImportError(f"package sources not found at {_SRC}")
-__path__ = [str(_SRC)]
-__file__ = str(_SRC / "__init__.py")
-exec(compile((_SRC / "__init__.py").read_text(), __file__, "exec"))
+
+def __getattr__(name):
+    # the public names, resolved lazily so that importing the package stays cheap
+    if name in ("LLM", "LLMEngine", "EngineConfig", "GenerationResult", "SchedulerConfig"):
+        from . import engine
+        return getattr(engine, name)
+    if name == "SamplingParams":
+        from .sampling import SamplingParams
+        return SamplingParams
+    raise AttributeError(name)
