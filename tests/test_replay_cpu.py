@@ -98,3 +98,39 @@ def test_a_step_prepared_ahead_with_a_late_token(tmp_path, cpu_ops):
     got = third.run(third.prepare(late), late_source=(sampled, [3, 1]))
     assert torch.equal(got, want)
     assert late[0].tokens[7] == -1 and third.cache.computed("a") == 20       # the host has not seen them
+
+
+def test_selfcheck_ways_of_cutting_cpu(tmp_path, cpu_ops):
+    """The four ways of cutting of ``engine.selfcheck`` on tiny A with the stand-in kernels:
+    every way leaves a row at every wanted position, all agree with the plain implementation,
+    and the pool that just holds four requests ends without a page lost."""
+    from tiny_llm_infer_b200.cache import CacheManager
+    from tiny_llm_infer_b200.engine import ModelRunner, load_model, selfcheck
+    tiny = TINIES["A"]
+    folder = make_folder(tiny, tmp_path / "model")
+    cfg, w = plain.read_model(folder)
+    reqs = requests_for(tiny, (150, 41, 66, 35, 50))
+    wanted = {k: selfcheck.wanted_positions(len(v), tail=8) for k, v in reqs.items()}
+    model, _ = load_model(folder, torch.float32, "cpu")
+    pages = selfcheck.pages_for(reqs, 16)
+    cache = CacheManager(model.cache_needs(), 16, pages, max_slots=4, max_seq_len=192, dtype=torch.float32,
+                         device="cpu")
+    runner = ModelRunner(model, cache, max_batch_tokens=192)
+    cut = selfcheck.CutRunner(runner, reqs, wanted)
+    rows = cut.all_ways(seed=1)
+    cache.audit()
+    assert len(rows) == 4 * sum(len(v) for v in wanted.values())
+    want = {}
+    for name, toks in reqs.items():
+        full = plain.logits_of(cfg, w, toks).to(torch.float32)
+        for way in ("whole", "tail", "portions", "mixed"):
+            for pos in wanted[name]:
+                want[(way, name, pos)] = full[pos]
+    result = selfcheck.compare(rows, want, near_tie=1e-5)
+    assert max(result[k] for k in ("whole", "tail", "portions", "mixed")) < 2e-4, result
+    assert all(result[k + ":argmax_misses"] == 0 for k in ("whole", "tail", "portions", "mixed"))
+    assert max(selfcheck.spread_between_ways(rows).values()) < 1e-3
+    # a wrong row is seen
+    key = ("mixed", "0", wanted["0"][-1])
+    rows[key] = rows[key] + 1.0 * (torch.arange(rows[key].numel()) == 3)
+    assert selfcheck.compare(rows, want, near_tie=1e-5)["mixed"] > 0.9
