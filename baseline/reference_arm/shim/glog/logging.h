@@ -1,4 +1,4 @@
-// Stand-in for glog, enough to compile the reference for the golden run.
+// Stand-in for glog, enough to compile the reference (golden outputs of the tests, reference arm of the benchmark).
 #pragma once
 #include <cstdlib>
 #include <iostream>

@@ -115,6 +115,267 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(mhz)}
 
 
+# ---------------------------------------------------------------------- the reference arm
+REF_BIN = ROOT / "baseline" / "_ref" / "bin"
+
+
+def _unavailable(why: str) -> int:
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def _reference_binaries():
+    """The reference built by baseline/reference_arm/build.py (its sources unchanged, three stand-in
+    headers); built now if its sources are at hand and the binaries are not."""
+    need = [REF_BIN / "decode_main", REF_BIN / "model_main"]
+    if all(p.is_file() for p in need):
+        return need, None
+    import os
+    src = Path(os.environ.get("TLLM_REFERENCE", "/root/reference"))
+    if not (src / "model" / "model_main.cpp").is_file():
+        return None, (f"the reference is not built (no {REF_BIN}) and its sources are not at {src}: "
+                      "run baseline/reference_arm/build.py where they are")
+    res = subprocess.run([sys.executable, str(ROOT / "baseline" / "reference_arm" / "build.py"), "--reference", str(src)],
+                         capture_output=True, text=True)
+    if res.returncode != 0 or not all(p.is_file() for p in need):
+        return None, "building the reference failed: " + (res.stderr or res.stdout).strip().splitlines()[-1][:200]
+    return need, None
+
+
+def _write_reference_model(folder: Path, sizes: dict, seed: int = 0):
+    """config.json, tokenizer.json and model.safetensors (FP16, the reference's storage type) of the
+    given sizes with random weights N(0, 0.02) and norm gains U[0.8, 1.2], written with torch and the
+    safetensors library alone.  The reference's tokenizer must know every id it may have to print
+    (layers/src/encode.cpp:311-315): the vocabulary is t0, t1, ..."""
+    import torch
+    from safetensors.torch import save_file
+    folder.mkdir(parents=True, exist_ok=True)
+    cfg = dict(sizes, model_type="qwen3", architectures=["Qwen3ForCausalLM"], torch_dtype="float16")
+    (folder / "config.json").write_text(json.dumps(cfg))
+    vocab, hidden, inter = sizes["vocab_size"], sizes["hidden_size"], sizes["intermediate_size"]
+    q = sizes["num_attention_heads"] * sizes["head_dim"]
+    kv = sizes["num_key_value_heads"] * sizes["head_dim"]
+    (folder / "tokenizer.json").write_text(json.dumps(
+        {"model": {"vocab": {f"t{i}": i for i in range(vocab)}, "merges": []}, "added_tokens": []}))
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+
+    def normal(*shape):
+        return (torch.randn(shape, generator=gen, device="cuda", dtype=torch.float32) * 0.02).to(torch.float16).cpu()
+
+    def gain(n):
+        return (torch.rand(n, generator=gen, device="cuda") * 0.4 + 0.8).to(torch.float16).cpu()
+
+    tensors = {"model.embed_tokens.weight": normal(vocab, hidden), "model.norm.weight": gain(hidden)}
+    if not sizes.get("tie_word_embeddings"):
+        tensors["lm_head.weight"] = normal(vocab, hidden)     # present as in a real checkpoint; the reference never reads it
+    for i in range(sizes["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        tensors.update({
+            p + "input_layernorm.weight": gain(hidden), p + "post_attention_layernorm.weight": gain(hidden),
+            p + "self_attn.q_proj.weight": normal(q, hidden), p + "self_attn.k_proj.weight": normal(kv, hidden),
+            p + "self_attn.v_proj.weight": normal(kv, hidden), p + "self_attn.o_proj.weight": normal(hidden, q),
+            p + "self_attn.q_norm.weight": gain(sizes["head_dim"]), p + "self_attn.k_norm.weight": gain(sizes["head_dim"]),
+            p + "mlp.gate_proj.weight": normal(inter, hidden), p + "mlp.up_proj.weight": normal(inter, hidden),
+            p + "mlp.down_proj.weight": normal(hidden, inter)})
+    save_file(tensors, str(folder / "model.safetensors"))
+    del tensors
+    torch.cuda.empty_cache()
+
+
+def _standing_prompt_len(batch: int, steps: int, warmup: int, budget: int = 256) -> int:
+    """Longest prompt with which decode_main's requests (which keep decoding while the other prompts
+    are computed) stay inside CONTEXT until the timed steps are over."""
+    n = CONTEXT
+    while n > 1:
+        budget_steps = -(-batch * n // budget)
+        if n + warmup + steps + budget_steps + budget_steps // 8 + 16 <= CONTEXT:
+            return n
+        n -= 1
+    return 1
+
+
+def reference_arm(args, model_name: str, model_sizes: dict) -> int:
+    """The unmodified reference on the same sizes and workload: decode steps of ``--batch`` requests
+    standing at a context of about 4096 through its LLMEngine (``value`` and ``e2e``: its step() takes
+    host token ids in and gives host token ids out, so the two are one number), and its own
+    ``model_main --bench`` on 128-token prompts with 128 outputs (``points``)."""
+    import os
+    import shutil
+    import tempfile
+    if args.gpus != 1:
+        print(f"bench.py: the reference runs on one GPU; --gpus {args.gpus} has nothing to measure")
+        return 2
+    bins, why = _reference_binaries()
+    if bins is None:
+        return _unavailable(why)
+    try:
+        import torch
+        if not torch.cuda.is_available():
+            return _unavailable("no CUDA device")
+    except ImportError:
+        return _unavailable("torch is needed to write the random model file")
+    args.warmup = max(args.warmup, 3)
+    layers = args.layers or model_sizes["num_hidden_layers"]
+    sizes = dict(model_sizes, num_hidden_layers=layers)
+    need_bytes = 2.2 * (layers * _layer_params(sizes) + 2 * sizes["vocab_size"] * sizes["hidden_size"]) + (1 << 30)
+    base = None
+    for cand in ("/dev/shm", tempfile.gettempdir()):
+        try:
+            if shutil.disk_usage(cand).free > need_bytes:
+                base = cand
+                break
+        except OSError:
+            continue
+    if base is None:
+        return _unavailable("no room for the reference's model file")
+    work = Path(tempfile.mkdtemp(prefix="tllm_ref_", dir=base))
+    pk = peaks()
+    try:
+        t0 = time.perf_counter()
+        _write_reference_model(work, sizes)
+        print(f"[bench] reference model written to {work} in {time.perf_counter() - t0:.1f} s", file=sys.stderr, flush=True)
+        clocks = ClockSampler()
+        clocks.start()
+        windows = []
+        vocab = sizes["vocab_size"]
+        prompt_len = _standing_prompt_len(args.batch, args.steps, args.warmup)
+        blocks = args.batch * (CONTEXT // PAGE) + 64
+        cmd = [str(bins[0]), str(work / "model.safetensors"), str(work / "tokenizer.json"), str(args.batch),
+               str(prompt_len), str(args.warmup), str(args.steps), str(CONTEXT), str(blocks), str(vocab - 1), "0"]
+        w0 = time.perf_counter()
+        res = subprocess.run(cmd, capture_output=True, text=True, timeout=1500)
+        windows.append((w0, time.perf_counter(), "reference decode"))
+        sys.stderr.write(res.stderr[-2000:])
+        if res.returncode != 0:
+            return _unavailable(f"the reference's decode run ended with {res.returncode}: "
+                                + (res.stderr.strip().splitlines() or ["no message"])[-1][:200])
+        dec = json.loads(res.stdout.strip().splitlines()[-1])
+        print(f"[bench] reference decode: {dec}", file=sys.stderr, flush=True)
+
+        points = {}
+        for b in ([1, 8, 64] if args.ref_all else [args.batch]):
+            cmd = [str(bins[1]), "--bench", "--tokenizer", str(work / "tokenizer.json"), "--model",
+                   str(work / "model.safetensors"), "--device", "cuda", "--num-seqs", str(b), "--min-input-len", "128",
+                   "--max-input-len", "128", "--min-output-len", "128", "--max-output-len", "128", "--warmup", "3",
+                   "--repeats", "5", "--max-seq-len", str(CONTEXT), "--num-kv-blocks", str(b * (256 // PAGE) + 16),
+                   "--max-token-id", str(vocab - 1), "--seed", "0"]
+            w0 = time.perf_counter()
+            res = subprocess.run(cmd, capture_output=True, text=True, timeout=1500)
+            windows.append((w0, time.perf_counter(), f"reference 128/128 b{b}"))
+            rates = [float(part.split("=")[1]) for line in res.stdout.splitlines() if line.startswith("run=")
+                     for part in line.split() if part.startswith("output_tokens_per_second=")]
+            if res.returncode != 0 or len(rates) != 5:
+                print(f"[bench] reference model_main --bench b{b} ended with {res.returncode}: {res.stderr[-400:]}",
+                      file=sys.stderr, flush=True)
+                continue
+            points[f"p128_e2e_b{b}"] = round(statistics.median(rates), 1)
+            print(f"[bench] reference 128/128 b{b}: {points[f'p128_e2e_b{b}']} output tok/s (median of 5)",
+                  file=sys.stderr, flush=True)
+    finally:
+        shutil.rmtree(work, ignore_errors=True)
+
+    weight_bytes = 2 * (layers * _layer_params(sizes) + vocab * sizes["hidden_size"])
+    kv_per_token = 2 * sizes["num_key_value_heads"] * sizes["head_dim"] * 2 * layers
+    # request i has decoded about (batch - 1 - i) / batch of the prompt steps' tokens before the timed steps
+    prefill_steps = dec.get("prefill_steps", 0)
+    mean_ctx = prompt_len + prefill_steps / 2.0 + args.warmup + (args.steps + 1) / 2.0
+    achieved = (weight_bytes + args.batch * mean_ctx * kv_per_token) / dec["seconds"] * args.steps / 1e9
+    table_entries = CONTEXT // PAGE
+    record = {
+        "impl": "reference",
+        "metric": f"decode tok/s @ batch {args.batch} ({model_name}, context 4096, 1 B200)",
+        "value": round(dec["tokens_per_second"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(dec["ms_per_step"], 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "fp16",
+        "data": "synthetic (random weights N(0,0.02), uniform random token ids); the reference multiplies by the "
+                "embedding matrix for the head whatever tie_word_embeddings says",
+        "config": _config(model_name, args.batch, layers, model_sizes, sizes, mean_ctx, weight_bytes, pk),
+        "e2e": {"value": round(dec["tokens_per_second"], 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": args.batch * (8 + 4 * table_entries + 20), "d2h_bytes_per_step": args.batch * 4},
+        "gpu_launches": (17 * layers + 6) * args.steps,
+        "prefill": None,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clocks.stop(windows),
+    }
+    print(json.dumps(record))
+    return 0
+
+
+def _layer_params(sizes: dict) -> int:
+    q = sizes["num_attention_heads"] * sizes["head_dim"]
+    kv = sizes["num_key_value_heads"] * sizes["head_dim"]
+    h = sizes["hidden_size"]
+    return (q + 2 * kv) * h + h * q + 3 * h * sizes["intermediate_size"]
+
+
+def _config(model_name, batch, layers, model_sizes, sizes, mean_ctx, weight_bytes, pk) -> dict:
+    """The ``config`` of the record, the same for both arms (flat, at most 20 keys)."""
+    return {"model": model_name, "global_batch": batch, "seq_len": CONTEXT, "parallelism": "single GPU",
+            "layers": layers, "layers_of_model": model_sizes["num_hidden_layers"],
+            "hidden_size": sizes["hidden_size"], "intermediate_size": sizes["intermediate_size"],
+            "q_heads": sizes["num_attention_heads"], "kv_heads": sizes["num_key_value_heads"],
+            "head_dim": sizes["head_dim"], "vocab_size": sizes["vocab_size"], "page_size": PAGE,
+            "decode_context": None if mean_ctx is None else round(mean_ctx, 1), "prefill_tokens": PREFILL_TOKENS,
+            "p128": "128-token prompts, 128 outputs, temperature 0.6",
+            "l2": f"inputs larger than L2 ({weight_bytes / 1e9:.1f} GB of weights per step)", "peaks": pk["source"]}
+
+
+def precheck(model, cfg, sizes, device) -> dict:
+    """Before anything is timed: the logits of the very model that is timed, by the bfloat16
+    kernels, against the float32 path of the same weights, on one request of 2,200 tokens and three
+    short ones cut in four ways (whole; the last 32 tokens one by one, which are replayed CUDA
+    graphs; portions of 2 to 700 tokens; mixed on a pool that just holds the four).  If the float32
+    twin of all layers does not fit beside the model, both are cut to the layers that do."""
+    import torch
+
+    from tiny_llm_infer_b200.cache import CacheManager
+    from tiny_llm_infer_b200.config import Qwen3Config
+    from tiny_llm_infer_b200.engine import ModelRunner, random_model, selfcheck
+
+    layers = sizes["num_hidden_layers"]
+    free, _ = torch.cuda.mem_get_info()
+    per_layer, ends = 4 * _layer_params(sizes), 4 * 2 * sizes["vocab_size"] * sizes["hidden_size"]
+    fit = int((free * 0.8 - ends - (8 << 30)) // (per_layer * 1.5))        # the twin, and the cut bfloat16 model if one is needed
+    check_layers = layers if layers * per_layer + ends + (8 << 30) < free * 0.8 else max(1, min(layers, fit))
+    gen = torch.Generator().manual_seed(7)
+    requests = {str(i): torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist()
+                for i, n in enumerate((2200, 300, 150, 90))}
+    wanted = {k: selfcheck.wanted_positions(len(v)) for k, v in requests.items()}
+
+    def ways(m, dtype):
+        cache = CacheManager(m.cache_needs(), PAGE, selfcheck.pages_for(requests, PAGE), max_slots=4,
+                             max_seq_len=2240, dtype=dtype, device=device)
+        runner = ModelRunner(m, cache, max_batch_tokens=2240)
+        rows = selfcheck.CutRunner(runner, requests, wanted).all_ways(seed=3)
+        runner.check_kernels()
+        cache.audit()
+        return rows
+
+    cut_cfg = Qwen3Config(layer_types=("full_attention",) * check_layers, **dict(sizes, num_hidden_layers=check_layers))
+    exact_model = random_model(cut_cfg, seed=0, dtype=torch.float32, device=device, std=0.02)
+    exact = ways(exact_model, torch.float32)
+    del exact_model
+    torch.cuda.empty_cache()
+    fast_model = model if check_layers == layers else random_model(cut_cfg, seed=0, dtype=torch.bfloat16, device=device, std=0.02)
+    fast = ways(fast_model, torch.bfloat16)
+    del fast_model
+    result = selfcheck.compare(fast, exact, near_tie=0.3)
+    spread32 = max(selfcheck.spread_between_ways(exact).values())
+    del exact, fast
+    torch.cuda.empty_cache()
+    names = ("whole", "tail", "portions", "mixed")
+    out = {"layers": check_layers, "rows": len(wanted["0"]) + sum(len(wanted[k]) for k in "123"),
+           "max_of_row_std": round(max(result[w + ":relative"] for w in names), 4),
+           "rms_of_row_std": round(max(result[w + ":rms"] for w in names), 4),
+           "argmax_misses": int(sum(result[w + ":argmax_misses"] for w in names)),
+           "float32_ways_relative": float(f"{spread32:.2e}")}
+    out["ok"] = bool(out["max_of_row_std"] <= 0.3 and out["rms_of_row_std"] <= 0.06 and out["argmax_misses"] == 0
+                     and spread32 <= 1e-4)
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -127,10 +388,15 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None,
                     help="fewer layers than the model has (named in the record) if memory or time needs it")
     ap.add_argument("--mixed", action="store_true",
-                    help="also the mixed run that goes with the 0.6B sizes: 64 requests, prompts of 16 to "
-                         "1024 tokens, 256 outputs each at temperature 0.6, budget 2048, through LLM.generate")
-    ap.add_argument("--skip-points", action="store_true", help="leave out the batch 1 and 64 points")
-    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "e2e", "mixed"],
+                    help="the mixed run (64 requests, prompts of 16 to 1024 tokens, 256 outputs each at temperature "
+                         "0.6, budget 2048, through LLM.generate) with the sizes of --model; at the default sizes it "
+                         "runs anyway, with the Qwen3-0.6B sizes it belongs to")
+    ap.add_argument("--skip-points", action="store_true",
+                    help="leave out the batch 1 and 64 points, the 128-token workload and the 0.6B mixed run")
+    ap.add_argument("--skip-check", action="store_true", help="leave out the logits check before the timed phases")
+    ap.add_argument("--ref-all", action="store_true",
+                    help="reference arm: its model_main --bench at batch 1, 8 and 64 instead of --batch alone")
+    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "e2e", "mixed", "p128"],
                     help="run one phase only (for profiling a small case); the record then lacks the others")
     args = ap.parse_args()
     model_name, model_sizes = MODELS[args.model]
@@ -140,10 +406,7 @@ def main() -> int:
         args.mixed = True
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "xu797/tiny-llm-infer is a CMake C++/CUDA project without setup.py or pyproject.toml: "
-                          "pip reports 'not installable'; it needs glog and armadillo, which are not in the image"}))
-        return 0
+        return reference_arm(args, model_name, model_sizes)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} has nothing to measure")
         return 2
@@ -167,6 +430,15 @@ def main() -> int:
     torch.cuda.synchronize()
     print(f"[bench] model built in {time.perf_counter() - t0:.1f} s", file=sys.stderr, flush=True)
 
+    check = None
+    if not args.skip_check and args.only == "all":
+        t0 = time.perf_counter()
+        check = precheck(model, cfg, sizes, device)
+        print(f"[bench] logits check in {time.perf_counter() - t0:.1f} s: {check}", file=sys.stderr, flush=True)
+        if not check["ok"]:
+            print(json.dumps({"error": "the bfloat16 kernels' logits do not match the float32 path", "check": check}))
+            return 1
+
     max_batch = 64 if (not args.skip_points or args.mixed) else max(args.batch, 1)
     pages = max_batch * (CONTEXT // PAGE) + 2 * (PREFILL_TOKENS // PAGE) + 64
     llm = LLM(None, dtype="bfloat16", max_model_len=CONTEXT, num_kv_blocks=pages, block_size=PAGE,
@@ -179,8 +451,7 @@ def main() -> int:
         return torch.randint(0, vocab, (n,), generator=gen).tolist()
 
     # byte and flop counts
-    layer_params = (cfg.q_dim + 2 * cfg.kv_dim) * cfg.hidden_size + cfg.hidden_size * cfg.q_dim \
-        + 3 * cfg.hidden_size * cfg.intermediate_size
+    layer_params = _layer_params(sizes)
     weight_bytes = 2 * (args.layers * layer_params + vocab * cfg.hidden_size)
     kv_bytes_per_token = 2 * cfg.kv_dim * 2 * args.layers
     windows = []
@@ -216,9 +487,9 @@ def main() -> int:
         print(f"[bench] prefill {prefill}", file=sys.stderr, flush=True)
 
     # ---------------------------------------------------------------- decode, timed on the device
-    def decode_device(batch, steps, warmup):
-        """Tokens per second of `steps` decode steps of `batch` requests that end at CONTEXT."""
-        start_len = CONTEXT - (steps + warmup)
+    def decode_device(batch, steps, warmup, end_context=CONTEXT, what="decode"):
+        """Tokens per second of `steps` decode steps of `batch` requests that end at `end_context`."""
+        start_len = end_context - (steps + warmup)
         names = [f"d{batch}_{i}" for i in range(batch)]
         for name in names:                                   # real prefill, in portions of 2048
             toks = tokens(start_len)
@@ -246,7 +517,7 @@ def main() -> int:
             if it >= warmup:
                 times.append((start, end))
         torch.cuda.synchronize()
-        windows.append((w_start, time.perf_counter(), f"decode b{batch}"))
+        windows.append((w_start, time.perf_counter(), f"{what} b{batch}"))
         launches = ops.launches - before
         ms = sum(a.elapsed_time(b) for a, b in times) / steps
         for name in names:
@@ -254,11 +525,13 @@ def main() -> int:
         mean_ctx = start_len + warmup + (steps - 1) / 2.0 + 1
         return batch / (ms / 1e3), ms, launches, mean_ctx
 
+    def hbm_fraction(batch, ms, ctx):
+        return (weight_bytes + batch * ctx * kv_bytes_per_token) / (ms / 1e3) / 1e9
+
     value = ms_per_step = launches = mean_ctx = roofline = None
     if args.only in ("all", "decode"):
         value, ms_per_step, launches, mean_ctx = decode_device(args.batch, args.steps, args.warmup)
-        step_bytes = weight_bytes + args.batch * mean_ctx * kv_bytes_per_token
-        achieved = step_bytes / (ms_per_step / 1e3) / 1e9
+        achieved = hbm_fraction(args.batch, ms_per_step, mean_ctx)
         roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                     "frac": round(achieved / pk["hbm_gbs"], 4)}
         print(f"[bench] decode b{args.batch}: {value:.1f} tok/s, {ms_per_step:.3f} ms/step, {roofline}",
@@ -304,28 +577,76 @@ def main() -> int:
         for b in (1, 64):
             v, ms_b, _, ctx_b = decode_device(b, min(args.steps, 32), args.warmup)
             points[f"decode_b{b}"] = round(v, 1)
-            bw = (weight_bytes + b * ctx_b * kv_bytes_per_token) / (ms_b / 1e3) / 1e9
+            bw = hbm_fraction(b, ms_b, ctx_b)
+            points[f"decode_b{b}_hbm_frac"] = round(bw / pk["hbm_gbs"], 4)
             print(f"[bench] decode b{b}: {v:.1f} tok/s, {ms_b:.3f} ms/step, {bw:.0f} GB/s", file=sys.stderr, flush=True)
 
-    mixed = None
-    if args.mixed:
+    # ---------------------------------------------------------------- 128-token prompts, 128 outputs
+    # The reference's own benchmark (benchmark/run_benchmark.sh:32-42, model/model_main.cpp:150-175,
+    # 354-368): `batch` prompts of 128 uniform token ids, 128 outputs each at temperature 0.6 with
+    # end-of-sequence ignored, output tokens / wall time from the first add_request to the last result,
+    # prompts included; three warm-up runs, then the median of five.  Beside it the decode steps of the
+    # same workload alone (contexts 128 to 256), timed on the device, with their share of the HBM peak.
+    def p128_e2e(batch):
+        rates = []
+        for run in range(8):
+            prompts = [tokens(128) for _ in range(batch)]
+            params = [SamplingParams(max_tokens=128, temperature=0.6, ignore_eos=True, seed=1000 * run + i + 1)
+                      for i in range(batch)]
+            torch.cuda.synchronize()
+            t_start = time.perf_counter()
+            outs = llm.generate(prompts, params)
+            elapsed = time.perf_counter() - t_start
+            assert sum(len(o.token_ids) for o in outs) == 128 * batch
+            if run >= 3:
+                rates.append(128 * batch / elapsed)
+                windows.append((t_start, t_start + elapsed, f"128/128 e2e b{batch}"))
+        return statistics.median(rates)
+
+    if (not args.skip_points and args.only == "all") or args.only == "p128":
+        for b in (1, 8, 64):
+            v, ms_b, _, ctx_b = decode_device(b, 120, 8, end_context=256, what="128/128 decode")
+            points[f"p128_decode_b{b}"] = round(v, 1)
+            points[f"p128_hbm_frac_b{b}"] = round(hbm_fraction(b, ms_b, ctx_b) / pk["hbm_gbs"], 4)
+            points[f"p128_e2e_b{b}"] = round(p128_e2e(b), 1)
+            print(f"[bench] 128/128 b{b}: decode steps {v:.1f} tok/s ({ms_b:.3f} ms/step, {points[f'p128_hbm_frac_b{b}']} of HBM), "
+                  f"end to end {points[f'p128_e2e_b{b}']} output tok/s", file=sys.stderr, flush=True)
+
+    # ---------------------------------------------------------------- the mixed run
+    def mixed_run(the_llm, the_vocab):
         g2 = torch.Generator().manual_seed(1)
 
         def workload():
             lens = torch.randint(16, 1025, (64,), generator=g2).tolist()
-            return ([torch.randint(0, vocab, (n,), generator=g2).tolist() for n in lens],
+            return ([torch.randint(0, the_vocab, (n,), generator=g2).tolist() for n in lens],
                     [SamplingParams(max_tokens=256, temperature=0.6, ignore_eos=True, seed=i + 1) for i in range(64)])
-        llm.generate(*workload())                               # first run: graphs are captured
+        the_llm.generate(*workload())                               # first run: graphs are captured
         prompts, params = workload()
         torch.cuda.synchronize()
         t_start = time.perf_counter()
-        outs = llm.generate(prompts, params)
+        outs = the_llm.generate(prompts, params)
         torch.cuda.synchronize()
         elapsed = time.perf_counter() - t_start
         windows.append((t_start, t_start + elapsed, "mixed run"))
         made = sum(len(o.token_ids) for o in outs)
-        mixed = {"value": round(made / elapsed, 1), "unit": "generated tokens/s", "requests": 64,
-                 "prompt_tokens": sum(map(len, prompts)), "generated_tokens": made, "seconds": round(elapsed, 3)}
+        return {"value": round(made / elapsed, 1), "unit": "generated tokens/s", "requests": 64,
+                "prompt_tokens": sum(map(len, prompts)), "generated_tokens": made, "seconds": round(elapsed, 3)}
+
+    mixed = None
+    if args.mixed:
+        mixed = dict(mixed_run(llm, vocab), model=model_name)
+    elif args.model == "8b" and not args.skip_points and args.only == "all":
+        # the mixed continuous-batching run belongs to the Qwen3-0.6B sizes: a second, small model
+        del llm, runner, engine, model
+        torch.cuda.empty_cache()
+        name06, sizes06 = MODELS["0.6b"]
+        cfg06 = Qwen3Config(layer_types=("full_attention",) * sizes06["num_hidden_layers"], **sizes06)
+        model06 = random_model(cfg06, seed=0, dtype=torch.bfloat16, device=device, std=0.02)
+        llm06 = LLM(None, dtype="bfloat16", max_model_len=CONTEXT, num_kv_blocks=64 * (1280 // PAGE) + 64, block_size=PAGE,
+                    max_num_batched_tokens=PREFILL_TOKENS, max_num_seqs=64, device=device, loaded=(model06, cfg06))
+        mixed = dict(mixed_run(llm06, cfg06.vocab_size), model=name06)
+    if mixed is not None:
+        points["mixed_run_tokens_per_s"] = mixed["value"]
         print(f"[bench] mixed run: {mixed}", file=sys.stderr, flush=True)
 
     record = {
@@ -333,16 +654,10 @@ def main() -> int:
         "value": None if value is None else round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": None if ms_per_step is None else round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (random weights N(0,0.02), uniform random token ids)",
-        "config": {"model": model_name, "global_batch": args.batch, "seq_len": CONTEXT,
-                   "parallelism": "single GPU", "layers": args.layers, "layers_of_model": model_sizes["num_hidden_layers"],
-                   "hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size,
-                   "q_heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
-                   "vocab_size": vocab, "page_size": PAGE, "decode_context": None if mean_ctx is None else round(mean_ctx, 1),
-                   "prefill_tokens": PREFILL_TOKENS, "l2": f"inputs larger than L2 ({weight_bytes / 1e9:.1f} GB of weights per step)",
-                   "peaks": pk["source"]},
+        "config": _config(model_name, args.batch, args.layers, model_sizes, sizes, mean_ctx, weight_bytes, pk),
         "e2e": e2e,
         "gpu_launches": launches,
-        "prefill": prefill, "roofline": roofline, "points": points, "mixed": mixed,
+        "prefill": prefill, "roofline": roofline, "points": points, "mixed": mixed, "check": check,
         "clocks": clocks.stop(windows),
     }
     print(json.dumps(record))

@@ -140,3 +140,74 @@ def test_overlapped_scheduling_under_random_workloads(tmp_path, cpu_ops, seed):
 
     ahead, plain_run = run(True), run(False)
     assert ahead[0] == plain_run[0] and sorted(ahead[1]) == sorted(plain_run[1])
+
+
+@pytest.mark.parametrize("overlap", [True, False])
+def test_a_step_that_cannot_be_laid_out_is_taken_back(tmp_path, cpu_ops, overlap):
+    """The runner refuses to lay a step out once (as it would a step over its token limit): the
+    error reaches the caller, the plan is taken back, and stepping on gives the tokens of a run
+    without the fault; nothing is decoded from a cache that lacks its prompt."""
+    from tiny_llm_infer_b200 import LLM, SamplingParams
+    from tiny_llm_infer_b200.engine import StepError
+    folder = make_folder(TINIES["A"], tmp_path / "m")
+    prompts = [prompt(i, n, 256) for i, n in enumerate((5, 17, 33, 9))]
+    sp = SamplingParams(max_tokens=8, ignore_eos=True)
+
+    def make():
+        return LLM(str(folder), dtype="float32", max_model_len=128, num_kv_blocks=16, block_size=16,
+                   max_num_batched_tokens=24, max_num_seqs=4, device="cpu", overlap_scheduling=overlap)
+    want = [o.token_ids for o in make().generate(prompts, sp)]
+
+    llm = make()
+    engine, runner = llm.engine, llm.runner
+    ids = [engine.add_request(p, sp) for p in prompts]
+    real_prepare, calls = runner.prepare, {"n": 0}
+
+    def prepare(entries):
+        calls["n"] += 1
+        if calls["n"] == 3:                          # a step that completes one prompt and decodes others
+            raise StepError("refused for the test")
+        return real_prepare(entries)
+    runner.prepare = prepare
+    results, errors = {}, 0
+    for _ in range(200):
+        if engine.is_finished():
+            break
+        try:
+            for r in engine.step():
+                results[r.request_id] = r.token_ids
+        except StepError:
+            errors += 1
+    assert errors == 1 and engine.is_finished()
+    assert [results[i] for i in ids] == want
+    llm.cache.audit()
+    assert llm.cache.free_pages() == {None: 16}
+
+
+def test_an_error_in_a_launched_step_stops_the_engine(tmp_path, cpu_ops):
+    """A step fails after it was laid out (a kernel refusing its arguments, a device error): what
+    ran and what the cache booked is unknown, so the error is raised, and every later step and
+    request is refused instead of running on."""
+    from tiny_llm_infer_b200 import LLM, SamplingParams
+    from tiny_llm_infer_b200.engine.llm_engine import EngineStopped
+    folder = make_folder(TINIES["A"], tmp_path / "m")
+    llm = LLM(str(folder), dtype="float32", max_model_len=128, num_kv_blocks=16, block_size=16,
+              max_num_batched_tokens=24, max_num_seqs=4, device="cpu")
+    engine, runner = llm.engine, llm.runner
+    for i, n in enumerate((5, 17, 33)):
+        engine.add_request(prompt(i, n, 256), SamplingParams(max_tokens=8, ignore_eos=True))
+    engine.step()
+    real_run = runner.run
+
+    def run(*a, **kw):
+        raise RuntimeError("device error for the test")
+    runner.run = run
+    with pytest.raises(RuntimeError, match="device error"):
+        for _ in range(3):                           # the step launched ahead fails: raised by the step it belongs to
+            engine.step()
+    runner.run = real_run
+    with pytest.raises(EngineStopped):
+        for _ in range(3):
+            engine.step()
+    with pytest.raises(EngineStopped):
+        engine.add_request([1, 2, 3])

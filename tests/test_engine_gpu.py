@@ -201,9 +201,9 @@ def test_request_checks(folders):
     llm = LLM(str(folders["A"]), dtype="bfloat16", max_model_len=32, num_kv_blocks=4)
     eng = llm.engine
     for bad, match in (((list(range(33)), SamplingParams()), "max_model_len"),
-                       (([], SamplingParams()), "at least one token"),
-                       (([1], SamplingParams(max_tokens=0)), "greater than zero"),
-                       (([1, 2], SamplingParams(max_tokens=32)), "completion exceeds"),
+                       (([], SamplingParams()), "prompt is empty"),
+                       (([1], SamplingParams(max_tokens=0)), "max_tokens is 0"),
+                       (([1, 2], SamplingParams(max_tokens=32)), "leaves room for 31"),
                        (([1], SamplingParams(top_p=0.0)), "top_p"),
                        (([1], SamplingParams(temperature=-1.0)), "temperature"),
                        (([300], SamplingParams(max_tokens=1)), "outside")):

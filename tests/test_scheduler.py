@@ -108,7 +108,7 @@ def test_out_of_pages_preempts_the_oldest_that_cannot_grow_and_recomputes():
 def test_prompt_larger_than_the_pool_is_an_error():
     sched, cache = make(pages=2, page=8)
     sched.add(seq(1, 17))
-    with pytest.raises(SchedulerError, match="more KV blocks"):
+    with pytest.raises(SchedulerError, match="needs 3 pages, the pool has 2"):
         sched.schedule()
 
 
@@ -129,7 +129,7 @@ def test_empty_request_and_wrong_sample_count():
         sched.add(Sequence(1, [], SamplingParams()))
     sched.add(seq(1, 3))
     plan = sched.schedule()
-    with pytest.raises(SchedulerError, match="wrong number"):
+    with pytest.raises(SchedulerError, match="0 sampled tokens for a plan of 1"):
         sched.postprocess(plan, [], lambda t: False)
 
 
@@ -201,3 +201,51 @@ def test_steps_launched_ahead_of_their_tokens():
     assert [s.id for s in done] == [1] and a.completion == [11, 13, 14] and b.completion == [12, 99]
     cache.audit()
     assert cache.free_pages() == {None: 8}
+
+
+def test_a_plan_that_is_taken_back_leaves_the_queues_as_they_were():
+    """``abort``: the step of a plan never ran.  Requests whose prompts it would have completed wait
+    again (and are not decoded from a cache that lacks their prompt), the order of both queues is
+    the old one, a request added meanwhile is kept, and the steps after it are those of a run in
+    which the plan was never made."""
+    def fresh():
+        sched, cache = make(pages=32, budget=32)
+        for i, n in enumerate((40, 9, 70)):
+            sched.add(seq(i + 1, n))
+        run_step(sched, cache)
+        run_step(sched, cache)                       # 2 is running now, 1 and 3 are partly computed
+        return sched, cache
+
+    clean, clean_cache = fresh()
+    want = [shape(run_step(clean, clean_cache)[0]) for _ in range(6)]
+
+    sched, cache = fresh()
+    running, waiting = list(sched.running), list(sched.waiting)
+    plan = sched.schedule()                          # would complete request 1's prompt
+    assert any(s.is_prefill and s.samples for s in plan.sequences)
+    late = seq(9, 3)
+    sched.add(late)
+    sched.abort(plan)
+    assert list(sched.running) == running and list(sched.waiting) == waiting + [late]
+    assert all(s.status is Status.WAITING and s.num_scheduled_tokens == 0 for s in waiting)
+    assert plan.sequences == []
+    sched.waiting.remove(late)
+    got = [shape(run_step(sched, cache)[0]) for _ in range(6)]
+    assert got == want
+    cache.audit()
+
+
+def test_a_plan_that_fails_half_made_changes_nothing():
+    """The second waiting prompt is larger than the pool: ``schedule`` raises, and the first, whose
+    prompt the half-made plan had completed, is still waiting with nothing scheduled."""
+    sched, cache = make(pages=4, page=8, budget=64)
+    first, huge = seq(1, 9), seq(2, 40)
+    sched.add(first)
+    sched.add(huge)
+    with pytest.raises(SchedulerError, match="needs 5 pages, the pool has 4"):
+        sched.schedule()
+    assert list(sched.waiting) == [first, huge] and not sched.running
+    assert first.status is Status.WAITING and first.num_scheduled_tokens == 0
+    sched.waiting.remove(huge)
+    plan, _ = run_step(sched, cache)
+    assert shape(plan) == [(1, 0, 9, True)]

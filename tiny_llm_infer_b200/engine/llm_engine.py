@@ -61,6 +61,12 @@ class _Step:
     ticket: int = -1           # of the sampler, once launched
 
 
+class EngineStopped(RuntimeError):
+    """A launched step failed (a kernel refused its arguments, the device reported an error): what
+    the cache holds no longer matches what the scheduler has booked, so the engine takes no more
+    requests and steps."""
+
+
 class LLMEngine:
     def __init__(self, runner: ModelRunner, config: EngineConfig, eos_token_ids: Seq[int] = (),
                  detokenize=None, overlap: bool = True):
@@ -78,24 +84,29 @@ class LLMEngine:
         self.overlap = overlap
         self._flying: List[_Step] = []                 # launched, tokens not read yet (at most two)
         self._deferred: Optional[Exception] = None
+        self._failed: Optional[Exception] = None       # an error in a launched step: the engine has stopped
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt_tokens: Seq[int], sampling: Optional[SamplingParams] = None) -> int:
         """Checks of the reference (engine/src/llm_engine.cpp:41-64)."""
+        if self._failed is not None:
+            raise EngineStopped(f"the engine stopped after an error in a launched step: {self._failed}")
         sampling = sampling or SamplingParams()
         sampling.validate()
+        limit = self.config.max_model_len
         if sampling.max_tokens == 0:
-            raise ValueError("max_tokens must be greater than zero.")
+            raise ValueError("max_tokens is 0: a request must ask for at least one token")
         prompt = [int(t) for t in prompt_tokens]
         if not prompt:
-            raise ValueError("A prompt must encode to at least one token.")
-        if len(prompt) > self.config.max_model_len:
-            raise ValueError("The prompt exceeds max_model_len.")
-        if sampling.max_tokens > self.config.max_model_len - len(prompt) + 1:
-            raise ValueError("The requested completion exceeds max_model_len.")
+            raise ValueError("the prompt is empty")
+        if len(prompt) > limit:
+            raise ValueError(f"the prompt has {len(prompt)} tokens, max_model_len is {limit}")
+        if sampling.max_tokens > limit - len(prompt) + 1:
+            raise ValueError(f"a prompt of {len(prompt)} tokens leaves room for {limit - len(prompt) + 1} generated "
+                             f"tokens under max_model_len {limit}; max_tokens is {sampling.max_tokens}")
         vocab = self.runner.vocab
         if min(prompt) < 0 or max(prompt) >= vocab:
-            raise ValueError(f"A prompt token id is outside [0, {vocab}).")
+            raise ValueError(f"a prompt token id is outside [0, {vocab})")
         with self._lock:
             request_id = self._next_id
             self._next_id += 1
@@ -118,18 +129,25 @@ class LLMEngine:
             plan = self.scheduler.schedule()
         if not plan.sequences:
             return None
-        entries, rows, row_of, late_of = [], [], [], []
-        for item in plan.sequences:
-            seq = item.sequence
-            end = item.token_start + item.token_count
-            late = item.token_count - 1 if seq.pending and end == len(seq) else None
-            want = [item.token_count - 1] if item.samples else []
-            entries.append(StepEntry(seq.id, seq.tokens[item.token_start:end], want, late))
-            if item.samples:
-                rows.append((seq.sampling.temperature, seq.sampling.top_p,
-                             draw_key(seq.seed, seq.num_completion_tokens)))
-                row_of.append(len(entries) - 1)
-        step = self.runner.prepare(entries)
+        try:
+            entries, rows, row_of, late_of = [], [], [], []
+            for item in plan.sequences:
+                seq = item.sequence
+                end = item.token_start + item.token_count
+                late = item.token_count - 1 if seq.pending and end == len(seq) else None
+                want = [item.token_count - 1] if item.samples else []
+                entries.append(StepEntry(seq.id, seq.tokens[item.token_start:end], want, late))
+                if item.samples:
+                    rows.append((seq.sampling.temperature, seq.sampling.top_p,
+                                 draw_key(seq.seed, seq.num_completion_tokens)))
+                    row_of.append(len(entries) - 1)
+            step = self.runner.prepare(entries)
+        except Exception:
+            # nothing of the plan has run: take it back, so that the next step starts from the
+            # queues as they were (pages reserved meanwhile stay with their requests)
+            with self._lock:
+                self.scheduler.abort(plan)
+            raise
         for index, _ in step.late:                   # whose token each late place waits for
             late_of.append(plan.sequences[index].sequence.id)
         return _Step(plan, step, rows, row_of, late_of)
@@ -137,13 +155,21 @@ class LLMEngine:
     def _launch(self, step: "_Step", before: Optional["_Step"]) -> None:
         """Upload and launch; the late tokens are rows of what ``before``, the step launched
         last and not read yet, samples: they stay on the device."""
-        if step.late_of:
-            row = {before.plan.sequences[i].sequence.id: r for r, i in enumerate(before.row_of)}
-            source = (self.sampler.device_tokens(before.ticket), [row[request] for request in step.late_of])
-            logits = self.runner.run(step.step, late_source=source)
-        else:
-            logits = self.runner.run(step.step)
-        step.ticket = self.sampler.launch(logits, step.rows)
+        try:
+            if step.late_of:
+                row = {before.plan.sequences[i].sequence.id: r for r, i in enumerate(before.row_of)}
+                source = (self.sampler.device_tokens(before.ticket), [row[request] for request in step.late_of])
+                logits = self.runner.run(step.step, late_source=source)
+            else:
+                logits = self.runner.run(step.step)
+            step.ticket = self.sampler.launch(logits, step.rows)
+        except Exception as error:
+            # part of the step may have run and the cache may have booked it: there is no way back
+            self.runner.abandon(step.step)
+            with self._lock:
+                self.scheduler.abort(step.plan)
+            self._failed = error
+            raise
         with self._lock:
             self.scheduler.advance(step.plan)
         self._flying.append(step)
@@ -157,12 +183,14 @@ class LLMEngine:
         if self._deferred is not None:
             error, self._deferred = self._deferred, None
             raise error
+        if self._failed is not None and not self._flying:
+            raise EngineStopped(f"the engine stopped after an error in a launched step: {self._failed}")
         if not self._flying:
             first = self._prepare()
             if first is None:
                 return []
             self._launch(first, None)
-        if self.overlap and len(self._flying) == 1:
+        if self.overlap and len(self._flying) == 1 and self._failed is None:
             try:
                 ahead = self._prepare()
                 if ahead is not None:
@@ -206,7 +234,7 @@ class LLMEngine:
         if not prompts:
             return []
         if not self.is_finished():
-            raise ValueError("Finish or step existing requests before calling generate.")
+            raise ValueError("generate() starts from an idle engine: step the requests it holds to their end first")
         if sampling is None or isinstance(sampling, SamplingParams):
             params = [sampling or SamplingParams()] * len(prompts)
         else:
@@ -214,7 +242,7 @@ class LLMEngine:
             if len(params) == 1:
                 params = params * len(prompts)
             if len(params) != len(prompts):
-                raise ValueError("Pass one SamplingParams object or one per prompt.")
+                raise ValueError(f"{len(params)} sampling settings for {len(prompts)} prompts: give one, or one each")
         ids = [self.add_request(p, s) for p, s in zip(prompts, params)]
         results: Dict[int, GenerationResult] = {}
         while not self.is_finished():

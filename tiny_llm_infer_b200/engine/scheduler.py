@@ -112,6 +112,8 @@ class BatchPlan:
     sequences: List[ScheduledSequence] = field(default_factory=list)
     num_tokens: int = 0
     preempted: List[Sequence] = field(default_factory=list)
+    # the two queues as they were before this plan was made (for ``Scheduler.abort``)
+    queues_before: Optional[tuple] = None
 
     @property
     def is_prefill(self) -> bool:
@@ -129,7 +131,7 @@ class Scheduler:
 
     def add(self, sequence: Sequence) -> None:
         if len(sequence) == 0:
-            raise ValueError("A scheduled request must contain at least one token.")
+            raise ValueError("a request needs at least one token")
         self.waiting.append(sequence)
 
     def is_finished(self) -> bool:
@@ -146,7 +148,36 @@ class Scheduler:
         plan.preempted.append(seq)
 
     def schedule(self) -> BatchPlan:
-        plan = BatchPlan()
+        """The next step's plan.  Making it moves requests between and inside the queues; if it
+        raises, or if the step it describes is never launched (``abort``), those moves are undone."""
+        plan = BatchPlan(queues_before=(list(self.running), list(self.waiting)))
+        try:
+            self._fill(plan)
+        except Exception:
+            self.abort(plan)
+            raise
+        return plan
+
+    def abort(self, plan: BatchPlan) -> None:
+        """Take back a plan whose step will not run (``advance`` was not called for it, and no
+        other plan was made since): the queues are as before it, requests whose prompts it would
+        have completed wait again, nothing counts as scheduled.  What making the plan did to the
+        cache stays and is consistent by itself: requests it admitted keep their slot and pages,
+        requests it preempted stay preempted, at the front of the waiting queue."""
+        running, waiting = plan.queues_before
+        known = set(map(id, running)) | set(map(id, waiting))
+        newcomers = [s for s in self.waiting if id(s) not in known]      # added while the plan was out
+        preempted = set(map(id, plan.preempted))
+        for item in plan.sequences:
+            seq = item.sequence
+            seq.num_scheduled_tokens = 0
+            if item.is_prefill and seq.status is Status.RUNNING:
+                seq.status = Status.WAITING
+        self.running = deque(s for s in running if id(s) not in preempted)
+        self.waiting = deque(list(reversed(plan.preempted)) + waiting + newcomers)
+        plan.sequences, plan.num_tokens = [], 0
+
+    def _fill(self, plan: BatchPlan) -> None:
         budget, max_seqs = self.config.max_num_batched_tokens, self.config.max_num_seqs
         used = 0
         # pass 1: one token for every running request
@@ -172,7 +203,7 @@ class Scheduler:
                     continue
             remaining = len(seq) - seq.num_cached_tokens
             if remaining <= 0:
-                raise SchedulerError("A waiting prompt has no uncomputed tokens to schedule.")
+                raise SchedulerError("a waiting request has nothing left to compute")
             count = min(remaining, budget - used)
             seq.num_scheduled_tokens = count
             plan.sequences.append(ScheduledSequence(seq, seq.num_cached_tokens, count, True,
@@ -185,15 +216,15 @@ class Scheduler:
                 self.waiting.append(seq)
         plan.num_tokens = used
         if not plan.sequences and not self.is_finished():
-            raise SchedulerError("The scheduler could not make progress with the available KV blocks.")
-        return plan
+            raise SchedulerError("no request can be scheduled although some are unfinished: the page pool is "
+                                 "too small for any of them to go on")
 
     def _admit(self, seq: Sequence) -> bool:
         """Slot and all pages of the present length, or nothing."""
         pages = -(-len(seq) // self.cache.page_size)
         for key, capacity in self.cache.capacity_pages().items():
             if pages > capacity:
-                raise SchedulerError("The prompt requires more KV blocks than the engine owns.")
+                raise SchedulerError(f"request {seq.id} needs {pages} pages, the pool has {capacity}")
         if self.cache.free_slots == 0:
             return False
         self.cache.admit(seq.id, seq.tokens)
@@ -208,7 +239,7 @@ class Scheduler:
         """Book the step: ``sampled[i]`` is the token of ``plan.sequences[i]`` (-1 where it
         sampled nothing).  Returns the requests that finished."""
         if len(sampled) != len(plan.sequences):
-            raise SchedulerError("The model runner returned the wrong number of sampled tokens.")
+            raise SchedulerError(f"{len(sampled)} sampled tokens for a plan of {len(plan.sequences)} requests")
         self.advance(plan)
         return self.resolve(plan, sampled, is_eos)
 
@@ -244,7 +275,7 @@ class Scheduler:
         step is resolved; the pages can go back at once, since whatever is launched later
         comes later on the stream."""
         if len(sampled) != len(plan.sequences):
-            raise SchedulerError("The model runner returned the wrong number of sampled tokens.")
+            raise SchedulerError(f"{len(sampled)} sampled tokens for a plan of {len(plan.sequences)} requests")
         finished = []
         for item, token in zip(plan.sequences, sampled):
             seq, index = item.sequence, item.pending_index
@@ -254,7 +285,7 @@ class Scheduler:
             if index >= len(seq.tokens):               # the request ended on an earlier token
                 continue
             if token < 0:
-                raise SchedulerError("The model runner did not return a token for a completed step.")
+                raise SchedulerError(f"no token was sampled for request {seq.id}, whose step asked for one")
             seq.tokens[index] = int(token)
             seq.pending -= 1
             self.cache.fill_token(seq.id, index, int(token))

@@ -19,11 +19,11 @@ class SamplingParams:
 
     def validate(self) -> None:
         if self.max_tokens < 0:
-            raise ValueError("max_tokens cannot be negative.")
+            raise ValueError(f"max_tokens is {self.max_tokens}; it cannot be negative")
         if self.temperature < 0.0:
-            raise ValueError("temperature cannot be negative.")
+            raise ValueError(f"temperature is {self.temperature}; it cannot be negative")
         if not 0.0 < self.top_p <= 1.0:
-            raise ValueError("top_p must be in the interval (0, 1].")
+            raise ValueError(f"top_p is {self.top_p}; it must lie in (0, 1]")
 
     @property
     def greedy(self) -> bool:
