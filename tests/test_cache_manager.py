@@ -7,8 +7,8 @@ import pytest
 from tiny_llm_infer_b200.cache import CacheError, CacheManager, OutOfPages, OutOfSlots, PagePool
 from tiny_llm_infer_b200.parts.spec import CacheSpec, StateSpec
 
-FULL = {0: (CacheSpec(2, 16, None), None), 1: (CacheSpec(2, 16, None), None)}
-MIXED = {0: (CacheSpec(2, 16, 24), None), 1: (CacheSpec(2, 16, None), None), 2: (CacheSpec(2, 16, 24), None)}
+FULL = {0: (CacheSpec.keys_and_values(2, 16, None), None), 1: (CacheSpec.keys_and_values(2, 16, None), None)}
+MIXED = {0: (CacheSpec.keys_and_values(2, 16, 24), None), 1: (CacheSpec.keys_and_values(2, 16, None), None), 2: (CacheSpec.keys_and_values(2, 16, 24), None)}
 
 
 def test_pool_lowest_first_and_double_free():
@@ -126,7 +126,7 @@ def test_random_orders_keep_every_invariant(needs, seed):
 
 def test_state_slots_are_zeroed_at_admission():
     import torch
-    needs = {0: (None, StateSpec((3, 2), "float32")), 1: (CacheSpec(1, 16, None), None)}
+    needs = {0: (None, StateSpec((3, 2), "float32")), 1: (CacheSpec.keys_and_values(1, 16, None), None)}
     m = CacheManager(needs, 8, 4, max_slots=2, max_seq_len=32, dtype=torch.float32, device="cpu")
     assert m.state[0].shape == (2, 3, 2) and m.kv[1].shape == (4, 2, 1, 8, 16)
     slot = m.admit("a")
@@ -216,7 +216,7 @@ def test_prefix_needs_tokens_and_full_caches_without_state():
     m.commit("c", 9, list(range(35, 39)))
     assert run_request(m, "d", list(range(30, 39))) == 0
     assert not CacheManager(MIXED, 4, 8, 2, 64, prefix_cache=True).prefix_active
-    with_state = {0: (CacheSpec(2, 16, None), StateSpec((3,), "float32"))}
+    with_state = {0: (CacheSpec.keys_and_values(2, 16, None), StateSpec((3,), "float32"))}
     assert not CacheManager(with_state, 4, 8, 2, 64, prefix_cache=True).prefix_active
 
 

@@ -43,6 +43,11 @@ def test_toy_parts_on_the_host_side(tmp_path, cpu_ops):
     run_toy(tmp_path, "cpu")
 
 
+def test_sandwich_parts_on_the_host_side(tmp_path, cpu_ops):
+    from test_engine_gpu import run_sandwich
+    run_sandwich(tmp_path, "cpu")
+
+
 def test_prefix_cache_changes_no_token(tmp_path, cpu_ops):
     """Prompts that begin alike share full pages (the second call finds the pages of the first,
     freed but not yet handed out again); what is generated is what the plain implementation

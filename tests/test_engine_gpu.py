@@ -253,6 +253,53 @@ def test_toy_parts_and_run_order_need_no_change_to_the_framework(tmp_path):
     run_toy(tmp_path, "cuda:0")
 
 
+def run_sandwich(tmp_path, device):
+    """A block of four norms, a block with two mixers (two caches per visit, named in the run order) and
+    a mixer whose cache is one vector per token: built from a folder, pool sized through the parts' own
+    ``workspace_floats``, stepped in portions beside a second request, against a plain restatement."""
+    from toys import register_sandwich, sandwich_plain
+    Config = register_sandwich()
+    from tiny_llm_infer_b200.cache import CacheManager
+    from tiny_llm_infer_b200.engine import ModelRunner, StepEntry, load_model
+    from tiny_llm_infer_b200.weights import write_random_model
+    folder = write_random_model(tmp_path / "sandwich", Config(), seed=6, std=0.15, norm_range=(0.7, 1.3))
+    _, w = plain.read_model(folder)
+    model, cfg = load_model(folder, torch.float32, device)
+    needs = model.cache_needs()
+    # layer 0 visited twice (a cache each), layer 1 once with the two caches the run order names
+    assert sorted(needs) == [7, 8, 9, 10]
+    assert needs[8][0].planes == ((1, 24),) and needs[7][0].planes == ((1, 16), (1, 16))
+    per_page = CacheManager.bytes_per_page(needs, 8, torch.float32)
+    assert per_page == {None: 4 * 8 * (3 * 2 * 16 + 24)}
+    assert model.workspace_floats(10, 2) == 6 * 10 * 40 + 10 * 3 * 56 + 2 * 120    # the SwiGLU is the widest part
+    cache = CacheManager(needs, 8, 24, 3, 128, torch.float32, device)
+    assert cache.kv[8].shape == (24, 1, 1, 8, 24) and cache.kv[7].shape == (24, 2, 1, 8, 16)
+    runner = ModelRunner(model, cache, 256)
+    a, b = prompt(3, 50, 120), prompt(4, 37, 120)
+    want_a, want_b = sandwich_plain(w, a, 1e-5), sandwich_plain(w, b, 1e-5)
+    got_a, got_b, ia, ib = [], [], 0, 0
+    for na, nb in ((7, 0), (2, 20), (13, 1), (1, 1), (1, 15), (26, 0)):
+        entries = []
+        if na:
+            entries.append(StepEntry("a", a[ia:ia + na], list(range(na))))
+        if nb:
+            entries.append(StepEntry("b", b[ib:ib + nb], list(range(nb))))
+        out = runner.step(entries).cpu().double()
+        got_a.append(out[:na]), got_b.append(out[na:])
+        ia, ib = ia + na, ib + nb
+    assert (torch.cat(got_a) - want_a).abs().max() < 2e-4
+    assert (torch.cat(got_b) - want_b).abs().max() < 2e-4
+    runner.release("a")
+    runner.release("b")
+    cache.audit()
+    whole = runner.step([StepEntry("c", b, list(range(37)))]).cpu().double()     # pages used again
+    assert (whole - want_b).abs().max() < 2e-4
+
+
+def test_blocks_with_four_norms_and_two_mixers_and_a_one_vector_cache(tmp_path):
+    run_sandwich(tmp_path, "cuda:0")
+
+
 @pytest.mark.parametrize("name,dtype", [("B", "float32"), ("E", "bfloat16")])
 def test_repeated_prompt_layouts_replay_as_graphs(folders, name, dtype):
     """A step layout that comes a second time is captured as a CUDA graph and replayed from the

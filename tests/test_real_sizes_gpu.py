@@ -74,7 +74,8 @@ def requests_of(vocab, lengths=LENGTHS):
 
 def sharpen(model, factor=2.0):
     for block in model.blocks:
-        block.mixer.q_gain.mul_(factor)
+        for mixer in block.mixers():
+            mixer.q_gain.mul_(factor)
 
 
 def runner_for(model, dtype, requests):

@@ -8,7 +8,7 @@ from tiny_llm_infer_b200.engine.scheduler import (Scheduler, SchedulerConfig, Sc
 from tiny_llm_infer_b200.parts.spec import CacheSpec
 from tiny_llm_infer_b200.sampling import SamplingParams
 
-NEEDS = {0: (CacheSpec(1, 16, None), None)}
+NEEDS = {0: (CacheSpec.keys_and_values(1, 16, None), None)}
 
 
 def make(pages=16, budget=32, seqs=4, page=8):

@@ -132,12 +132,13 @@ class PagePool:
 @dataclass
 class LayerCacheView:
     """What one visit of a mixer sees of the cache."""
-    kv: Optional[torch.Tensor]            # [pages, 2, kv_heads, page_size, head_dim]
+    kv: Optional[torch.Tensor]            # planes of one shape: [pages, planes, heads, page_size, width]; else None
     block_table: Optional[torch.Tensor]   # [slots, max_pages] int32, -1 where no page
     page_size: int
     writes: bool
     state: Optional[torch.Tensor]         # [slots, *state shape]
     window: Optional[int] = None
+    planes: Tuple[torch.Tensor, ...] = ()  # per plane a view [pages, heads, page_size, width] of the cache's pages
 
 
 class _Group:
@@ -230,7 +231,9 @@ class CacheManager:
         self._chain: List[bytes] = [b""] * max_slots                   # hash of the last of them
         self.prefix_hit_pages = 0
         self.prefix_lookups = 0
-        self.kv: Dict[int, torch.Tensor] = {}
+        self.pages: Dict[int, torch.Tensor] = {}                       # per cache [pages, elements of a page]
+        self.planes: Dict[int, Tuple[torch.Tensor, ...]] = {}
+        self.kv: Dict[int, torch.Tensor] = {}                          # the same memory, where all planes have one shape
         self.state: Dict[int, torch.Tensor] = {}
         if device is not None:
             self._allocate_device()
@@ -239,10 +242,20 @@ class CacheManager:
     def _allocate_device(self) -> None:
         for cache_id, (spec, state) in self._specs.items():
             if spec is not None:
+                # a page holds its planes one after the other, each [heads, page_size, width]: the tokens
+                # of one head of one plane are one contiguous block
                 g = self._cache_group[cache_id]
-                self.kv[cache_id] = torch.zeros(
-                    (g.pool.num_pages, 2, spec.kv_heads, self.page_size, spec.head_dim),
-                    dtype=self.dtype, device=self.device)
+                flat = torch.zeros((g.pool.num_pages, self.page_size * spec.elements_per_token),
+                                   dtype=self.dtype, device=self.device)
+                views, at = [], 0
+                for heads, width in spec.planes:
+                    n = heads * self.page_size * width
+                    views.append(flat[:, at:at + n].unflatten(1, (heads, self.page_size, width)))
+                    at += n
+                self.pages[cache_id], self.planes[cache_id] = flat, tuple(views)
+                if spec.uniform:
+                    heads, width = spec.planes[0]
+                    self.kv[cache_id] = flat.view(g.pool.num_pages, len(spec.planes), heads, self.page_size, width)
             if state is not None:
                 self.state[cache_id] = torch.zeros((self.max_slots, *state.shape),
                                                    dtype=getattr(torch, state.dtype), device=self.device)
@@ -258,7 +271,7 @@ class CacheManager:
         out: Dict[Optional[int], int] = {}
         for spec, _ in needs.values():
             if spec is not None:
-                out[spec.window] = out.get(spec.window, 0) + 2 * spec.kv_heads * page_size * spec.head_dim * size
+                out[spec.window] = out.get(spec.window, 0) + spec.elements_per_token * page_size * size
         return out
 
     def sync(self) -> None:
@@ -283,7 +296,7 @@ class CacheManager:
         return LayerCacheView(
             kv=self.kv.get(cache_id), block_table=None if g is None else g.device_table,
             page_size=self.page_size, writes=writes, state=self.state.get(cache_id),
-            window=None if g is None else g.window)
+            window=None if g is None else g.window, planes=self.planes.get(cache_id, ()))
 
     # ------------------------------------------------------------------ requests
     @property

@@ -6,8 +6,9 @@
 Options keep the reference's names, meanings and defaults (model/model_main.cpp:41-60,
 465-559): ``--max-new-tokens`` 64, ``--max-seq-len`` 2048 (256 for ``--bench``),
 ``--num-kv-blocks`` 0 (sized from free memory), ``--gpu-memory-utilization`` 0.9 (0.7 for
-``--bench``); the engine runs with up to min(16, prompts) requests, a token budget of
-min(max-seq-len, 256) and pages of 16 tokens (model/model_main.cpp:403-408).  ``--infer``
+``--bench``); the engine runs with up to min(16, prompts) requests (``--bench``: ``--num-seqs``,
+model/model_main.cpp:276-279), a token budget of min(max-seq-len, 256) and pages of 16 tokens
+(model/model_main.cpp:403-408).  ``--infer``
 is greedy unless ``--temperature`` is given.  ``--bench`` makes seeded synthetic requests
 as the reference does (:150-175): lengths uniform in the ranges, ids uniform in
 [0, min(max-token-id, vocab-1)], temperature 0.6, EOS ignored, request seed
@@ -133,16 +134,25 @@ def main(argv=None) -> int:
 
     # --bench
     max_seq_len = args.max_seq_len or 256
+    if min(args.num_seqs, args.min_input_len, args.min_output_len, args.repeats) <= 0 or args.warmup < 0 \
+            or args.min_input_len > args.max_input_len or args.min_output_len > args.max_output_len \
+            or args.max_token_id < 0:
+        print("--bench needs positive counts and ranges with min <= max", file=sys.stderr)      # model/model_main.cpp:130-146
+        return 2
     if args.max_input_len + args.max_output_len > max_seq_len + 1:
         print("--max-input-len + --max-output-len exceed --max-seq-len", file=sys.stderr)
         return 2
     llm = LLM(args.model, dtype=args.dtype, max_model_len=max_seq_len, num_kv_blocks=args.num_kv_blocks,
-              block_size=16, max_num_batched_tokens=min(max_seq_len, 256), max_num_seqs=min(16, args.num_seqs),
+              block_size=16, max_num_batched_tokens=min(max_seq_len, 256), max_num_seqs=args.num_seqs,
               gpu_memory_utilization=args.gpu_memory_utilization or 0.7, device=device,
               enable_prefix_caching=not args.no_prefix_caching,
               overlap_scheduling=not args.no_overlap_scheduling, prompt_graphs=args.prompt_graphs)
     vocab = llm.runner.vocab
     import torch
+
+    def wait():
+        if device.startswith("cuda"):
+            torch.cuda.synchronize()
 
     def run(requests) -> int:
         outs = llm.engine.generate([p for p, _ in requests], [s for _, s in requests])
@@ -162,10 +172,10 @@ def main(argv=None) -> int:
             manifest = {"requests": [dict(prompt_token_ids=p, max_tokens=s.max_tokens, temperature=s.temperature,
                                           top_p=s.top_p, ignore_eos=s.ignore_eos, seed=s.seed) for p, s in requests]}
             Path(f"{args.manifest_prefix}_run{index + 1}.json").write_text(json.dumps(manifest, indent=2) + "\n")
-        torch.cuda.synchronize()
+        wait()
         started = time.perf_counter()
         tokens = run(requests)
-        torch.cuda.synchronize()
+        wait()
         elapsed = time.perf_counter() - started
         total_tokens += tokens
         total_elapsed += elapsed

@@ -314,22 +314,22 @@ static int launch_decode(const void* q, const void* cache, const int* positions,
                          int page_size, int q_heads, int kv_heads, int window, float scale, int splits,
                          float* part_o, float* part_ml, bool cluster, void* out, cudaStream_t stream) {
     const size_t smem = (size_t)kDecWarps * kDecStages * 2 * kTileKeys * HD * 2;
-    static bool configured = false;
-    if (!configured) {
+    static OncePerDevice configured;
+    if (configured.first()) {
         cudaError_t e = cudaFuncSetAttribute(paged_attention_decode_kernel<HD>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) { set_error("paged_attention_decode: %s", cudaGetErrorString(e)); return (int)e; }
-        configured = true;
+        configured.done();
     }
     const dim3 grid(splits, kv_heads, n_rows);
     if (cluster && splits > 1 && splits <= 16) {
         // the splits of a (row, key/value head) as one cluster (more than 8 blocks need the opt-in)
-        static bool wide = false;
-        if (splits > 8 && !wide) {
+        static OncePerDevice wide;
+        if (splits > 8 && wide.first()) {
             cudaError_t e = cudaFuncSetAttribute(paged_attention_decode_kernel<HD>,
                                                  cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
             if (e != cudaSuccess) { set_error("paged_attention_decode: %s", cudaGetErrorString(e)); return (int)e; }
-            wide = true;
+            wide.done();
         }
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = grid;

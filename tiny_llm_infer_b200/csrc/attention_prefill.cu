@@ -194,12 +194,12 @@ static int launch_prefill(const void* q, const void* cache, const int* seg_info,
                           int n_tiles, const int* block_table, int max_pages, int page_size, int q_heads,
                           int kv_heads, int window, float scale, void* out, cudaStream_t stream) {
     const size_t smem = (size_t)4 * kBN * HD * 2;
-    static bool configured = false;
-    if (!configured) {
+    static OncePerDevice configured;
+    if (configured.first()) {
         cudaError_t e = cudaFuncSetAttribute(paged_attention_prefill_kernel<HD>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) { set_error("paged_attention_prefill: %s", cudaGetErrorString(e)); return (int)e; }
-        configured = true;
+        configured.done();
     }
     launch_pdl(kPdlAttention, paged_attention_prefill_kernel<HD>, dim3(n_tiles, q_heads), dim3(kPfWarps * 32), smem, stream,
         (const bf16*)q, (const bf16*)cache, seg_info, tiles, block_table, max_pages, page_size, q_heads,

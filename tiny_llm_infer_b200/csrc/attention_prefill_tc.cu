@@ -696,12 +696,12 @@ extern "C" int tllm_paged_attention_prefill_tc(
     CUtensorMap mq;
     TLLM_REQUIRE(pftc::make_map(&mq, q, tokens, (long long)q_heads * 128, 128),
                  "paged_attention_prefill_tc: cuTensorMapEncodeTiled failed or is not available");
-    static bool configured = false;
-    if (!configured) {
+    static OncePerDevice configured;
+    if (configured.first()) {
         cudaError_t e = cudaFuncSetAttribute(pftc::paged_attention_prefill_tc_kernel,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, pftc::kSmemBytes);
         if (e != cudaSuccess) { set_error("paged_attention_prefill_tc: %s", cudaGetErrorString(e)); return (int)e; }
-        configured = true;
+        configured.done();
     }
     const int rows_per_tile = tllm_paged_attention_prefill_tc_rows(q_heads, kv_heads);
     const int pair_heads = rows_per_tile == 128;

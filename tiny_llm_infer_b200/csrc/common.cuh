@@ -92,6 +92,21 @@ inline cudaError_t launch_pdl(int cls, void (*kernel)(KArgs...), dim3 grid, dim3
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// Set-up that a launcher does once per device (a function attribute belongs to the device that was
+// current when it was set): `OncePerDevice flag;` as a function-local static, then
+// `if (flag.first()) { ...; flag.done(); }`.  first() is false for a device index it cannot tell or
+// hold, so that the set-up is then simply repeated at every call.
+struct OncePerDevice {
+    static constexpr int kMax = 64;
+    bool seen[kMax] = {};
+    int device = -1;
+    bool first() {
+        if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMax) { device = -1; return true; }
+        return !seen[device];
+    }
+    void done() { if (device >= 0) seen[device] = true; }
+};
+
 // Host side: the last error text of this thread's most recent failing entry point.
 void set_error(const char* fmt, ...);
 

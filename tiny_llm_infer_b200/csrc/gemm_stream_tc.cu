@@ -387,12 +387,12 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* y, int M, 
     const size_t part_bytes = (size_t)MB * (kTileN + 4) * 4;
     if (smem < part_bytes) smem = part_bytes;
     smem += 1024;
-    static bool configured = false;
-    if (!configured) {
+    static OncePerDevice configured;
+    if (configured.first()) {
         cudaError_t e = cudaFuncSetAttribute(gemm_stream_tc_kernel<MB, SWIGLU, OutT>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
         if (e != cudaSuccess) { set_error("gemm_stream_tc: %s", cudaGetErrorString(e)); return (int)e; }
-        configured = true;
+        configured.done();
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(splits, (N + kTileN - 1) / kTileN);

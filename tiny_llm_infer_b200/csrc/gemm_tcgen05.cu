@@ -414,12 +414,12 @@ template <bool SWIGLU, int MT>
 static int launch_tcgen05(const CUtensorMap& mx, const CUtensorMap& mw, void* y, int M, int N, int K, int half_n,
                           int interleaved, int* error_word, cudaStream_t stream) {
     const size_t smem = (size_t)(MT == 1 ? 4 : 3) * (kBM * MT * kBK * 2 + kStageBBytes) + 1024 + 4 * 32 * (64 * 2 + 16);
-    static bool configured = false;
-    if (!configured) {
+    static OncePerDevice configured;
+    if (configured.first()) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<SWIGLU, MT>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) { set_error("gemm_tcgen05: %s", cudaGetErrorString(e)); return (int)e; }
-        configured = true;
+        configured.done();
     }
     const int out_cols = SWIGLU ? half_n : N;
     const int col_tile = SWIGLU ? 128 : kBN;

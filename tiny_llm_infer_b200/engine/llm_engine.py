@@ -253,20 +253,19 @@ class LLMEngine:
 
 # ---------------------------------------------------------------------- pool sizing
 def estimate_num_kv_blocks(model, block_size: int, dtype: torch.dtype, max_num_batched_tokens: int,
-                           gpu_memory_utilization: float, device) -> int:
+                           gpu_memory_utilization: float, device, max_num_seqs: int = 16,
+                           memory: Optional[tuple] = None) -> int:
     """Pages that fit beside the weights: budget = total * utilization - used now; a
     reserve of max(256 MiB, total / 20, the step's workspace) stays free (the reference's
-    rule, model/src/qwen3.cpp:96-151, with this engine's workspace: the widest
-    activations of a step)."""
+    rule, model/src/qwen3.cpp:96-151, with this engine's workspace: what the model's parts
+    say they make in a step, ``Model.workspace_floats``).  ``memory``: (free, total) bytes
+    instead of asking the device."""
     if not 0.0 < gpu_memory_utilization <= 0.95:
         raise ValueError("gpu_memory_utilization must be in (0, 0.95]")
-    free, total = torch.cuda.mem_get_info(device)
+    free, total = memory if memory is not None else torch.cuda.mem_get_info(device)
     used = total - free
     per_page = sum(CacheManager.bytes_per_page(model.cache_needs(), block_size, dtype).values())
-    d = model.desc
-    widest = max([d.hidden_size] + [p.params.get("intermediate_size", 0) * 3 for l in d.layers
-                                    for p in l.parts.values()])
-    workspace = 4 * max_num_batched_tokens * (6 * d.hidden_size + widest)
+    workspace = 4 * model.workspace_floats(max_num_batched_tokens, min(max_num_seqs, max_num_batched_tokens))
     reserve = max(256 << 20, total // 20, workspace)
     budget = int(total * gpu_memory_utilization) - used - reserve
     return max(0, budget // max(per_page, 1))
@@ -303,8 +302,8 @@ class LLM:
         if max_num_batched_tokens is None:
             max_num_batched_tokens = min(max_model_len, 256)
         if num_kv_blocks <= 0:
-            num_kv_blocks = estimate_num_kv_blocks(self.model, block_size, torch_dtype,
-                                                   max_num_batched_tokens, gpu_memory_utilization, device)
+            num_kv_blocks = estimate_num_kv_blocks(self.model, block_size, torch_dtype, max_num_batched_tokens,
+                                                   gpu_memory_utilization, device, max_num_seqs)
             cap = -(-max_model_len // block_size) * max_num_seqs
             num_kv_blocks = min(num_kv_blocks, cap)
             if num_kv_blocks <= 0:

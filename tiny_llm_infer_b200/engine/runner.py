@@ -98,8 +98,8 @@ class ModelRunner:
         # a step may be captured as a CUDA graph only if every launch of it reads the step's data from
         # device buffers: mixers say so themselves (graph_safe = True), other parts may say no
         self._graph_safe = all(
-            getattr(b.mixer, "graph_safe", False)
-            and all(getattr(getattr(b, role, None), "graph_safe", True) for role in getattr(b, "roles", ()) if role != "mixer")
+            all(getattr(m, "graph_safe", False) for m in b.mixers())
+            and all(getattr(part, "graph_safe", True) for part in b.parts.values() if part not in b.mixers())
             for b in model.blocks)
         self._graph_pool = None
         self._prompt_pool = None

@@ -23,15 +23,12 @@ def _specs(category: str, spec: PartSpec) -> Dict[str, ParamSpec]:
             registry.lookup(category, spec.kind).param_specs(**spec.params).items()}
 
 
-_ROLE_CATEGORY = {"norm1": "norm", "norm2": "norm", "norm": "norm", "mixer": "mixer",
-                  "ffn": "feed_forward", "feed_forward": "feed_forward"}
-
-
-def role_category(role: str) -> str:
-    try:
-        return _ROLE_CATEGORY[role]
-    except KeyError:
-        raise KeyError(f"a block role must be one of {sorted(_ROLE_CATEGORY)}, got {role!r}") from None
+def role_categories(block: str) -> Dict[str, str]:
+    """role -> registry of its part, as the block class declares them."""
+    roles = registry.lookup("block", block).roles
+    if not isinstance(roles, dict):
+        raise TypeError(f"block {block!r} must declare roles as {{role: registry}}, got {roles!r}")
+    return roles
 
 
 def expected_tensors(desc: ModelDescription) -> Tuple[Dict[str, ParamSpec], List[str]]:
@@ -40,8 +37,11 @@ def expected_tensors(desc: ModelDescription) -> Tuple[Dict[str, ParamSpec], List
     out: Dict[str, ParamSpec] = {}
     out.update(_specs("embedding", desc.embedding))
     for layer in desc.layers:
+        roles = role_categories(layer.block)
         for role, spec in layer.parts.items():
-            out.update(_specs(role_category(role), spec))
+            if role not in roles:
+                raise KeyError(f"block {layer.block!r} has roles {sorted(roles)}, the layer names {role!r}")
+            out.update(_specs(roles[role], spec))
     out.update(_specs("norm", desc.final_norm))
     head = _specs("head", desc.head)
     out.update(head)
@@ -56,19 +56,21 @@ class Model:
         self.blocks = []
         self._parts: List[Tuple[PartSpec, object]] = [(desc.embedding, self.embedding)]
         for layer in desc.layers:
+            roles = role_categories(layer.block)
+            missing = [r for r in roles if r not in layer.parts]
+            unknown = [r for r in layer.parts if r not in roles]
+            if missing or unknown:
+                raise ValueError(f"block {layer.block!r} has roles {sorted(roles)}: missing {missing}, unknown {unknown}")
             parts = {}
             for role, spec in layer.parts.items():
-                parts[role] = _make(role_category(role), spec, dtype, device)
+                parts[role] = _make(roles[role], spec, dtype, device)
                 self._parts.append((spec, parts[role]))
-            block_cls = registry.lookup("block", layer.block)
-            missing = [r for r in block_cls.roles if r not in parts]
-            if missing:
-                raise ValueError(f"block {layer.block!r} needs parts {missing}")
-            self.blocks.append(block_cls(parts))
+            self.blocks.append(registry.lookup("block", layer.block)(parts))
         self.final_norm = _make("norm", desc.final_norm, dtype, device)
         self.head = _make("head", desc.head, dtype, device)
         self._parts += [(desc.final_norm, self.final_norm), (desc.head, self.head)]
-        self.order = desc.resolved_order()          # (layer, cache id, writes)
+        # (layer, one cache id per mixer of its block, writes)
+        self.order = desc.resolved_order([len(b.mixers()) for b in self.blocks])
         self.loaded = False
 
     # ---- weights
@@ -86,21 +88,36 @@ class Model:
     # ---- what the cache manager must provide, per cache id
     def cache_needs(self) -> Dict[int, Tuple[Optional[CacheSpec], Optional[StateSpec]]]:
         needs: Dict[int, Tuple[Optional[CacheSpec], Optional[StateSpec]]] = {}
-        for layer, cache_id, _ in self.order:
-            mixer = self.blocks[layer].mixer
-            need = (mixer.cache_spec(), mixer.state_spec())
-            if cache_id in needs and needs[cache_id] != need:
-                raise ValueError(f"cache {cache_id} is shared by mixers with different needs")
-            needs[cache_id] = need
+        for layer, cache_ids, _ in self.order:
+            for mixer, cache_id in zip(self.blocks[layer].mixers(), cache_ids):
+                need = (mixer.cache_spec(), mixer.state_spec())
+                if cache_id in needs and needs[cache_id] != need:
+                    raise ValueError(f"cache {cache_id} is shared by mixers with different needs")
+                needs[cache_id] = need
         return needs
+
+    def parts(self) -> List[object]:
+        """Every part of the model (embedding, the layers' parts, final norm, head)."""
+        return [part for _, part in self._parts]
+
+    def workspace_floats(self, tokens: int, wanted: int) -> int:
+        """Float32 words (an upper estimate) of the activations alive at once in a step of ``tokens``
+        rows of which ``wanted`` get logits: the residual stream and a handful of rows of the model's
+        width, plus the widest thing any one part makes.  A part says what it makes with
+        ``workspace_floats(tokens)``; one that does not is taken to stay within the model's width."""
+        widest = max([0] + [int(part.workspace_floats(tokens)) for part in self.parts()
+                            if part is not self.head and hasattr(part, "workspace_floats")])
+        head = int(self.head.workspace_floats(wanted)) if hasattr(self.head, "workspace_floats") else wanted * self.desc.vocab_size
+        return 6 * tokens * self.desc.hidden_size + widest + head
 
     # ---- one step
     def forward(self, ctx, caches) -> torch.Tensor:
         """Logits [len(ctx.want_rows), vocab] float32.  ``caches.view(cache_id, writes)``
-        gives the ``LayerCacheView`` of a visit."""
+        gives the ``LayerCacheView`` of a visit's mixer (a list of them for a block with several)."""
         h = self.embedding.forward(ctx.token_ids)
         pending = None
-        for layer, cache_id, writes in self.order:
-            pending = self.blocks[layer].forward(h, pending, ctx, caches.view(cache_id, writes))
+        for layer, cache_ids, writes in self.order:
+            views = [caches.view(cache_id, writes) for cache_id in cache_ids]
+            pending = self.blocks[layer].forward(h, pending, ctx, views[0] if len(views) == 1 else views)
         x = self.final_norm.forward(h, pending, rows=ctx.want_rows)
         return self.head.forward(x)

@@ -33,6 +33,8 @@ class GroupedQueryAttention:
                  scale: Optional[float] = None):
         if q_heads % kv_heads:
             raise ValueError(f"{q_heads} query heads cannot share {kv_heads} key/value heads")
+        if qk_norm_eps is not None and not qk_norm_eps > 0.0:
+            raise ValueError(f"qk_norm_eps must be positive (or None for no head norm), got {qk_norm_eps}")
         self.hidden, self.q_heads, self.kv_heads, self.head_dim = hidden_size, q_heads, kv_heads, head_dim
         self.dtype, self.device = dtype, device
         self.qk_norm_eps = qk_norm_eps
@@ -69,10 +71,13 @@ class GroupedQueryAttention:
 
     # ---- what the cache manager has to provide
     def cache_spec(self) -> Optional[CacheSpec]:
-        return CacheSpec(self.kv_heads, self.head_dim, self.window)
+        return CacheSpec.keys_and_values(self.kv_heads, self.head_dim, self.window)
 
     def state_spec(self) -> Optional[StateSpec]:
         return None
+
+    def workspace_floats(self, tokens: int) -> int:
+        return tokens * (3 * self.q_heads + 2 * self.kv_heads) * self.head_dim     # q|k|v, q, the heads' outputs
 
     # ---- one step
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
@@ -81,7 +86,7 @@ class GroupedQueryAttention:
         q = torch.empty((tokens, self.q_heads * self.head_dim), dtype=self.dtype, device=x.device)
         norm = ops.QK_NORM if self.qk_norm_eps is not None else 0
         store = ops.QK_STORE if cache.writes else 0
-        eps = self.qk_norm_eps or 1.0
+        eps = self.qk_norm_eps if self.qk_norm_eps is not None else 1.0
         args = dict(positions=ctx.positions, token_slot=ctx.token_slot, block_table=cache.block_table,
                     cache=cache.kv, page_size=cache.page_size, q_out=q, q_heads=self.q_heads,
                     kv_heads=self.kv_heads, head_dim=self.head_dim)

@@ -7,20 +7,36 @@ last layer is taken by the model's final norm.
 """
 from __future__ import annotations
 
-from typing import Dict, Optional
+from typing import Dict, List, Optional
 
 import torch
 
 from .registry import register
 
 
-@register("block", "prenorm")
-class PreNormBlock:
-    roles = ("norm1", "mixer", "norm2", "ffn")
+class Block:
+    """Base of the arrangements.  A block class declares ``roles``: the names of the parts it
+    arranges and, for each, the registry it is chosen from (``norm``, ``mixer``,
+    ``feed_forward``); any number of each.  The model builds the parts a layer's description
+    gives for these names and hands them over; they become attributes under their role names.
+    ``forward(h, pending, ctx, cache)``: ``cache`` is the ``LayerCacheView`` of the block's mixer,
+    or, for a block with several mixers, the list of their views in the order of ``roles``."""
+    roles: Dict[str, str] = {}
 
     def __init__(self, parts: Dict[str, object]):
-        self.norm1, self.mixer = parts["norm1"], parts["mixer"]
-        self.norm2, self.ffn = parts["norm2"], parts["ffn"]
+        self.parts = {role: parts[role] for role in self.roles}
+        for role, part in self.parts.items():
+            setattr(self, role, part)
+
+    def mixers(self) -> List[object]:
+        """The block's mixers in the order of ``roles`` (the cache manager and the run order give
+        each a cache of its own)."""
+        return [self.parts[role] for role, category in self.roles.items() if category == "mixer"]
+
+
+@register("block", "prenorm")
+class PreNormBlock(Block):
+    roles = {"norm1": "norm", "mixer": "mixer", "norm2": "norm", "ffn": "feed_forward"}
 
     def forward(self, h: torch.Tensor, pending: Optional[torch.Tensor], ctx, cache) -> torch.Tensor:
         x = self.norm1.forward(h, pending)

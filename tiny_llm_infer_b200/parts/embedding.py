@@ -52,5 +52,8 @@ class LMHead:
         if self.tied:
             self.weight = embedding.weight
 
+    def workspace_floats(self, rows: int) -> int:
+        return rows * self.vocab                 # the logits
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return ops.linear(x, self.weight, out_dtype=torch.float32)

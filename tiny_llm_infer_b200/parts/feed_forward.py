@@ -40,6 +40,9 @@ class SwiGLUFeedForward:
             self.w_gate_up = torch.cat([p.to(common) for p in parts], dim=0).contiguous()
         self.w_down = t["down_proj.weight"].contiguous()
 
+    def workspace_floats(self, tokens: int) -> int:
+        return 3 * tokens * self.inter          # the product of gate and up, and the activation
+
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         act = ops.linear_swiglu(x, self.w_gate_up, out_dtype=self.dtype, interleaved=self.interleaved)
         return ops.linear(act, self.w_down, out_dtype=self.dtype)

@@ -10,7 +10,7 @@ The reference wires its one decoder layer by hand as a struct of layer pointers
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Dict, List, Optional, Tuple
+from typing import Any, Dict, List, Optional, Sequence, Tuple, Union
 
 
 @dataclass(frozen=True)
@@ -42,10 +42,12 @@ class LayerSpec:
 class ExecEntry:
     """One visit of the run order.  ``layer`` names the layer whose weights run.
     ``cache`` names the cache instance the visit's mixer works on (``None``: an instance
-    of its own).  Two visits that name the same ``cache`` share keys and values; the one
-    with ``writes_cache=False`` only reads what the other has written in this step."""
+    of its own); for a block with several mixers it is a tuple, one id per mixer in the
+    order of the block's roles.  Two visits that name the same ``cache`` share keys and
+    values; the one with ``writes_cache=False`` only reads what the other has written in
+    this step."""
     layer: int
-    cache: Optional[int] = None
+    cache: Union[None, int, Tuple[int, ...]] = None
     writes_cache: bool = True
 
 
@@ -60,36 +62,63 @@ class ModelDescription:
     final_norm: PartSpec
     head: PartSpec
 
-    def resolved_order(self) -> List[Tuple[int, int, bool]]:
-        """(layer, cache id, writes) for every visit, with default cache ids filled in.
-        Cache ids given explicitly keep their value; visits without one get fresh ids
-        above every explicit id."""
-        explicit = [e.cache for e in self.order if e.cache is not None]
+    def resolved_order(self, mixers_per_layer: Optional[Sequence[int]] = None) -> List[Tuple[int, Tuple[int, ...], bool]]:
+        """(layer, cache ids, writes) for every visit, one cache id per mixer of the layer's
+        block (``mixers_per_layer``; one each if not given), with default ids filled in.
+        Cache ids given explicitly keep their value; mixers without one get fresh ids above
+        every explicit id."""
+        def ids_of(entry) -> Tuple[int, ...]:
+            if entry.cache is None:
+                return ()
+            return (entry.cache,) if isinstance(entry.cache, int) else tuple(entry.cache)
+
+        explicit = [c for e in self.order for c in ids_of(e)]
         next_id = (max(explicit) + 1) if explicit else 0
         out = []
         for e in self.order:
             if e.layer < 0 or e.layer >= len(self.layers):
                 raise ValueError(f"run order names layer {e.layer}, model has {len(self.layers)}")
-            if e.cache is None:
-                out.append((e.layer, next_id, e.writes_cache))
-                next_id += 1
-            else:
-                out.append((e.layer, e.cache, e.writes_cache))
-        written = {c for _, c, w in out if w}
-        for layer, cache, writes in out:
-            if not writes and cache not in written:
-                raise ValueError(f"visit of layer {layer} reads cache {cache} that no visit writes")
+            count = 1 if mixers_per_layer is None else mixers_per_layer[e.layer]
+            ids = ids_of(e)
+            if not ids:
+                ids = tuple(range(next_id, next_id + count))
+                next_id += count
+            elif len(ids) != count:
+                raise ValueError(f"visit of layer {e.layer} names {len(ids)} caches, its block has {count} mixers")
+            out.append((e.layer, ids, e.writes_cache))
+        written = {c for _, ids, w in out if w for c in ids}
+        for layer, ids, writes in out:
+            if not writes and any(c not in written for c in ids):
+                raise ValueError(f"visit of layer {layer} reads a cache among {ids} that no visit writes")
         return out
 
 
 @dataclass(frozen=True)
 class CacheSpec:
-    """What a mixer needs from the paged cache: keys and values of ``kv_heads`` heads of
-    width ``head_dim`` per token; ``window=None`` keeps every key, a number keeps the
-    last ``window`` keys."""
-    kv_heads: int
-    head_dim: int
+    """What a mixer keeps per token in the paged cache: one or more *planes*, each ``heads``
+    vectors of ``width`` elements per token (keys and values of grouped-query attention are
+    two planes of equal shape; a mixer that caches one compressed vector per token has one
+    plane of one head; keys and values of different widths are two planes of different
+    shape).  ``window=None`` keeps every token, a number keeps the last ``window``."""
+    planes: Tuple[Tuple[int, int], ...]
     window: Optional[int] = None
+
+    @classmethod
+    def keys_and_values(cls, kv_heads: int, head_dim: int, window: Optional[int] = None) -> "CacheSpec":
+        return cls(((kv_heads, head_dim), (kv_heads, head_dim)), window)
+
+    def __post_init__(self):
+        if not self.planes or any(h <= 0 or w <= 0 for h, w in self.planes):
+            raise ValueError(f"a cache needs at least one plane of positive size, got {self.planes}")
+
+    @property
+    def uniform(self) -> bool:
+        """All planes have one shape: the cache is one tensor [pages, planes, heads, page, width]."""
+        return all(p == self.planes[0] for p in self.planes)
+
+    @property
+    def elements_per_token(self) -> int:
+        return sum(h * w for h, w in self.planes)
 
 
 @dataclass(frozen=True)
