@@ -51,10 +51,11 @@ def json_include() -> Path:
     raise SystemExit("nlohmann/json.hpp not found (the reference needs it)")
 
 
-def build(ref: Path, out: Path, jobs: int = 8) -> None:
-    obj, bins = out / "obj", out / "bin"
+def compile_reference(ref: Path, out: Path, jobs: int = 8):
+    """Compile every source of the reference into ``out/obj``; returns (the g++ command that
+    compiles and links a main against them, the object files, the link flags)."""
+    obj = out / "obj"
     obj.mkdir(parents=True, exist_ok=True)
-    bins.mkdir(parents=True, exist_ok=True)
     incs = []
     for d in ("utils", "memory", "tensor", "kernels", "layers", "model", "engine"):
         incs += ["-I", ref / d / "include"]
@@ -85,6 +86,13 @@ def build(ref: Path, out: Path, jobs: int = 8) -> None:
     for p in running:
         assert p.wait() == 0, "compilation of the reference failed"
     link = ["-L/usr/local/cuda/lib64", "-Wl,-rpath,/usr/local/cuda/lib64", "-lcudart", "-lcublas", "-lcurand", "-lgomp"]
+    return cxx, objects, link
+
+
+def build(ref: Path, out: Path, jobs: int = 8) -> None:
+    cxx, objects, link = compile_reference(ref, out, jobs)
+    bins = out / "bin"
+    bins.mkdir(parents=True, exist_ok=True)
     for name, main in (("model_main", ref / "model" / "model_main.cpp"), ("decode_main", HERE / "decode_main.cpp")):
         cmd = [*cxx, main, *objects, "-o", bins / name, *link]
         print("+ link", name, flush=True)

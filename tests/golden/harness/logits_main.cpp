@@ -1,19 +1,19 @@
 // Golden run, part 1: the reference's own Qwen3Model on the CPU, one whole prompt through
 // forward_paged_batch with a scrambled page table, logits of every row to a file.
-// usage: logits_main MODEL_DIR OUT.bin PAGE_SIZE NUM_PAGES id0 id1 ...
+// usage: logits_main MODEL_DIR OUT.bin PAGE_SIZE NUM_PAGES MAX_SEQ_LEN id0 id1 ...
 #include <cstdio>
 #include <cstdlib>
 #include <vector>
 #include "qwen3.h"
 int main(int argc, char** argv) {
     std::string dir = argv[1];
-    const int page = atoi(argv[3]), pages = atoi(argv[4]);
+    const int page = atoi(argv[3]), pages = atoi(argv[4]), max_seq_len = atoi(argv[5]);
     std::vector<int32_t> toks;
-    for (int i = 5; i < argc; ++i) toks.push_back(atoi(argv[i]));
-    my_vllm::Qwen3Model model(dir + "/tokenizer.json", dir + "/model.safetensors", 128);
+    for (int i = 6; i < argc; ++i) toks.push_back(atoi(argv[i]));
+    my_vllm::Qwen3Model model(dir + "/tokenizer.json", dir + "/model.safetensors", max_seq_len);
     my_vllm::Status s = model.init(my_vllm::DeviceType::kDeviceCPU);
     if (!s) { fprintf(stderr, "init: %s\n", s.get_err_msg().c_str()); return 1; }
-    s = model.configure_paged_kv_cache(pages, page, 64);
+    s = model.configure_paged_kv_cache(pages, page, max_seq_len);
     if (!s) { fprintf(stderr, "kv: %s\n", s.get_err_msg().c_str()); return 1; }
     std::vector<int32_t> table;                       // pages handed out from the top, odd ones first
     for (int p = pages - 1; p >= 0; --p) if (p % 2) table.push_back(p);

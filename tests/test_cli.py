@@ -171,7 +171,9 @@ def test_pool_sized_from_free_memory(tmp_path):
     total, free = 10 << 30, 7 << 30
     per_page = 3 * 2 * 2 * 8 * 32 * 2                   # layers * (K, V) * kv heads * page * head width * bytes
     assert CacheManager.bytes_per_page(model.cache_needs(), 8, torch.bfloat16) == {None: per_page}
-    workspace = 4 * (6 * 32 * 96 + 3 * 32 * 200 + 16 * 384)
+    # residual stream and rows of the model's width; the widest part (attention: q|k|v, q and the heads'
+    # outputs, wider here than the SwiGLU's 3 * 200 per token); the logits of 16 rows
+    workspace = 4 * (6 * 32 * 96 + max(3 * 32 * 200, 32 * (3 * 6 + 2 * 2) * 32) + 16 * 384)
     assert 4 * model.workspace_floats(32, 16) == workspace
     want = (int(total * 0.5) - (total - free) - max(256 << 20, total // 20, workspace)) // per_page
     assert estimate_num_kv_blocks(model, 8, torch.bfloat16, 32, 0.5, "cuda:0", 16, memory=(free, total)) == want

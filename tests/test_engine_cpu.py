@@ -24,6 +24,28 @@ def test_greedy_matches_plain_under_budgets_and_few_pages(tmp_path, cpu_ops, bud
     assert llm.cache.free_pages() == {None: blocks}
 
 
+def test_tiny_b_tied_takes_the_reference_engines_steps(tmp_path, cpu_ops):
+    """The reference's engine on tiny B with a tied head (tests/golden/tiny_b_tied_engine.json):
+    prompts of 1/9/40/70 tokens, 12 greedy tokens each, pages of 8, token budgets 32 and 256, a
+    pool that holds everything and one of 14 pages (the longest request alone needs 11).  This
+    engine gives the same tokens in the same number of steps."""
+    import json
+    from pathlib import Path
+
+    from test_plain import b_tied
+    from tiny_llm_infer_b200 import LLM, SamplingParams
+    meta = json.loads((Path(__file__).parent / "golden" / "tiny_b_tied_engine.json").read_text())
+    folder = make_folder(b_tied(), tmp_path / "m")
+    for run in meta["runs"]:
+        llm = LLM(str(folder), dtype="float32", max_model_len=meta["max_model_len"], num_kv_blocks=run["pages"],
+                  block_size=meta["page_size"], max_num_batched_tokens=run["budget"], max_num_seqs=4, device="cpu",
+                  overlap_scheduling=False)
+        outs = llm.generate(meta["prompts"], SamplingParams(max_tokens=meta["max_tokens"], ignore_eos=True))
+        assert [o.token_ids for o in outs] == run["tokens"], run
+        assert llm.engine.counters.steps == run["steps"], (run["budget"], run["pages"])
+        llm.cache.audit()
+
+
 def test_preemption_and_sampling_keys(tmp_path, cpu_ops):
     from tiny_llm_infer_b200 import LLM, SamplingParams
     folder = make_folder(TINIES["A"], tmp_path / "m")

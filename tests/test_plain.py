@@ -33,6 +33,32 @@ def test_greedy_tokens_match_the_reference_engine(tmp_path):
     assert [r["steps"] for r in meta["runs"]] == [8, 16, 20, 22]
 
 
+def b_tied():
+    import dataclasses
+    return dict(TINIES["B"], cfg=dataclasses.replace(TINIES["B"]["cfg"], tie_word_embeddings=True))
+
+
+def test_tiny_b_with_a_tied_head_matches_the_reference(tmp_path):
+    """Everything tiny B has that tiny A has not, on the reference's own output: three query heads
+    per key/value head, head width 32 with a q width that is not the model's, feed-forward width
+    200, eps 1e-5, theta 1e6, pages of 8, 70 tokens.  (The reference always multiplies by the
+    embedding for the head, so B's head is tied here.)  Weights N(0, 0.05): logits up to 4, FP16
+    rounding of every intermediate tensor accordingly larger than for A."""
+    meta = json.loads((GOLDEN / "tiny_b_tied_engine.json").read_text())
+    ref = np.load(GOLDEN / "tiny_b_tied_logits.npy")
+    cfg, w = plain.read_model(make_folder(b_tied(), tmp_path / "m"))
+    ours = plain.logits_of(cfg, w, meta["logits_prompt"]).numpy()
+    assert ref.shape == ours.shape == (70, 384)
+    assert np.abs(ref).max() > 1.0
+    assert np.abs(ref - ours).max() < 4e-3 * np.abs(ref).max()
+    top = ours.argmax(-1)
+    assert (np.take_along_axis(ref, top[:, None], 1)[:, 0] >= ref.max(-1) - 2e-3).all()
+    greedy = [plain.greedy(cfg, w, p, meta["max_tokens"]) for p in meta["prompts"]]
+    for run in meta["runs"]:
+        assert run["tokens"] == greedy, run
+    assert [r["steps"] for r in meta["runs"]] == [15, 27, 12]
+
+
 def test_causality_and_window(tmp_path):
     """Logits at a position do not depend on later tokens; in a windowed layer not on keys
     the window has passed either."""
