@@ -125,3 +125,21 @@ def compare(out_dir, tb: TraceBuilder, plain_logits: Dict[str, np.ndarray], voca
             if d > top:
                 top, where = d, (step, name, pos)
     return worst, where
+
+
+def row_checks(out_dir, tb: TraceBuilder, plain_logits: Dict[str, np.ndarray], vocab: int):
+    """Two figures that a tolerance on single logits does not give: the largest root-mean-square
+    difference of a row relative to the row's own spread (its standard deviation), and the largest
+    amount by which the engine's argmax falls short of the plain implementation's maximum in the
+    plain implementation's own row (0 where the two pick the same token)."""
+    worst_rms, worst_gap, where = 0.0, 0.0, None
+    for step, rows in tb.expect.items():
+        got = read_logits(out_dir, step, vocab).astype(np.float64)
+        for r, (name, pos) in enumerate(rows):
+            want = plain_logits[name[1:]][pos]
+            rms = float(np.sqrt(np.mean((got[r] - want) ** 2)) / max(float(want.std()), 1e-30))
+            gap = float(want.max() - want[int(got[r].argmax())])
+            if rms > worst_rms:
+                worst_rms, where = rms, (step, name, pos)
+            worst_gap = max(worst_gap, gap)
+    return worst_rms, worst_gap, where

@@ -354,8 +354,8 @@ def request_data(lens, nkv, hd, ps, seed, num_pages, max_pages):
 
 @pytest.mark.parametrize("nh,nkv,hd,ps,window", [(32, 8, 128, 16, None), (4, 2, 64, 16, None), (16, 1, 128, 32, None),
                                                  (6, 2, 64, 64, 100), (3, 3, 128, 16, 33), (14, 2, 64, 16, None)])
-@pytest.mark.parametrize("splits,cluster", [(1, True), (3, True), (8, True), (13, True), (3, False), (8, False), (20, True)])
-def test_decode_kernel_split_keys(ops, nh, nkv, hd, ps, window, splits, cluster):
+@pytest.mark.parametrize("splits", [1, 3, 8, 13, 20])
+def test_decode_kernel_split_keys(ops, nh, nkv, hd, ps, window, splits):
     """One-token rows of four requests (contexts 1 to 700), a padding row, a row list; for
     each query one far key dominates: the first key the window admits or a page's last."""
     lens = [700, 1, 130, 65]
@@ -378,8 +378,7 @@ def test_decode_kernel_split_keys(ops, nh, nkv, hd, ps, window, splits, cluster)
     rows = torch.tensor([0, 1, 3, 4, 6, 5, 2], dtype=torch.int32)          # every row, in another order
     out = torch.full((T, nh * hd), 3.0, dtype=torch.bfloat16, device="cuda")
     ops.paged_attention_decode(dev(q.reshape(T, -1).to(torch.bfloat16)), cache, dev(pos), dev(slot), dev(rows), T,
-                               dev(table), ps, nh, nkv, hd, window, 1 / math.sqrt(hd), out, 700, splits=splits,
-                               cluster=cluster)
+                               dev(table), ps, nh, nkv, hd, window, 1 / math.sqrt(hd), out, 700, splits=splits)
     got = out.cpu().double().view(T, nh, hd)
     assert (got[2] == 0).all()
     for t in range(T):
@@ -600,52 +599,7 @@ def test_gemm_tcgen05(ops, M, N, K, swiglu, short_tiles):
     assert (y.cpu().double() - ref).abs().max() < 1.6e-2 * ref.abs().max()
 
 
-@pytest.mark.parametrize("M", [9, 32, 33, 64, 100, 128])
-@pytest.mark.parametrize("N,K,splits", [(256, 64, 1), (304, 328, 2), (1000, 1000, 8), (80, 4104, 5), (4096, 1024, 3),
-                                        (1008, 4096, None)])
-@pytest.mark.parametrize("mode", ["bf16", "f32", "swiglu"])
-def test_gemm_stream_tc(ops, M, N, K, splits, mode):
-    """The weight-streaming tcgen05 product for 9 to 128 rows: row counts inside and at the edges
-    of the paddings (32, 64, 128), weight rows that end inside a tile of 128, K that ends inside
-    a stage of 64, one to eight blocks sharing a tile's K (one of them left without a stage
-    when K is short), float32 and bfloat16 results, fused SwiGLU over interleaved rows.  One
-    weight row and one k-column are much larger than the rest."""
-    if mode == "swiglu" and N % 16:
-        pytest.skip("interleaved rows come in sixteens")
-    x = rnd(M, K, seed=420, scale=0.5).to(torch.bfloat16)
-    w = rnd(N, K, seed=421, scale=0.5).to(torch.bfloat16)
-    w[N - 1] *= 8
-    w[:, K - 1] *= 6
-    ref = x.double() @ w.double().T
-    if splits is not None and splits > -(-K // 64):
-        with pytest.raises(ops.KernelError, match="splits"):
-            ops.gemm_stream_tc(dev(x), dev(w), splits=splits)
-        return
-    if mode == "swiglu":
-        ref = plain.silu(ref[:, :N // 2]) * ref[:, N // 2:]
-        y = ops.gemm_stream_tc(dev(x), dev(ops.interleave_gate_up(w[:N // 2], w[N // 2:])), swiglu=True, splits=splits)
-    else:
-        y = ops.gemm_stream_tc(dev(x), dev(w), torch.float32 if mode == "f32" else torch.bfloat16, splits=splits)
-    ops.check_error_word("cuda:0")
-    assert y.shape == ref.shape and y.dtype == (torch.float32 if mode == "f32" else torch.bfloat16)
-    assert (y.cpu().double() - ref).abs().max() < (2e-3 if mode == "f32" else 1.6e-2) * ref.abs().max()
-
-
-def test_gemm_stream_tc_refusals_and_rule(ops):
-    x = torch.zeros((129, 64), dtype=torch.bfloat16, device="cuda")
-    w = torch.zeros((128, 64), dtype=torch.bfloat16, device="cuda")
-    with pytest.raises(ops.KernelError, match="outside 1..128"):
-        ops.gemm_stream_tc(x, w)
-    with pytest.raises(ops.KernelError, match="multiple of 8"):
-        ops.gemm_stream_tc(x[:16, :60].contiguous(), w[:, :60].contiguous())
-    with pytest.raises(ops.KernelError, match="sixteens"):
-        ops.gemm_stream_tc(x[:16], w[:72], swiglu=True)
-    # Qwen3-8B: q/k/v 48 tiles x 4, o 32 x 8, gate-up 192 x 1, down 32 x 8; 0.6B: q/k/v 32 x 4, head one block each
-    assert [ops.stream_tc_splits(n, k) for n, k in ((6144, 4096), (4096, 4096), (24576, 4096), (4096, 12288),
-                                                     (4096, 1024), (151936, 1024))] == [4, 8, 1, 8, 4, 1]
-
-
-def test_linear_takes_the_tcgen05_path_for_many_rows(ops, monkeypatch):
+def test_linear_takes_the_tcgen05_path_for_many_rows(ops):
     assert ops.tcgen05_pays(2048, 4096, 4096, torch.bfloat16) and not ops.tcgen05_pays(2048, 6144, 4096, torch.bfloat16)
     assert not ops.tcgen05_pays(64, 4096, 4096, torch.bfloat16) and not ops.tcgen05_pays(2048, 4096, 4096, torch.float32)
     x = rnd(600, 136, seed=410).to(torch.bfloat16)
@@ -666,16 +620,16 @@ def test_linear_takes_the_tcgen05_path_for_many_rows(ops, monkeypatch):
         ops.check_error_word("cuda:0")
         assert (act.cpu().double() - ref[:rows]).abs().max() < 1.6e-2 * ref.abs().max()
     assert ops.tcgen05_calls == before + 2
-    # with the weight-streaming tcgen05 product switched on, 9 to 64 rows take it, fused with SwiGLU
-    monkeypatch.setattr(ops, "STREAM_TC_MAX_ROWS", 64)
-    for rows in (9, 40):
-        act = ops.linear_swiglu(dev(x[:rows]), wi, torch.bfloat16, interleaved=True)
-        y = ops.linear(dev(x[:rows]), dev(w))
-        ops.check_error_word("cuda:0")
-        assert (act.cpu().double() - ref[:rows]).abs().max() < 1.6e-2 * ref.abs().max()
-        full = x[:rows].double() @ w.double().T
-        assert (y.cpu().double() - full).abs().max() < 1.6e-2 * full.abs().max()
-    assert ops.tcgen05_calls == before + 6
+    # the plain product through ``linear``: 3 x 42 tiles of 256 x 256
+    w2 = rnd(10752, 136, seed=412, scale=0.3).to(torch.bfloat16)
+    y = ops.linear(dev(x), dev(w2))
+    assert ops.tcgen05_calls == before + 3
+    ops.check_error_word("cuda:0")
+    full = x.double() @ w2.double().T
+    assert (y.cpu().double() - full).abs().max() < 1.6e-2 * full.abs().max()
+    y9 = ops.linear(dev(x[:9]), dev(w2))                                     # the library's, same values
+    assert ops.tcgen05_calls == before + 3
+    assert (y9.cpu().double() - full[:9]).abs().max() < 1.6e-2 * full.abs().max()
 
 
 @pytest.mark.parametrize("M", [1, 5, 8])
@@ -692,7 +646,7 @@ def test_linear_swiglu_few_rows(ops, M, inter, K):
     acts = [ops.linear_swiglu(dev(x), dev(w), torch.bfloat16)]
     if inter % 8 == 0:
         wi = dev(ops.interleave_gate_up(w[:inter], w[inter:]))
-        acts += [ops.gemm_skinny_swiglu(dev(x), dev(w)), ops.gemm_skinny_swiglu(dev(x), wi, interleaved=True),
+        acts += [ops.gemm_skinny_swiglu(dev(x), wi),
                  ops.linear_swiglu(dev(x), wi, torch.bfloat16, interleaved=True)]
     else:
         with pytest.raises(ops.KernelError, match="multiple of 8"):

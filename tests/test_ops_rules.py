@@ -27,14 +27,6 @@ def test_prefill_splits_fill_the_gpu_only_when_runs_stay_long():
             assert s in (1, 2, 4, 8) and (s == 1 or (blocks * s <= ops.SM_COUNT and -(-ctx // 64) // s >= 8))
 
 
-def test_stream_tc_splits_keep_all_blocks_running_at_once():
-    sizes = ((6144, 4096), (4096, 4096), (24576, 4096), (4096, 12288), (4096, 1024), (151936, 1024))
-    assert [ops.stream_tc_splits(n, k) for n, k in sizes] == [4, 8, 1, 8, 4, 1]
-    for n, k in sizes + ((100, 64), (128, 512), (5000, 8192)):
-        s = ops.stream_tc_splits(n, k)
-        assert s in (1, 2, 4, 8) and s <= max(1, -(-k // 64))
-
-
 def test_the_tcgen05_product_is_chosen_where_its_tiles_fill_the_gpu():
     bf = torch.bfloat16
     assert ops.tcgen05_pays(2048, 4096, 4096, bf) and ops.tcgen05_pays(2048, 12288, 4096, bf, col_tile=128)

@@ -112,11 +112,33 @@ def test_swiglu_part(dtype, I):
          "down_proj.weight": rnd(H, I, seed=3, scale=0.1).to(dtype)}
     part.load({k: v.to(DEV) for k, v in w.items()})
     assert part.interleaved == (I % 8 == 0)
-    for rows in (5, 11, 300):                    # the few-row kernels, the library, the tcgen05 kernel
+    for rows in (5, 11, 300):                    # the few-row kernels, the library (300 rows are too few tiles for tcgen05)
         x = rnd(rows, H, seed=4).to(dtype)
         got = part.forward(x.to(DEV), None).cpu().double()
         want = plain.feed_forward(x.double(), *(w[k].double() for k in ("gate_proj.weight", "up_proj.weight", "down_proj.weight")))
         assert (got - want).abs().max() < tol(dtype, want.abs().max().item())
+
+
+def test_swiglu_part_on_the_tcgen05_product():
+    """A feed-forward wide enough, with rows enough, that both of its products run on the tcgen05
+    kernel (3 x 42 tiles of 256 x 128 for gate/up with SwiGLU, 3 x 42 of 256 x 256 for down)."""
+    from tiny_llm_infer_b200 import ops
+    from tiny_llm_infer_b200.parts.feed_forward import SwiGLUFeedForward
+    H, I, rows, dtype = 10752, 5376, 600, torch.bfloat16
+    part = SwiGLUFeedForward(hidden_size=H, intermediate_size=I, dtype=dtype, device=DEV)
+    w = {"gate_proj.weight": rnd(I, H, seed=1, scale=0.02).to(dtype), "up_proj.weight": rnd(I, H, seed=2, scale=0.02).to(dtype),
+         "down_proj.weight": rnd(H, I, seed=3, scale=0.02).to(dtype)}
+    part.load({k: v.to(DEV) for k, v in w.items()})
+    x = rnd(rows, H, seed=4).to(dtype)
+    before = ops.tcgen05_calls
+    got = part.forward(x.to(DEV), None)
+    assert ops.tcgen05_calls == before + 2
+    ops.check_error_word(DEV)
+    xd = x.to(DEV).double()
+    wd = {k: v.to(DEV).double() for k, v in w.items()}
+    act = plain.silu(xd @ wd["gate_proj.weight"].T) * (xd @ wd["up_proj.weight"].T)
+    want = act.to(dtype).double() @ wd["down_proj.weight"].T          # the part rounds the activation to bfloat16
+    assert (got.double() - want).abs().max() < tol(dtype, want.abs().max().item())
 
 
 def test_prenorm_block_equals_a_plain_decoder_layer():

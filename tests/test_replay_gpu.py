@@ -9,7 +9,10 @@ Tolerances.  float32: 1e-4 absolute on logits of size 1 to 3 (the same compariso
 the kernels restated in float32 torch gives 1e-5).  bfloat16: per configuration, three
 times what a restatement with the engine's rounding points (weights, activations and
 cache in bfloat16, sums in float32) differs from the plain implementation; the ways of
-cutting must agree with one another three times closer than that."""
+cutting must agree with one another three times closer than that.  Beside the bound on single
+logits, per row: the root-mean-square difference relative to the row's own spread (``BF16_RMS``;
+1e-4 in float32), and the engine's argmax must be the plain implementation's or fall short of
+its maximum by less than half the tolerance (1e-4 in float32)."""
 import subprocess
 import sys
 from pathlib import Path
@@ -26,6 +29,9 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 SHARPEN = {"A": 1.0, "B": 1.5, "C": 1.5, "D": 1.5, "E": 1.5}
 BF16_TOL = {"A": 0.012, "B": 0.15, "C": 0.3, "D": 0.17, "E": 0.24}
+# a row's root-mean-square difference relative to the row's standard deviation: two and a half times
+# what a B200 shows (0.006, 0.036, 0.045, 0.031, 0.033); a logit error of a tenth of the row's spread fails
+BF16_RMS = {"A": 0.015, "B": 0.09, "C": 0.11, "D": 0.08, "E": 0.08}
 F32_TOL = 1e-4
 
 
@@ -85,6 +91,11 @@ def test_replay_all_ways_of_cutting(case, dtype, tmp_path):
     assert max(worst.values()) < limit, (worst, where)
     spread = mode_spread(out, tb, cfg["vocab_size"])
     assert max(spread.values()) < limit / 3, spread
+    rms, gap, at = replay.row_checks(out, tb, want, cfg["vocab_size"])
+    print(f"\n[{name} {dtype}] worst {max(worst.values()):.5f}, row rms / row spread {rms:.5f}, argmax short by {gap:.5f}")
+    rms_limit, gap_limit = (1e-4, 1e-4) if dtype == "float32" else (BF16_RMS[name], BF16_TOL[name] / 2)
+    assert rms < rms_limit, (rms, at)
+    assert gap < gap_limit, gap
 
 
 def test_first_tokens_and_page_edges(case, tmp_path):

@@ -29,18 +29,6 @@ constexpr int kTileKeys = 16;
 // at batch 8 and 10.09 at batch 64, two stages 4.14 and 9.92.
 constexpr int kDecStages = 2;
 
-__device__ __forceinline__ void cluster_sync() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
-}
-// a float of shared memory of the block with the given rank in this block's cluster
-__device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, int rank) {
-    uint32_t remote;
-    float v;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(local_addr), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(remote) : "memory");
-    return v;
-}
-
 template <int HD>
 __global__ void __launch_bounds__(kDecWarps * 32)
 paged_attention_decode_kernel(const bf16* q, const bf16* cache,
@@ -48,14 +36,11 @@ paged_attention_decode_kernel(const bf16* q, const bf16* cache,
                               const int* __restrict__ rows, const int* __restrict__ block_table,
                               int max_pages, int page_size, int q_heads, int kv_heads, int window,
                               float scale_log2e, int splits, float* __restrict__ part_o,
-                              float* __restrict__ part_ml, int in_cluster, bf16* __restrict__ out) {
+                              float* __restrict__ part_ml, bf16* __restrict__ out) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    // The kernel after this one may start early once every block has let it.  With a second kernel
-    // to combine the splits that is at once (the short combine then hides the next product's
-    // start); in cluster mode the product would come next, be resident beside this kernel from the
-    // start and fetch its weights in competition with the keys, so it is let in only when this
-    // block has read its keys.
-    if (!in_cluster) TLLM_PDL_TRIGGER();
+    // The kernel after this one (the short one that combines the splits, which in its turn hides the
+    // start of the product after it) may start early once every block has let it.
+    TLLM_PDL_TRIGGER();
     constexpr int kChunks = HD / 8;                 // 16-byte chunks per row
     constexpr int kTileBytes = kTileKeys * HD * 2;  // one K or V tile
     const int split = blockIdx.x, g = blockIdx.y, ridx = blockIdx.z;
@@ -65,7 +50,7 @@ paged_attention_decode_kernel(const bf16* q, const bf16* cache,
     const int slot = token_slot[r];
     if (slot < 0) {
         TLLM_PDL_WAIT();
-        if (splits == 1 || (in_cluster && split == 0))       // else the combine kernel writes the zeros
+        if (splits == 1)                                     // else the combine kernel writes the zeros
             for (int i = threadIdx.x; i < group * HD; i += blockDim.x)
                 out[((size_t)r * q_heads + g * group) * HD + i] = __float2bfloat16_rn(0.0f);
         return;
@@ -215,14 +200,10 @@ paged_attention_decode_kernel(const bf16* q, const bf16* cache,
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
 
     // ---- merge the four warps (shared memory is reused once every copy has landed)
-    if (in_cluster) TLLM_PDL_TRIGGER();
     __syncthreads();
     float* os = reinterpret_cast<float*>(smem_raw);             // [warps][16][HD]
     float* ms = os + kDecWarps * 16 * HD;                       // [warps][16]
     float* ls = ms + kDecWarps * 16;                            // [warps][16]
-    float* bo = ls + kDecWarps * 16;                            // [group][HD]: this block's merged partial,
-    float* bm = bo + 16 * HD;                                   // [16] its maximum
-    float* bl = bm + 16;                                        // [16] and sum (cluster mode)
 #pragma unroll
     for (int i = 0; i < HD / 8; ++i) {
         const int col = i * 8 + (lane & 3) * 2;
@@ -253,35 +234,12 @@ paged_attention_decode_kernel(const bf16* q, const bf16* cache,
         const int head = g * group + row;
         if (splits == 1) {
             out[((size_t)r * q_heads + head) * HD + d] = __float2bfloat16_rn(acc / total);
-        } else if (in_cluster) {
-            bo[idx] = acc;
-            if (d == 0) { bm[row] = mm; bl[row] = total; }
         } else {
             const size_t p_idx = ((size_t)ridx * q_heads + head) * splits + split;
             part_o[p_idx * HD + d] = acc;
             if (d == 0) { part_ml[p_idx * 2] = mm; part_ml[p_idx * 2 + 1] = total; }
         }
     }
-    if (splits == 1 || !in_cluster) return;
-    // ---- the blocks of a (row, key/value head) form a thread-block cluster: every block takes a
-    // share of the outputs and reads the others' partial results out of their shared memory, in
-    // the order of the splits, so nothing goes through global memory and no second kernel runs
-    cluster_sync();
-    const uint32_t bo_s = smem_u32(bo), bm_s = smem_u32(bm), bl_s = smem_u32(bl);
-    for (int idx = split * blockDim.x + threadIdx.x; idx < group * HD; idx += splits * blockDim.x) {
-        const int row = idx / HD, d = idx - row * HD;
-        float mm = -INFINITY;
-        for (int s = 0; s < splits; ++s) mm = fmaxf(mm, ld_cluster_f32(bm_s + row * 4, s));
-        float total = 0.0f, acc = 0.0f;
-        for (int s = 0; s < splits; ++s) {
-            const float m_s = ld_cluster_f32(bm_s + row * 4, s);
-            const float f = m_s == -INFINITY ? 0.0f : exp2f(m_s - mm);
-            total += ld_cluster_f32(bl_s + row * 4, s) * f;
-            acc += ld_cluster_f32(bo_s + idx * 4, s) * f;
-        }
-        out[((size_t)r * q_heads + g * group + row) * HD + d] = __float2bfloat16_rn(acc / total);
-    }
-    cluster_sync();                                          // nobody leaves while its shared memory is read
 }
 
 // out[row, head, :] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), splits in index order.
@@ -312,7 +270,7 @@ template <int HD>
 static int launch_decode(const void* q, const void* cache, const int* positions, const int* token_slot,
                          const int* rows, int n_rows, const int* block_table, int max_pages,
                          int page_size, int q_heads, int kv_heads, int window, float scale, int splits,
-                         float* part_o, float* part_ml, bool cluster, void* out, cudaStream_t stream) {
+                         float* part_o, float* part_ml, void* out, cudaStream_t stream) {
     const size_t smem = (size_t)kDecWarps * kDecStages * 2 * kTileKeys * HD * 2;
     static OncePerDevice configured;
     if (configured.first()) {
@@ -322,37 +280,9 @@ static int launch_decode(const void* q, const void* cache, const int* positions,
         configured.done();
     }
     const dim3 grid(splits, kv_heads, n_rows);
-    if (cluster && splits > 1 && splits <= 16) {
-        // the splits of a (row, key/value head) as one cluster (more than 8 blocks need the opt-in)
-        static OncePerDevice wide;
-        if (splits > 8 && wide.first()) {
-            cudaError_t e = cudaFuncSetAttribute(paged_attention_decode_kernel<HD>,
-                                                 cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-            if (e != cudaSuccess) { set_error("paged_attention_decode: %s", cudaGetErrorString(e)); return (int)e; }
-            wide.done();
-        }
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = grid;
-        cfg.blockDim = dim3(kDecWarps * 32);
-        cfg.dynamicSmemBytes = smem;
-        cfg.stream = stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = splits;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        cudaError_t e = cudaLaunchKernelEx(&cfg, paged_attention_decode_kernel<HD>, (const bf16*)q, (const bf16*)cache,
-                                           positions, token_slot, rows, block_table, max_pages, page_size, q_heads,
-                                           kv_heads, window, scale * 1.4426950408889634f, splits,
-                                           (float*)nullptr, (float*)nullptr, 1, (bf16*)out);
-        if (e != cudaSuccess) { set_error("paged_attention_decode: %s", cudaGetErrorString(e)); return (int)e; }
-        return finish_launch("paged_attention_decode");
-    }
     launch_pdl(kPdlAttention, paged_attention_decode_kernel<HD>, grid, dim3(kDecWarps * 32), smem, stream,
         (const bf16*)q, (const bf16*)cache, positions, token_slot, rows, block_table, max_pages, page_size,
-        q_heads, kv_heads, window, scale * 1.4426950408889634f, splits, part_o, part_ml, 0, (bf16*)out);
+        q_heads, kv_heads, window, scale * 1.4426950408889634f, splits, part_o, part_ml, (bf16*)out);
     int rc = finish_launch("paged_attention_decode");
     if (rc != 0 || splits == 1) return rc;
     launch_pdl(kPdlCombine, paged_attention_combine_kernel<HD>, dim3(n_rows, q_heads), dim3(HD), 0, stream,
@@ -365,9 +295,7 @@ static int launch_decode(const void* q, const void* cache, const int* positions,
 using namespace tllm;
 
 // Scratch the caller provides when splits > 1:
-//   part_o  float[n_rows * q_heads * splits * head_dim],  part_ml  float[n_rows * q_heads * splits * 2];
-// or none (both null) for up to 16 splits: the blocks of a (row, key/value head) then run as one
-// thread-block cluster and combine their partial results through distributed shared memory.
+//   part_o  float[n_rows * q_heads * splits * head_dim],  part_ml  float[n_rows * q_heads * splits * 2].
 extern "C" int tllm_paged_attention_decode(
     const void* q, const void* cache, const int* positions, const int* token_slot, const int* rows,
     int n_rows, const int* block_table, int max_pages, int page_size, int q_heads, int kv_heads,
@@ -380,16 +308,13 @@ extern "C" int tllm_paged_attention_decode(
     TLLM_REQUIRE(page_size > 0 && page_size % 16 == 0, "paged_attention_decode: page size %d is no multiple of 16", page_size);
     TLLM_REQUIRE(splits >= 1 && splits <= 65535 && n_rows >= 0 && n_rows <= 65535 && kv_heads <= 65535,
                  "paged_attention_decode: bad grid");
-    const bool cluster = splits > 1 && part_o == nullptr && part_ml == nullptr;
-    TLLM_REQUIRE(splits == 1 || cluster || (part_o && part_ml), "paged_attention_decode: splits need scratch");
-    TLLM_REQUIRE(!cluster || splits <= 16, "paged_attention_decode: %d splits without scratch exceed a cluster of 16",
-                 splits);
+    TLLM_REQUIRE(splits == 1 || (part_o && part_ml), "paged_attention_decode: %d splits need scratch", splits);
     if (n_rows == 0) return 0;
     if (head_dim == 64)
         return launch_decode<64>(q, cache, positions, token_slot, rows, n_rows, block_table, max_pages, page_size,
-                                 q_heads, kv_heads, window, scale, splits, part_o, part_ml, cluster, out, stream);
+                                 q_heads, kv_heads, window, scale, splits, part_o, part_ml, out, stream);
     return launch_decode<128>(q, cache, positions, token_slot, rows, n_rows, block_table, max_pages, page_size,
-                              q_heads, kv_heads, window, scale, splits, part_o, part_ml, cluster, out, stream);
+                              q_heads, kv_heads, window, scale, splits, part_o, part_ml, out, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -52,23 +52,21 @@ struct SkinnyStage {
     uint4 a_lo[kSkinnyUnroll], a_hi[kSkinnyUnroll], b[kSkinnyUnroll][NT];
 };
 
-// SWIGLU: w holds N gate rows and N up rows; the block owns eight gate rows as the upper half of
-// its 16-row tile and the up rows that belong to them as the lower half, so that a gate sum and
-// its up sum meet in one thread's accumulator; it writes silu(gate) * up: y is [M, N].  The grid,
-// the bytes per block and the registers are those of the plain product of the 2 N rows.  With the
-// rows interleaved by eight in memory (eight gate rows, their eight up rows, and so on) the
-// sixteen rows of a block are neighbours, as in the plain product; stacked ([gate; up]) they are
-// two runs of eight, N rows apart, which streams a fifth slower.
+// SWIGLU: w holds N gate rows and N up rows interleaved by eight (eight gate rows, their eight up
+// rows, and so on); the block's 16-row tile is eight gate rows as its upper half and the up rows
+// that belong to them as its lower half, so that a gate sum and its up sum meet in one thread's
+// accumulator; it writes silu(gate) * up: y is [M, N].  The grid, the bytes per block, the memory
+// pattern and the registers are those of the plain product of the 2 N rows.
 template <int NT, typename TOut, bool SWIGLU>
 __global__ void __launch_bounds__(kSkinnyWarps * 32)
-skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, TOut* y, int M, int N, int K, int interleaved) {
+skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, TOut* y, int M, int N, int K) {
     __shared__ float red[kSkinnyWarps][16][NT * 8 + 1];
     asm volatile("griddepcontrol.launch_dependents;\n" ::);
     const int r0 = blockIdx.x * (SWIGLU ? 8 : 16);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, c = lane & 3, rq = lane >> 2;
     // first rows of the tile's halves in w (SWIGLU: r0 counts outputs, and N % 8 == 0)
-    const size_t lo_row = !SWIGLU ? min(r0 + rq, N - 1) : (interleaved ? 2 * r0 + rq : r0 + rq);
-    const size_t hi_row = !SWIGLU ? min(r0 + rq + 8, N - 1) : (interleaved ? lo_row + 8 : lo_row + N);
+    const size_t lo_row = !SWIGLU ? min(r0 + rq, N - 1) : 2 * r0 + rq;
+    const size_t hi_row = !SWIGLU ? min(r0 + rq + 8, N - 1) : lo_row + 8;
     const bf16* w_lo = w + lo_row * K;
     const bf16* w_hi = w + hi_row * K;
     const bf16* xr[NT];
@@ -165,8 +163,7 @@ skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, TOut* y, int M, in
 }
 
 template <int NT, typename TOut, bool SWIGLU>
-static int launch_skinny(const void* x, const void* w, void* y, int M, int N, int K, int interleaved,
-                         cudaStream_t stream) {
+static int launch_skinny(const void* x, const void* w, void* y, int M, int N, int K, cudaStream_t stream) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(SWIGLU ? (N + 7) / 8 : (N + 15) / 16);
     cfg.blockDim = dim3(kSkinnyWarps * 32);
@@ -178,7 +175,7 @@ static int launch_skinny(const void* x, const void* w, void* y, int M, int N, in
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<NT, TOut, SWIGLU>, (const bf16*)x, (const bf16*)w,
-                                       (TOut*)y, M, N, K, interleaved);
+                                       (TOut*)y, M, N, K);
     if (e != cudaSuccess) {
         set_error("gemm_skinny: %s", cudaGetErrorString(e));
         return (int)e;
@@ -202,18 +199,18 @@ extern "C" int tllm_gemm_skinny(const void* x, const void* w, void* y, int out_d
     TLLM_REQUIRE(out_dtype == kBF16 || out_dtype == kF32, "gemm_skinny: unknown output dtype");
     if (M == 0) return 0;
     if (out_dtype == kBF16) {
-        if (M <= 8) return launch_skinny<1, bf16, false>(x, w, y, M, N, K, 0, stream);
-        if (M <= 16) return launch_skinny<2, bf16, false>(x, w, y, M, N, K, 0, stream);
-        return launch_skinny<4, bf16, false>(x, w, y, M, N, K, 0, stream);
+        if (M <= 8) return launch_skinny<1, bf16, false>(x, w, y, M, N, K, stream);
+        if (M <= 16) return launch_skinny<2, bf16, false>(x, w, y, M, N, K, stream);
+        return launch_skinny<4, bf16, false>(x, w, y, M, N, K, stream);
     }
-    if (M <= 8) return launch_skinny<1, float, false>(x, w, y, M, N, K, 0, stream);
-    if (M <= 16) return launch_skinny<2, float, false>(x, w, y, M, N, K, 0, stream);
-    return launch_skinny<4, float, false>(x, w, y, M, N, K, 0, stream);
+    if (M <= 8) return launch_skinny<1, float, false>(x, w, y, M, N, K, stream);
+    if (M <= 16) return launch_skinny<2, float, false>(x, w, y, M, N, K, stream);
+    return launch_skinny<4, float, false>(x, w, y, M, N, K, stream);
 }
 
-// y[M, N] = silu(x . gate^T) * (x . up^T) for w of 2 N rows, stacked [gate; up] or interleaved by
-// eight (eight gate rows, their eight up rows, ...), bfloat16 out, M <= 16.
-extern "C" int tllm_gemm_skinny_swiglu(const void* x, const void* w, void* y, int M, int N, int K, int interleaved,
+// y[M, N] = silu(x . gate^T) * (x . up^T) for w of 2 N rows, gate and up interleaved by eight
+// (eight gate rows, their eight up rows, ...), bfloat16 out, M <= 16.
+extern "C" int tllm_gemm_skinny_swiglu(const void* x, const void* w, void* y, int M, int N, int K,
                                        cudaStream_t stream) {
     TLLM_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_skinny_swiglu: bad sizes");
     TLLM_REQUIRE(M <= 16, "gemm_skinny_swiglu: %d rows exceed 16", M);
@@ -222,6 +219,6 @@ extern "C" int tllm_gemm_skinny_swiglu(const void* x, const void* w, void* y, in
     TLLM_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15u) == 0,
                  "gemm_skinny_swiglu: operands must be 16-byte aligned");
     if (M == 0) return 0;
-    if (M <= 8) return launch_skinny<1, bf16, true>(x, w, y, M, N, K, interleaved, stream);
-    return launch_skinny<2, bf16, true>(x, w, y, M, N, K, interleaved, stream);
+    if (M <= 8) return launch_skinny<1, bf16, true>(x, w, y, M, N, K, stream);
+    return launch_skinny<2, bf16, true>(x, w, y, M, N, K, stream);
 }

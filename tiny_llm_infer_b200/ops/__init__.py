@@ -3,12 +3,10 @@ product.  Every function here works on CUDA tensors on the current stream and ha
 other implementation: if the kernel library cannot be built or loaded, the first call
 raises ``KernelLibraryError``.
 
-The matrix product (``linear``, ``linear_swiglu``) has three kernels of this package for
+The matrix product (``linear``, ``linear_swiglu``) has two kernels of this package for
 bfloat16, chosen by the number of rows: up to 8 the weight-streaming mma.sync product
 (``gemm_skinny``), from 256 on, where the tiles fill the GPU, the TMA + tcgen05 product
-(``gemm_tcgen05``); a weight-streaming tcgen05 product for 9 to 128 rows (``gemm_stream_tc``) is
-there and tested but equals the library at best, so ``STREAM_TC_MAX_ROWS`` keeps it off.
-Everything else is the library's (cuBLAS through ``torch.mm``), as in the reference, which calls
+(``gemm_tcgen05``).  Everything else is the library's (cuBLAS through ``torch.mm``), as in the reference, which calls
 ``cublasHgemm`` for every projection with more than one row
 (kernels/src/matmul_kernel_cuda.cu:83-91); in float32 mode it runs with the
 reduced-precision matrix modes switched off.
@@ -16,7 +14,6 @@ reduced-precision matrix modes switched off.
 from __future__ import annotations
 
 import ctypes
-import os
 from typing import Optional
 
 import torch
@@ -77,8 +74,7 @@ def _declare(h) -> None:
         "tllm_sample_split": [vp, i32, i32, i64, vp, vp, vp, vp, i32, vp, vp],
         "tllm_gemm_skinny": [vp, vp, vp, i32, i32, i32, i32, vp],
         "tllm_gemm_tcgen05": [vp, vp, vp, i32, i32, i32, i32, vp, vp],
-        "tllm_gemm_skinny_swiglu": [vp, vp, vp, i32, i32, i32, i32, vp],
-        "tllm_gemm_stream_tc": [vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp],
+        "tllm_gemm_skinny_swiglu": [vp, vp, vp, i32, i32, i32, vp],
         "tllm_paged_attention_decode": [vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32,
                                         i32, vp, vp, vp, vp],
         "tllm_paged_attention_prefill": [vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32, vp, vp],
@@ -256,23 +252,15 @@ def fast_attention_ok(dtype, page_size: int, q_heads: int, kv_heads: int, head_d
 
 
 def paged_attention_decode(q, cache, positions, token_slot, rows, n_rows, block_table, page_size,
-                           q_heads, kv_heads, head_dim, window, scale, out, max_context, splits=None,
-                           cluster=False):
+                           q_heads, kv_heads, head_dim, window, scale, out, max_context, splits=None):
     """Attention of one-token rows (``rows``: their indices, None for all), keys split over
     ``splits`` blocks per (row, key/value head); the splits' partial results go through scratch
-    in global memory to a second small kernel.  ``cluster=True`` (up to 16 splits): the blocks
-    of a (row, key/value head) run as one thread-block cluster and combine through
-    distributed shared memory instead, with no scratch and no second kernel.  Measured at
-    Qwen3-8B sizes, context 4096: alone the cluster form is the faster one (26.0 against 27.8 µs
-    per layer at 8 rows, 11.1 against 11.5 at one row; 169 against 164 at 64 rows), inside a
-    decode step the slower one (4.21 against 4.17 ms at 8 rows: the short combine kernel hides
-    the start of the product that follows), so the engine does not ask for it."""
+    in global memory to a second small kernel that combines them in the order of the splits."""
     _cuda(q, cache, positions, token_slot, rows, block_table, out)
     if splits is None:
         splits = decode_splits(n_rows, kv_heads, max_context)
     part_o = part_ml = None
-    scratch = splits > 1 and not (cluster and splits <= 16)
-    if scratch:
+    if splits > 1:
         n = n_rows * q_heads * splits
         ws = workspace(q.device, n * (head_dim + 2))
         part_o, part_ml = ws[:n * head_dim], ws[n * head_dim:n * (head_dim + 2)]
@@ -280,7 +268,7 @@ def paged_attention_decode(q, cache, positions, token_slot, rows, n_rows, block_
         _p(q), _p(cache), _p(positions), _p(token_slot), _p(rows), n_rows, _p(block_table),
         block_table.shape[1], page_size, q_heads, kv_heads, head_dim, int(window or 0), float(scale),
         splits, _p(part_o), _p(part_ml), _p(out), _stream()), "paged_attention_decode",
-        kernels=2 if scratch else 1)
+        kernels=2 if splits > 1 else 1)
     return out
 
 
@@ -412,14 +400,6 @@ def uniform_of(seed: int, token: int) -> float:
     return float(lib().tllm_uniform_of(seed & 0xFFFFFFFFFFFFFFFF, token))
 
 
-# Rows up to which gate/up product and SwiGLU are one weight-streaming kernel when the weight is
-# stacked [gate; up].  0: not used.  Measured at Qwen3-8B sizes, 8 rows: a block then streams eight
-# gate rows and the eight up rows that belong to them, 96 MB apart, and takes 43.0 µs where the
-# product of all 2 N rows (sixteen neighbouring rows per block) takes 35.1 µs and the SwiGLU kernel
-# 2.1 µs more; a decode step takes 4.45 ms with it and 4.16 ms without.  With gate and up rows
-# interleaved by eight (what the feed-forward part stores) the patterns are the same and the
-# fused kernel is used up to SKINNY_MAX_ROWS.
-SKINNY_SWIGLU_MAX_ROWS = 0
 SKINNY_MAX_ROWS = 8       # up to this many rows the weight-streaming product beats the library
 
 
@@ -490,56 +470,6 @@ def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, swiglu: bool = False, sh
     return y
 
 
-# Above SKINNY_MAX_ROWS and up to this many rows ``linear`` takes the weight-streaming tcgen05
-# product (the kernel takes up to 128).  0: never, the library's product runs instead; that is the
-# setting, because the kernel equals the library where it is best and loses elsewhere.  Measured
-# per layer (q/k/v, o, gate-up + SwiGLU, down) with weights that do not stay in L2, at Qwen3-8B
-# sizes: 16 rows 13.0 + 12.9 + 39.1 + 20.5 against the library's 18.0 + 17.0 + 43 + 23.8 µs, 64 rows
-# 15.0 + 12.0 + 42.3 + 22.5 against 17.6 + 13.2 + 45 + 24.5, 128 rows 17.8 + 14.9 + 47.3 + 26.5 against
-# 14.5 + 12.5 + 46 + 25.5; but inside a decode step the two are level (batch 16: 5.42 against 5.47 ms,
-# batch 64: 9.92 against 9.86 ms), at Qwen3-0.6B sizes a step of 64 rows takes 2.19 ms with it and
-# 2.11 without (the head, 151936 x 1024: 74 against 60 µs), and at Qwen3-32B sizes with 64 rows it
-# trails (q/k/v 24.8 against 21.8 µs, o 20.7 against 19.6, down 52.3 against 52.0).
-STREAM_TC_MAX_ROWS = int(os.environ.get("TLLM_STREAM_TC_ROWS", "0"))     # the variable: for measurements
-
-
-def stream_tc_splits(out_rows: int, k: int) -> int:
-    """Blocks (1, 2, 4 or 8, one cluster) that share the K of a tile of 128 weight rows in
-    ``gemm_stream_tc``: the most that still run all at once (clusters do not pack the last
-    slots of the GPU, so 260 of its 296 count), each with four stages of 64 or more.  Measured
-    at Qwen3-8B sizes, 64 rows: q/k/v (48 tiles) 27.6, 18.2, 15.0, 20.7 µs for 1, 2, 4, 8 blocks,
-    o (32 tiles) 27.2, 17.7, 12.8, 12.0, gate-up (192 tiles) 42.3, 46.1, 48.0, 62.0."""
-    tiles = -(-out_rows // 128)
-    splits = 1
-    while splits < 8 and tiles * splits * 2 <= 260 and -(-k // 64) // (splits * 2) >= 4:
-        splits *= 2
-    return splits
-
-
-def gemm_stream_tc(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
-                   swiglu: bool = False, splits: Optional[int] = None) -> torch.Tensor:
-    """y = x . weight^T for up to 128 bfloat16 rows on tcgen05 with the roles swapped (128 weight
-    rows fill the tensor core's rows, the rows of x its columns; csrc/gemm_stream_tc.cu): the
-    weights stream once from HBM, ``splits`` blocks of a cluster share a tile's K and add their
-    partial sums through distributed shared memory.  ``swiglu``: gate and up rows interleaved by
-    eight, the result is silu(x . gate^T) * (x . up^T)."""
-    _cuda(x, weight)
-    rows, k = x.shape
-    n = weight.shape[0]
-    assert weight.shape[1] == k and x.dtype == weight.dtype == torch.bfloat16
-    y = torch.empty((rows, n // 2 if swiglu else n), dtype=out_dtype, device=x.device)
-    if rows == 0:
-        return y
-    if splits is None:
-        splits = stream_tc_splits(n, k)
-    global tcgen05_calls
-    tcgen05_calls += 1
-    _check(lib().tllm_gemm_stream_tc(_p(x), _p(weight), _p(y), rows, n, k, int(swiglu),
-                                     int(out_dtype == torch.float32), splits, _p(error_word(x.device)), _stream()),
-           "gemm_stream_tc")
-    return y
-
-
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """y[T, N] = x[T, K] . weight[N, K]^T with float32 accumulation.  A weight kept in
     float32 is multiplied in float32 whatever the activations are stored in."""
@@ -557,9 +487,6 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     if weight.dtype == torch.bfloat16 and 0 < rows <= SKINNY_MAX_ROWS and k % 8 == 0 \
             and x.is_contiguous() and weight.is_contiguous() and want in _DT:
         return gemm_skinny(x, weight, want)
-    if weight.dtype == torch.bfloat16 and SKINNY_MAX_ROWS < rows <= STREAM_TC_MAX_ROWS and k % 8 == 0 \
-            and x.is_contiguous() and weight.is_contiguous() and want in _DT:
-        return gemm_stream_tc(x, weight, want)
     if want == torch.bfloat16 and tcgen05_pays(rows, weight.shape[0], k, weight.dtype) \
             and x.is_contiguous() and weight.is_contiguous():
         return gemm_tcgen05(x, weight)
@@ -568,14 +495,14 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     return torch.mm(x, weight.t(), out_dtype=want)
 
 
-def gemm_skinny_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, interleaved: bool = False) -> torch.Tensor:
-    """silu(x . Wg^T) * (x . Wu^T) for at most 16 bfloat16 rows as one weight-streaming kernel."""
+def gemm_skinny_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(x . Wg^T) * (x . Wu^T) for at most 16 bfloat16 rows as one weight-streaming kernel;
+    ``w_gate_up`` holds the rows of Wg and Wu interleaved by eight (``interleave_gate_up``)."""
     _cuda(x, w_gate_up)
     rows, k = x.shape
     inter = w_gate_up.shape[0] // 2
     act = torch.empty((rows, inter), dtype=torch.bfloat16, device=x.device)
-    _check(lib().tllm_gemm_skinny_swiglu(_p(x), _p(w_gate_up), _p(act), rows, inter, k, int(interleaved),
-                                         _stream()), "gemm_skinny_swiglu")
+    _check(lib().tllm_gemm_skinny_swiglu(_p(x), _p(w_gate_up), _p(act), rows, inter, k, _stream()), "gemm_skinny_swiglu")
     return act
 
 
@@ -591,10 +518,8 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out_dtype: torch.dty
         and w_gate_up.is_contiguous()
     if plain and tcgen05_pays(rows, inter, k, w_gate_up.dtype, col_tile=128):
         return gemm_tcgen05(x, w_gate_up, swiglu=True, interleaved=interleaved)
-    if plain and 0 < rows <= (SKINNY_MAX_ROWS if interleaved else SKINNY_SWIGLU_MAX_ROWS) and k % 8 == 0:
-        return gemm_skinny_swiglu(x, w_gate_up, interleaved)
-    if plain and interleaved and SKINNY_MAX_ROWS < rows <= STREAM_TC_MAX_ROWS and k % 8 == 0:
-        return gemm_stream_tc(x, w_gate_up, torch.bfloat16, swiglu=True)
+    if plain and interleaved and 0 < rows <= SKINNY_MAX_ROWS and k % 8 == 0:
+        return gemm_skinny_swiglu(x, w_gate_up)
     gate_up = linear(x, w_gate_up, out_dtype=out_dtype)
     act = torch.empty((rows, inter), dtype=out_dtype, device=x.device)
     return swiglu(gate_up, act, interleaved)
