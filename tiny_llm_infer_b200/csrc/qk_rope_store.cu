@@ -93,156 +93,153 @@ __global__ void qk_norm_rope_store_kernel(
 
 // Vector form for head widths 64, 128 and 256 with the whole head rotated: one block per
 // token.  The block first writes the token's cosines and sines to shared memory (once, not
-// once per head), then its warps take the heads in turn.  A lane holds VEC = head_dim / 32
-// neighbouring elements (one 4-, 8- or 16-byte access); the rotation partner of an element
-// is VEC * 16 elements away, that is, in lane ^ 16.
-template <typename T, int VEC> struct VecIO;
-template <int VEC> struct VecIO<bf16, VEC> {
-    // what a load leaves in registers until it is needed: half the registers of the float form
-    struct Raw { uint32_t w[VEC / 2]; };
-    static __device__ __forceinline__ Raw load_raw(const bf16* p) {
-        Raw raw;
-        if constexpr (VEC == 2) {
-            raw.w[0] = *reinterpret_cast<const uint32_t*>(p);
-        } else if constexpr (VEC == 4) {
-            const uint2 u = *reinterpret_cast<const uint2*>(p);
-            raw.w[0] = u.x; raw.w[1] = u.y;
-        } else {
-            const uint4 u = *reinterpret_cast<const uint4*>(p);
-            raw.w[0] = u.x; raw.w[1] = u.y; raw.w[2] = u.z; raw.w[3] = u.w;
-        }
-        return raw;
-    }
-    static __device__ __forceinline__ void unpack(const Raw& raw, float (&v)[VEC]) {
+// once per head), then its warps take the heads in turn.  A lane holds eight neighbouring
+// elements of a head (one 16-byte access in bfloat16), so a head is HD / 8 lanes and a warp
+// works on 32 / (HD / 8) heads at once; the rotation partner of an element is HD / 2 elements
+// away, that is, HD / 16 lanes.  With many tokens the kernel is bound by the instructions it
+// issues, not by memory (one head per warp and four elements per lane: 158 warp instructions
+// per head, 2 TB/s at 2048 tokens of Qwen3-8B sizes), hence the wide lanes, the cosines and signed
+// sines kept in registers for all heads of the token, and the three rounds of heads loaded before
+// the first is worked on.
+template <typename T> struct Vec8;
+template <> struct Vec8<bf16> {
+    struct Raw { uint4 u; };
+    static __device__ __forceinline__ Raw load_raw(const bf16* p) { return Raw{*reinterpret_cast<const uint4*>(p)}; }
+    static __device__ __forceinline__ void unpack(const Raw& raw, float (&v)[8]) {
+        const uint32_t w[4] = {raw.u.x, raw.u.y, raw.u.z, raw.u.w};
 #pragma unroll
-        for (int i = 0; i < VEC / 2; ++i) {
-            v[2 * i] = __uint_as_float(raw.w[i] << 16);
-            v[2 * i + 1] = __uint_as_float(raw.w[i] & 0xffff0000u);
+        for (int i = 0; i < 4; ++i) {
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
         }
     }
-    static __device__ __forceinline__ void load(const bf16* p, float (&v)[VEC]) { unpack(load_raw(p), v); }
-    static __device__ __forceinline__ void store(bf16* p, const float (&v)[VEC]) {
-        if constexpr (VEC == 2) {
-            *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v[0], v[1]);
-        } else if constexpr (VEC == 4) {
-            uint2 raw;
-            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
-            h[0] = __floats2bfloat162_rn(v[0], v[1]);
-            h[1] = __floats2bfloat162_rn(v[2], v[3]);
-            *reinterpret_cast<uint2*>(p) = raw;
-        } else {
-            uint4 raw;
-            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+    static __device__ __forceinline__ void store(bf16* p, const float (&v)[8]) {
+        uint4 raw;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-            *reinterpret_cast<uint4*>(p) = raw;
-        }
+        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        *reinterpret_cast<uint4*>(p) = raw;
     }
+    static __device__ __forceinline__ float inv_root(float x) { return rsqrtf(x); }
 };
-template <int VEC> struct VecIO<float, VEC> {
-    struct Raw { float v[VEC]; };
+template <> struct Vec8<float> {
+    struct Raw { float4 a, b; };
     static __device__ __forceinline__ Raw load_raw(const float* p) {
-        Raw raw;
-#pragma unroll
-        for (int i = 0; i < VEC; i += 2) {
-            const float2 f = *reinterpret_cast<const float2*>(p + i);
-            raw.v[i] = f.x; raw.v[i + 1] = f.y;
-        }
-        return raw;
+        return Raw{*reinterpret_cast<const float4*>(p), *reinterpret_cast<const float4*>(p + 4)};
     }
-    static __device__ __forceinline__ void unpack(const Raw& raw, float (&v)[VEC]) {
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) v[i] = raw.v[i];
+    static __device__ __forceinline__ void unpack(const Raw& raw, float (&v)[8]) {
+        v[0] = raw.a.x; v[1] = raw.a.y; v[2] = raw.a.z; v[3] = raw.a.w;
+        v[4] = raw.b.x; v[5] = raw.b.y; v[6] = raw.b.z; v[7] = raw.b.w;
     }
-    static __device__ __forceinline__ void load(const float* p, float (&v)[VEC]) { unpack(load_raw(p), v); }
-    static __device__ __forceinline__ void store(float* p, const float (&v)[VEC]) {
-#pragma unroll
-        for (int i = 0; i < VEC; i += 2) *reinterpret_cast<float2*>(p + i) = make_float2(v[i], v[i + 1]);
+    static __device__ __forceinline__ void store(float* p, const float (&v)[8]) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
     }
+    static __device__ __forceinline__ float inv_root(float x) { return 1.0f / sqrtf(x); }   // the 32-bit path: exact root and quotient
 };
 
-template <typename T, typename TG, int VEC>
-__global__ void __launch_bounds__(256, (VEC <= 4 && sizeof(T) == 2) ? 4 : 2) qk_norm_rope_store_vec_kernel(
+template <typename T, typename TG, int HD>
+__global__ void __launch_bounds__(256) qk_norm_rope_store_vec_kernel(
     T* qkv, const TG* __restrict__ q_gain, const TG* __restrict__ k_gain, float eps,
     const float* __restrict__ inv_freq, const int* __restrict__ positions,
     const int* __restrict__ token_slot, const int* __restrict__ block_table, int max_pages,
     T* __restrict__ cache, int page_size, T* __restrict__ q_out, int q_heads, int kv_heads, int flags) {
-    constexpr int HD = VEC * 32, HALF = HD / 2;
-    __shared__ float cs[HALF], sn[HALF];
+    constexpr int HALF = HD / 2, LPH = HD / 8, HPW = 32 / LPH;   // lanes per head, heads per warp
+    __shared__ __align__(16) float cs[HALF], sn[HALF];
     TLLM_PDL_ENTER();
     const int t = blockIdx.x;
     const int slot = token_slot[t];
     if (slot < 0) return;
     const int pos = positions[t];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-    const bool rope = (flags & kFlagRope) != 0;
+    const int sub = lane / LPH, l = lane % LPH;
+    const bool rope = (flags & kFlagRope) != 0, norm = (flags & kFlagNorm) != 0;
     const int heads_total = q_heads + 2 * kv_heads;
-    const int e0 = lane * VEC;
+    const int e0 = l * 8;
     T* row = qkv + (size_t)t * heads_total * HD;
     // With few tokens the heads of a token are spread over gridDim.y blocks (one round per warp);
-    // with many a warp takes several heads, and loads kRounds of them before it works on the
-    // first, so that their latencies overlap.  The first loads are issued before the angles are
-    // computed (sincosf of a large argument is slow) and before the page is looked up.
-    constexpr int kRounds = 6;
-    const int stride = warps * gridDim.y;
-    typename VecIO<T, VEC>::Raw xs[kRounds];
+    // with many a warp takes several rounds of heads, and loads kRounds of them before it works on
+    // the first, so that their latencies overlap.  The first loads are issued before the angles
+    // are computed and before the page is looked up.
+    constexpr int kRounds = 3;
+    const int stride = warps * HPW * gridDim.y;
+    const int head0 = (blockIdx.y * warps + warp) * HPW + sub;
+    typename Vec8<T>::Raw xs[kRounds];
     auto load_heads = [&](int first) {
 #pragma unroll
         for (int r = 0; r < kRounds; ++r) {
             const int head = first + r * stride;
-            if (head < heads_total) xs[r] = VecIO<T, VEC>::load_raw(row + (size_t)head * HD + e0);
+            if (head < heads_total) xs[r] = Vec8<T>::load_raw(row + (size_t)head * HD + e0);
         }
     };
-    load_heads(blockIdx.y * warps + warp);
+    load_heads(head0);
     if (rope)
         for (int i = threadIdx.x; i < HALF; i += blockDim.x) sincosf((float)pos * inv_freq[i], &sn[i], &cs[i]);
-    float gq[VEC], gk[VEC];
-    if (flags & kFlagNorm) {
+    float gq[8], gk[8];
+    if (norm) {
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) { gq[i] = to_f32<TG>(q_gain[e0 + i]); gk[i] = to_f32<TG>(k_gain[e0 + i]); }
+        for (int i = 0; i < 8; ++i) { gq[i] = to_f32<TG>(q_gain[e0 + i]); gk[i] = to_f32<TG>(k_gain[e0 + i]); }
     }
     int page = -1;
     if (flags & kFlagStore) page = block_table[(size_t)slot * max_pages + pos / page_size];
     __syncthreads();
-    for (int first = blockIdx.y * warps + warp; first < heads_total; first += stride * kRounds) {
-        if (first != blockIdx.y * warps + warp) load_heads(first);
+    // pair (i, i + HALF): x'_i = x_i cos a - x_{i+HALF} sin a; x'_{i+HALF} = x_i sin a + x_{i+HALF} cos a,
+    // for both halves x' = x cos a + partner * (-+ sin a): cosines and signed sines of this lane's elements
+    const bool low = l < LPH / 2;
+    float cc[8], sx[8];
+    if (rope) {
+        const int f0 = low ? e0 : e0 - HALF;
+        const float4 c0 = *reinterpret_cast<const float4*>(cs + f0), c1 = *reinterpret_cast<const float4*>(cs + f0 + 4);
+        const float4 s0 = *reinterpret_cast<const float4*>(sn + f0), s1 = *reinterpret_cast<const float4*>(sn + f0 + 4);
+        cc[0] = c0.x; cc[1] = c0.y; cc[2] = c0.z; cc[3] = c0.w; cc[4] = c1.x; cc[5] = c1.y; cc[6] = c1.z; cc[7] = c1.w;
+        sx[0] = s0.x; sx[1] = s0.y; sx[2] = s0.z; sx[3] = s0.w; sx[4] = s1.x; sx[5] = s1.y; sx[6] = s1.z; sx[7] = s1.w;
+        if (low) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sx[i] = -sx[i];
+        }
+    }
+    for (int first = head0; first < heads_total; first += stride * kRounds) {
+        if (first != head0) load_heads(first);
 #pragma unroll
         for (int r = 0; r < kRounds; ++r) {
             const int head = first + r * stride;
-            if (head >= heads_total) break;
-            float x[VEC];
-            VecIO<T, VEC>::unpack(xs[r], x);
+            // heads of one warp differ by less than HPW: whether a head exists may differ inside the
+            // warp, so lanes without one keep going (with a copy of a head that exists) for the shuffles
+            const bool live = head < heads_total;
+            if (__all_sync(0xffffffffu, !live)) break;
+            float x[8];
+            Vec8<T>::unpack(xs[r], x);
             const bool is_q = head < q_heads, is_k = !is_q && head < q_heads + kv_heads;
-            T* src = row + (size_t)head * HD + e0;
-            if ((is_q || is_k) && (flags & kFlagNorm)) {
+            if (norm) {
                 float ss = 0.0f;
 #pragma unroll
-                for (int i = 0; i < VEC; ++i) ss += x[i] * x[i];
-                ss = warp_sum(ss);
-                const float scale = 1.0f / sqrtf(ss / (float)HD + eps);
+                for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
 #pragma unroll
-                for (int i = 0; i < VEC; ++i) x[i] = (is_q ? gq[i] : gk[i]) * x[i] * scale;
-            }
-            if ((is_q || is_k) && rope) {
-                const bool low = lane < 16;
-                const int f0 = low ? e0 : e0 - HALF;
+                for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                if (is_q || is_k) {
+                    const float scale = Vec8<T>::inv_root(ss / (float)HD + eps);
 #pragma unroll
-                for (int i = 0; i < VEC; ++i) {
-                    const float other = __shfl_xor_sync(0xffffffffu, x[i], 16);
-                    const float c = cs[f0 + i], s = sn[f0 + i];
-                    x[i] = low ? x[i] * c - other * s : other * s + x[i] * c;
+                    for (int i = 0; i < 8; ++i) x[i] = (is_q ? gq[i] : gk[i]) * x[i] * scale;
                 }
             }
+            if (rope) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float other = __shfl_xor_sync(0xffffffffu, x[i], LPH / 2);
+                    if (is_q || is_k) x[i] = fmaf(x[i], cc[i], other * sx[i]);
+                }
+            }
+            if (!live) continue;
             if (is_q) {
-                if (flags & kFlagQOut) VecIO<T, VEC>::store(q_out + ((size_t)t * q_heads + head) * HD + e0, x);
+                if (flags & kFlagQOut) Vec8<T>::store(q_out + ((size_t)t * q_heads + head) * HD + e0, x);
             } else {
                 if ((flags & kFlagStore) && page >= 0) {
                     const int kvh = is_k ? head - q_heads : head - q_heads - kv_heads;
                     T* dst = cache + ((((size_t)page * 2 + (is_k ? 0 : 1)) * kv_heads + kvh) * page_size +
                                       (pos % page_size)) * HD + e0;
-                    VecIO<T, VEC>::store(dst, x);
+                    Vec8<T>::store(dst, x);
                 }
-                if (flags & kFlagKvOut) VecIO<T, VEC>::store(src, x);
+                if (flags & kFlagKvOut) Vec8<T>::store(row + (size_t)head * HD + e0, x);
             }
         }
     }
@@ -273,19 +270,20 @@ extern "C" int tllm_qk_norm_rope_store(
     const bool whole_rotation = !(flags & kFlagRope) || rotary_dim == head_dim;
     const auto al = [](const void* p, int bytes) { return (reinterpret_cast<uintptr_t>(p) & (bytes - 1)) == 0; };
     if (whole_rotation && (head_dim == 64 || head_dim == 128 || head_dim == 256)) {
-        const int need = dtype == kBF16 ? (head_dim / 32) * 2 : 8;     // widest access of the vector form
+        const int need = 16;                                           // widest access of the vector form
         if (al(qkv, need) && al(cache, need) && al(q_out, need) && (dtype == kBF16 || dtype == kF32)) {
             const int vblock = 256;
-            const int vgroups = tokens <= 64 ? (q_heads + 2 * kv_heads + 7) / 8 : 1;
-#define VLAUNCH(T, TG, VEC)                                                                         \
-    launch_pdl(kPdlQk, qk_norm_rope_store_vec_kernel<T, TG, VEC>, dim3(tokens, vgroups), dim3(vblock), 0, stream, \
+            const int per_block = 8 * (32 / (head_dim / 8));           // heads a block takes in one round
+            const int vgroups = tokens <= 64 ? (q_heads + 2 * kv_heads + per_block - 1) / per_block : 1;
+#define VLAUNCH(T, TG, HD)                                                                          \
+    launch_pdl(kPdlQk, qk_norm_rope_store_vec_kernel<T, TG, HD>, dim3(tokens, vgroups), dim3(vblock), 0, stream, \
         (T*)qkv, (const TG*)q_gain, (const TG*)k_gain, eps, inv_freq, positions, token_slot,        \
         block_table, max_pages, (T*)cache, page_size, (T*)q_out, q_heads, kv_heads, flags)
 #define VDISPATCH(T, TG)                                              \
     do {                                                              \
-        if (head_dim == 64) VLAUNCH(T, TG, 2);                        \
-        else if (head_dim == 128) VLAUNCH(T, TG, 4);                  \
-        else VLAUNCH(T, TG, 8);                                       \
+        if (head_dim == 64) VLAUNCH(T, TG, 64);                       \
+        else if (head_dim == 128) VLAUNCH(T, TG, 128);                \
+        else VLAUNCH(T, TG, 256);                                     \
     } while (0)
             if (dtype == kBF16) {
                 if (gain_dtype == kBF16) VDISPATCH(bf16, bf16); else VDISPATCH(bf16, float);
