@@ -551,6 +551,49 @@ def test_fast_attention_refuses_other_shapes(ops):
     assert not ops.fast_attention_ok(torch.float32, 16, 4, 2, 64)
 
 
+@pytest.mark.parametrize("xd,wd,yd", [(torch.float32, torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16, torch.float32),
+                                      (torch.bfloat16, torch.bfloat16, torch.bfloat16), (torch.float32, torch.bfloat16, torch.float32)])
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (3, 77, 131), (33, 200, 1000)])
+def test_gemm_plain_against_float64(ops, xd, wd, yd, M, N, K):
+    """The plain product (one thread per output, float32 sum in order) against a float64 product."""
+    x, w = rnd(M, K, seed=700).to(xd), rnd(N, K, seed=701, scale=0.2).to(wd)
+    y = ops.gemm_plain(dev(x), dev(w), yd)
+    ref = x.double() @ w.double().T
+    assert y.dtype == yd and y.shape == (M, N)
+    assert (y.cpu().double() - ref).abs().max() < (1e-5 if yd == torch.float32 else 1.6e-2) * max(ref.abs().max().item(), 1.0)
+
+
+@pytest.mark.parametrize("what,M,N,K", [("skinny", 8, 6144, 4096), ("skinny", 5, 4096, 12288), ("skinny_head", 3, 151936, 1024),
+                                        ("tcgen05", 2048, 4096, 12288), ("tcgen05_swiglu", 2048, 24576, 4096),
+                                        ("library", 64, 6144, 4096), ("library_f32", 40, 5120, 5120)])
+def test_fast_products_against_their_plain_twin_at_real_shapes(ops, what, M, N, K):
+    """Every product the engine can take, at shapes of Qwen3-8B / 0.6B / 32B layers, against the plain
+    kernel of this package on the same operands (a float64 product of these sizes on the host takes
+    too long): through ``ops.linear`` / ``ops.linear_swiglu``, which must choose the kernel named."""
+    f32 = what == "library_f32"
+    dt = torch.float32 if f32 else torch.bfloat16
+    g = torch.Generator(device="cuda").manual_seed(11)
+    x = (torch.randn(M, K, device="cuda", generator=g) * 0.5).to(dt)
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.02).to(dt)
+    w[N // 2 + 3] *= 7.0                                   # one row that stands out
+    w[N - 1] *= 5.0
+    before = ops.tcgen05_calls
+    if what == "tcgen05_swiglu":
+        inter = N // 2
+        got = ops.linear_swiglu(x, ops.interleave_gate_up(w[:inter], w[inter:]).contiguous(), torch.bfloat16, interleaved=True)
+        full = ops.gemm_plain(x, w, torch.float32)
+        ref = torch.nn.functional.silu(full[:, :inter]) * full[:, inter:]
+    else:
+        got = ops.linear(x, w, out_dtype=torch.float32 if what in ("skinny_head", "library_f32") else None)
+        ref = ops.gemm_plain(x, w, torch.float32)
+    assert (ops.tcgen05_calls > before) == what.startswith("tcgen05")
+    ops.check_error_word("cuda:0")
+    scale = ref.abs().max().item()
+    assert scale > 1.0
+    err = (got.float() - ref).abs().max().item()
+    assert err < (1e-5 if f32 else 1.6e-2 if got.dtype == torch.bfloat16 else 2e-3) * scale, (err, scale)
+
+
 @pytest.mark.parametrize("M", [1, 2, 7, 8, 9, 16, 17, 32])
 @pytest.mark.parametrize("N,K", [(200, 96), (1000, 1000), (77, 4104), (4096, 264)])
 def test_gemm_skinny(ops, M, N, K):

@@ -101,8 +101,8 @@ __global__ void qk_norm_rope_store_kernel(
 // per head, 2 TB/s at 2048 tokens of Qwen3-8B sizes), hence the wide lanes, the cosines and signed
 // sines kept in registers for all heads of the token, and the three rounds of heads loaded before
 // the first is worked on.
-template <typename T> struct Vec8;
-template <> struct Vec8<bf16> {
+template <typename T> struct HeadVec8;
+template <> struct HeadVec8<bf16> {
     struct Raw { uint4 u; };
     static __device__ __forceinline__ Raw load_raw(const bf16* p) { return Raw{*reinterpret_cast<const uint4*>(p)}; }
     static __device__ __forceinline__ void unpack(const Raw& raw, float (&v)[8]) {
@@ -122,7 +122,7 @@ template <> struct Vec8<bf16> {
     }
     static __device__ __forceinline__ float inv_root(float x) { return rsqrtf(x); }
 };
-template <> struct Vec8<float> {
+template <> struct HeadVec8<float> {
     struct Raw { float4 a, b; };
     static __device__ __forceinline__ Raw load_raw(const float* p) {
         return Raw{*reinterpret_cast<const float4*>(p), *reinterpret_cast<const float4*>(p + 4)};
@@ -164,12 +164,12 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_vec_kernel(
     constexpr int kRounds = 3;
     const int stride = warps * HPW * gridDim.y;
     const int head0 = (blockIdx.y * warps + warp) * HPW + sub;
-    typename Vec8<T>::Raw xs[kRounds];
+    typename HeadVec8<T>::Raw xs[kRounds];
     auto load_heads = [&](int first) {
 #pragma unroll
         for (int r = 0; r < kRounds; ++r) {
             const int head = first + r * stride;
-            if (head < heads_total) xs[r] = Vec8<T>::load_raw(row + (size_t)head * HD + e0);
+            if (head < heads_total) xs[r] = HeadVec8<T>::load_raw(row + (size_t)head * HD + e0);
         }
     };
     load_heads(head0);
@@ -208,7 +208,7 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_vec_kernel(
             const bool live = head < heads_total;
             if (__all_sync(0xffffffffu, !live)) break;
             float x[8];
-            Vec8<T>::unpack(xs[r], x);
+            HeadVec8<T>::unpack(xs[r], x);
             const bool is_q = head < q_heads, is_k = !is_q && head < q_heads + kv_heads;
             if (norm) {
                 float ss = 0.0f;
@@ -217,7 +217,7 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_vec_kernel(
 #pragma unroll
                 for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
                 if (is_q || is_k) {
-                    const float scale = Vec8<T>::inv_root(ss / (float)HD + eps);
+                    const float scale = HeadVec8<T>::inv_root(ss / (float)HD + eps);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) x[i] = (is_q ? gq[i] : gk[i]) * x[i] * scale;
                 }
@@ -231,15 +231,15 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_vec_kernel(
             }
             if (!live) continue;
             if (is_q) {
-                if (flags & kFlagQOut) Vec8<T>::store(q_out + ((size_t)t * q_heads + head) * HD + e0, x);
+                if (flags & kFlagQOut) HeadVec8<T>::store(q_out + ((size_t)t * q_heads + head) * HD + e0, x);
             } else {
                 if ((flags & kFlagStore) && page >= 0) {
                     const int kvh = is_k ? head - q_heads : head - q_heads - kv_heads;
                     T* dst = cache + ((((size_t)page * 2 + (is_k ? 0 : 1)) * kv_heads + kvh) * page_size +
                                       (pos % page_size)) * HD + e0;
-                    Vec8<T>::store(dst, x);
+                    HeadVec8<T>::store(dst, x);
                 }
-                if (flags & kFlagKvOut) Vec8<T>::store(row + (size_t)head * HD + e0, x);
+                if (flags & kFlagKvOut) HeadVec8<T>::store(row + (size_t)head * HD + e0, x);
             }
         }
     }

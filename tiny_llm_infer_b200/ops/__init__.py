@@ -73,6 +73,7 @@ def _declare(h) -> None:
         "tllm_sample": [vp, i32, i32, i64, vp, vp, vp, vp],
         "tllm_sample_split": [vp, i32, i32, i64, vp, vp, vp, vp, i32, vp, vp],
         "tllm_gemm_skinny": [vp, vp, vp, i32, i32, i32, i32, vp],
+        "tllm_gemm_plain": [vp, i32, vp, i32, vp, i32, i32, i32, i32, vp],
         "tllm_gemm_tcgen05": [vp, vp, vp, i32, i32, i32, i32, vp, vp],
         "tllm_gemm_skinny_swiglu": [vp, vp, vp, i32, i32, i32, vp],
         "tllm_paged_attention_decode": [vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32,
@@ -413,6 +414,19 @@ def gemm_skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -
     y = torch.empty((rows, n), dtype=out_dtype, device=x.device)
     _check(lib().tllm_gemm_skinny(_p(x), _p(weight), _p(y), _DT[out_dtype], rows, n, k, _stream()),
            "gemm_skinny")
+    return y
+
+
+def gemm_plain(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """y = x . weight^T by the plain kernel (csrc/gemm_plain.cu): one thread per output, the sum over
+    k in order in float32, any sizes, bfloat16 or float32 operands.  Slow; it is what the fast products
+    are checked against at sizes too large for the host."""
+    _cuda(x, weight)
+    rows, k = x.shape
+    n = weight.shape[0]
+    assert weight.shape[1] == k
+    y = torch.empty((rows, n), dtype=out_dtype, device=x.device)
+    _check(lib().tllm_gemm_plain(_p(x), _dt(x), _p(weight), _dt(weight), _p(y), _dt(y), rows, n, k, _stream()), "gemm_plain")
     return y
 
 
