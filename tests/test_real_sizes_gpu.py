@@ -128,6 +128,44 @@ def test_bfloat16_kernels_against_the_float32_path_at_real_sizes(name):
     assert worst <= BF16_TOL, worst
 
 
+def test_a_long_context_at_real_widths():
+    """One request of 20,000 tokens (two layers of the 0.6B sizes): the prompt in portions of 4096 and of
+    300 tokens (few query rows against many keys: the prompt kernel's key splits and their combine
+    step), then 16 tokens one by one (decode attention over 20,000 keys in some twenty splits), the
+    bfloat16 kernels against the float32 path at the last positions of every portion."""
+    sizes = {**SIZES["0.6b"], "num_hidden_layers": 2}
+    cfg = Qwen3Config(layer_types=("full_attention",) * 2, **sizes)
+    gen = torch.Generator().manual_seed(9)
+    toks = torch.randint(0, cfg.vocab_size, (20000,), generator=gen).tolist()
+    cuts = [4096, 4096, 300, 4096, 2, 4096, 3298] + [1] * 16
+    assert sum(cuts) == len(toks)
+    rows = {}
+    for dtype in (torch.float32, torch.bfloat16):
+        model = random_model(cfg, seed=13, dtype=dtype, device="cuda:0", std=0.02)
+        sharpen(model)
+        cache = CacheManager(model.cache_needs(), PAGE, 20000 // PAGE + 2, max_slots=1, max_seq_len=20032, dtype=dtype,
+                             device="cuda:0")
+        runner = ModelRunner(model, cache, max_batch_tokens=4096)
+        got, at = [], 0
+        for n in cuts:
+            want = sorted({max(0, n - 2), n - 1})
+            got += list(runner.step([selfcheck.StepEntry("long", toks[at:at + n], want)]).clone())
+            at += n
+        runner.check_kernels()
+        rows[dtype] = torch.stack(got)
+        del model, cache, runner
+        torch.cuda.empty_cache()
+    exact, fast = rows[torch.float32], rows[torch.bfloat16]
+    spread = exact.std(dim=1, keepdim=True)
+    assert torch.isfinite(fast).all()
+    rel = ((fast - exact).abs() / spread).max().item()
+    rms = ((fast - exact).square().mean(dim=1).sqrt() / spread[:, 0]).max().item()
+    print(f"\n[20,000 tokens] bfloat16 against float32: largest {rel:.4f}, rms {rms:.4f} of a row's spread")
+    assert rel <= BF16_TOL and rms <= BF16_RMS
+    picks = fast.argmax(dim=1)
+    assert ((exact.max(dim=1).values - exact.gather(1, picks[:, None])[:, 0]) <= NEAR_TIE).all()
+
+
 def test_float32_path_against_the_plain_implementation_at_real_widths(tmp_path):
     """Two layers of the 0.6B sizes from a model folder (the loader at real widths too)."""
     cfg = Qwen3Config(**{**SIZES["0.6b"], "num_hidden_layers": 2}, layer_types=("full_attention",) * 2)
