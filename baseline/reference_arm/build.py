@@ -102,7 +102,8 @@ def build(ref: Path, out: Path, jobs: int = 8) -> None:
 
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("--reference", default=os.environ.get("TLLM_REFERENCE", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("TLLM_REFERENCE", str(ROOT.parent / "reference")),
+                    help="the reference's source tree (default: $TLLM_REFERENCE, or a folder `reference` beside this repository)")
     ap.add_argument("--out", default=str(ROOT / "baseline" / "_ref"))
     ap.add_argument("--jobs", type=int, default=os.cpu_count() or 4)
     args = ap.parse_args()

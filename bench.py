@@ -11,6 +11,19 @@ the wall clock.  One JSON line is printed.  The sizes are those of Qwen3-8B
 (the benchmark configuration); every request stands at a context of about 4096 tokens while it decodes
 (the prompts are really prefilled, in portions of 2048 tokens, outside the timed region).
 
+Beside the headline, in ``points`` (flat, numbers only): decode at batch 1 and 64 at the same context;
+the reference's own benchmark workload (``p128_*``: 128-token prompts, 128 outputs, batch 1 / 8 / 64:
+the decode steps alone timed on the device with their share of the HBM peak, and output tokens per
+second end to end with the prompts inside the timed region, median of five runs after three
+warm-ups); the mixed continuous-batching run that goes with the Qwen3-0.6B sizes.  ``prefill`` is one
+prompt of 2048 tokens.  ``check``: the logits of the model that was timed, bfloat16 kernels against
+the float32 path under four ways of cutting; a mismatch ends the run with an error line and code 1.
+
+``--impl reference`` runs the unmodified reference (built by baseline/reference_arm/build.py into
+baseline/_ref/) on the same sizes and the same decode workload through its own LLMEngine, and its own
+``model_main --bench`` on the 128-token workload; it prints the same line with ``"impl": "reference"``,
+or ``{"impl": "reference", "unavailable": why}``.
+
 For more than one GPU this engine has nothing to run: it prints one line and exits 2.
 """
 import argparse
@@ -131,7 +144,7 @@ def _reference_binaries():
     if all(p.is_file() for p in need):
         return need, None
     import os
-    src = Path(os.environ.get("TLLM_REFERENCE", "/root/reference"))
+    src = Path(os.environ.get("TLLM_REFERENCE", str(ROOT.parent / "reference")))    # or a folder beside this one
     if not (src / "model" / "model_main.cpp").is_file():
         return None, (f"the reference is not built (no {REF_BIN}) and its sources are not at {src}: "
                       "run baseline/reference_arm/build.py where they are")

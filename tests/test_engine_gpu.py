@@ -173,6 +173,42 @@ def test_eos_stops_and_is_ignored_on_request(folders, tmp_path):
     assert llm.generate([p], SamplingParams(max_tokens=6, ignore_eos=True))[0].token_ids == ref
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_overlapped_scheduling_with_requests_that_end_early(folders, tmp_path, dtype):
+    """Requests that end on an end-of-sequence token have a row in the step launched before that was
+    known, and the step at which a waiting request is admitted moves with it, so the rows that share
+    a step (and with them, in bfloat16, the product kernel and the last bits) can differ between a
+    run with the overlap and one without.  In float32 the tokens are equal; in bfloat16 every token
+    of either run is the plain implementation's choice for its own prefix or within its margin, each
+    request ends on an end-of-sequence token or at its length, and no page is lost."""
+    from tiny_llm_infer_b200 import LLM, SamplingParams
+    cfg, w = plain.read_model(folders["B"])
+    prompts = [prompt(20 + i, n, cfg["vocab_size"]) for i, n in enumerate((5, 17, 33, 9, 40, 12))]
+    greedy = [plain.greedy(cfg, w, p, 10) for p in prompts]
+    eos = sorted({g[3] for g in greedy[:3]} | {greedy[4][6]})      # some requests stop after a few tokens
+    raw = json.loads((folders["B"] / "config.json").read_text())
+    raw["eos_token_id"] = eos
+    folder = tmp_path / "eos"
+    folder.mkdir()
+    (folder / "config.json").write_text(json.dumps(raw))
+    (folder / "model.safetensors").write_bytes((folders["B"] / "model.safetensors").read_bytes())
+    runs = []
+    for overlap in (True, False):
+        llm = LLM(str(folder), dtype=dtype, max_model_len=128, num_kv_blocks=24, block_size=8,
+                  max_num_batched_tokens=32, max_num_seqs=3, overlap_scheduling=overlap)
+        outs = llm.generate(prompts, SamplingParams(max_tokens=10))
+        runs.append([o.token_ids for o in outs])
+        llm.cache.audit()
+        assert llm.cache.free_pages() == {None: 24}
+        for p, toks in zip(prompts, runs[-1]):
+            assert 0 < len(toks) <= 10 and (len(toks) == 10 or toks[-1] in eos) and not set(toks[:-1]) & set(eos)
+            ok, info = teacher_forced_ok(cfg, w, p, toks, 1e-4 if dtype == "float32" else 0.08)
+            assert ok, info
+    assert any(len(t) < 10 for t in runs[0])
+    if dtype == "float32":
+        assert runs[0] == runs[1]
+
+
 def test_temperature_draws_do_not_depend_on_batching(folders):
     from tiny_llm_infer_b200 import LLM, SamplingParams
     cfg, w = plain.read_model(folders["B"])
