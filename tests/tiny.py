@@ -2,7 +2,8 @@
 width, heads and groups, head width, feed-forward width (200 is no multiple of 128),
 vocabulary, rope base, eps, tied or untied head, spread of the weights.  C adds sliding
 layers (window 24) between full ones, with sizes of its own.  D has a head width (64) and
-a page size (16) that the tensor-core attention kernels take, one full and one sliding layer."""
+a page size (16) that the tensor-core attention kernels take, one full and one sliding layer.  E has
+head width 128 (the tcgen05 prompt kernel); F has sizes that fit no fast path."""
 from __future__ import annotations
 
 import tempfile
@@ -44,7 +45,14 @@ TINY_E = dict(cfg=Qwen3Config(hidden_size=192, intermediate_size=328, num_hidden
                               tie_word_embeddings=False, sliding_window=150,
                               layer_types=(SLIDING, FULL)),
               seed=4, std=0.05, norm_range=(0.7, 1.3), page_size=32, lengths=(70, 300, 130, 41, 200, 35))
-TINIES = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
+# sizes that fit no fast path: a head width of 80, three query heads on one key/value head, a model width
+# and a feed-forward width that are no multiples of 16 (136, 100: gate and up stay stacked), an odd vocabulary
+TINY_F = dict(cfg=Qwen3Config(hidden_size=136, intermediate_size=100, num_hidden_layers=2,
+                              num_attention_heads=3, num_key_value_heads=1, head_dim=80, vocab_size=1001,
+                              max_position_embeddings=512, rms_norm_eps=2e-6, rope_theta=3e4,
+                              tie_word_embeddings=True, layer_types=(FULL,) * 2),
+              seed=5, std=0.07, norm_range=(0.6, 1.4), page_size=16, lengths=(70, 97, 41, 35))
+TINIES = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E, "F": TINY_F}
 
 
 def make_folder(tiny, folder=None, dtype=torch.bfloat16, shards=1) -> Path:
