@@ -117,3 +117,44 @@ def test_broken_containers(tmp_path):
     (folder / "model.safetensors").unlink()
     with pytest.raises(WeightsError, match="neither"):
         load_weights(folder, exp, torch.bfloat16, "cpu", ign)
+
+
+def test_random_tensors_do_not_depend_on_slabs_or_device_order():
+    """An element is a function of (seed, tensor name, its index): a tensor made whole, made as a flat
+    vector or cut out of a longer run of the same counters holds the same values; other seeds and names
+    hold others; the draws have the spread that was asked for."""
+    from tiny_llm_infer_b200.parts.spec import ParamSpec
+    from tiny_llm_infer_b200.weights import random_init as ri
+    a = ri.random_tensor("w.weight", ParamSpec((37, 91)), 5, 0.05, (0.5, 1.5), torch.float32, "cpu")
+    flat = ri.random_tensor("w.weight", ParamSpec((37 * 91,)), 5, 0.05, (0.5, 1.5), torch.float32, "cpu")
+    assert torch.equal(a.view(-1), flat)
+    key = ri._tensor_key(5, "w.weight")
+    for start, n in ((0, 10), (1, 9), (3, 100), (1000, 37 * 91 - 1000)):          # odd starts cut a pair in two
+        piece = (ri._normal(key, start, n, "cpu") * 0.05).to(torch.float32)
+        assert torch.equal(piece, flat[start:start + n])
+    assert not torch.equal(a, ri.random_tensor("w.weight", ParamSpec((37, 91)), 6, 0.05, (0.5, 1.5), torch.float32, "cpu"))
+    assert not torch.equal(a, ri.random_tensor("v.weight", ParamSpec((37, 91)), 5, 0.05, (0.5, 1.5), torch.float32, "cpu"))
+    big = ri.random_tensor("big", ParamSpec((400, 500)), 1, 0.05, (0.5, 1.5), torch.float32, "cpu")
+    assert abs(big.mean().item()) < 1e-3 and abs(big.std().item() - 0.05) < 1e-3 and big.abs().max() < 0.3
+    gains = ri.random_tensor("n.weight", ParamSpec((4096,), "norm"), 1, 0.05, (0.5, 1.5), torch.float32, "cpu")
+    assert 0.5 <= gains.min() and gains.max() <= 1.5 and abs(gains.mean().item() - 1.0) < 0.02
+    assert ri.random_tensor("t", ParamSpec((3,), "index"), 1, 0.05, (0.5, 1.5), torch.float32, "cpu").dtype == torch.int32
+
+
+@pytest.mark.gpu
+def test_a_model_filled_on_the_device_holds_the_folders_weights(tmp_path):
+    """``random_model`` (tensors made on the GPU, part by part) and a folder written on the host from
+    the same configuration and seed, read back through the loader, hold the same weights to the bit
+    (the generator is integer and float64 arithmetic that both run alike), in both storage types."""
+    from tiny_llm_infer_b200.engine import load_model, random_model
+    tiny = TINIES["B"]
+    folder = write_random_model(tmp_path / "m", tiny["cfg"], tiny["seed"], tiny["std"], tiny["norm_range"])
+    for dtype in (torch.bfloat16, torch.float32):
+        loaded, _ = load_model(folder, dtype, "cuda:0")
+        made = random_model(tiny["cfg"], tiny["seed"], dtype, "cuda:0", std=tiny["std"], norm_range=tiny["norm_range"])
+        for a, b in zip(loaded.parts(), made.parts()):
+            for name, value in vars(a).items():
+                if isinstance(value, torch.Tensor):
+                    assert torch.equal(value, getattr(b, name)), (type(a).__name__, name)
+        mixer_a, mixer_b = loaded.blocks[0].mixers()[0], made.blocks[0].mixers()[0]
+        assert torch.equal(mixer_a.w_qkv, mixer_b.w_qkv) and mixer_a.w_qkv.dtype == dtype
