@@ -76,7 +76,7 @@ def linear_swiglu(x, w_gate_up, out_dtype, interleaved=False):
 
 
 def qk_norm_rope_store(qkv, q_gain, k_gain, eps, inv_freq, rotary_dim, positions, token_slot,
-                       block_table, cache, page_size, q_out, q_heads, kv_heads, head_dim, flags):
+                       block_table, cache, page_size, q_out, q_heads, kv_heads, head_dim, flags, table=None):
     T = qkv.shape[0]
     x = qkv.float().view(T, q_heads + 2 * kv_heads, head_dim)
     q, k, v = x[:, :q_heads], x[:, q_heads:q_heads + kv_heads], x[:, q_heads + kv_heads:]

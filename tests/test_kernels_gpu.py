@@ -144,6 +144,62 @@ def test_qk_norm_rope_store(ops, dtype, nh, nkv, hd, rot):
         assert (cache_h[page, 1, :, off] - v[t]).abs().max() < tol(dtype, scale)
     untouched = cache_h.permute(0, 3, 1, 2, 4)[~touched]
     assert (untouched == 0).all()                        # nothing else was written
+    if rot == hd:
+        # with the step's table of cosines and sines instead of sincosf in the kernel: the same bits
+        rope_table = ops.rope_table(dev(positions), dev(inv_freq))
+        angle = positions.float()[:, None] * inv_freq[None, :]
+        assert torch.equal(rope_table[:, 0].cpu()[slot >= 0], torch.cos(angle)[slot >= 0]) or \
+            (rope_table[:, 0].cpu() - torch.cos(angle)).abs().max() < 1e-6
+        cache2 = torch.zeros_like(cache)
+        q_out2 = torch.full_like(q_out, 9.0)
+        ops.qk_norm_rope_store(dev(qkv), dev(qg), dev(kg), eps, dev(inv_freq), rot, dev(positions), dev(slot),
+                               dev(table), cache2, ps, q_out2, nh, nkv, hd, flags, table=rope_table)
+        assert torch.equal(q_out2, q_out) and torch.equal(cache2, cache)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd", [(7, 3, 128), (5, 2, 64), (3, 1, 256), (32, 8, 128)])
+def test_qk_norm_rope_store_with_many_tokens(ops, dtype, nh, nkv, hd):
+    """More than 64 tokens take the form in which a warp has six heads on their way: head counts that
+    fill neither a warp nor a round, every token at its own place, with and without the step's table."""
+    T, ps, eps, theta = 150, 16, 1e-6, 1e6
+    g = torch.Generator().manual_seed(21)
+    qkv = rnd(T, (nh + 2 * nkv) * hd, seed=16, scale=2.0).to(dtype)
+    qg = (rnd(hd, seed=17) * 0.3 + 1).to(dtype)
+    kg = (rnd(hd, seed=18) * 0.3 + 1).to(dtype)
+    slots, max_pages, pages = 3, 8, 30
+    slot = torch.randint(0, slots, (T,), generator=g).to(torch.int32)
+    slot[5] = slot[77] = -1
+    positions = torch.zeros(T, dtype=torch.int32)
+    for s in range(slots):                      # distinct positions inside a slot, in a scrambled order
+        mine = (slot == s).nonzero()[:, 0]
+        positions[mine] = torch.randperm(max_pages * ps, generator=g)[:len(mine)].to(torch.int32)
+    table = scrambled_tables(slots, max_pages, pages, seed=19)
+    inv_freq = (theta ** (-2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd)).float()
+    flags = ops.QK_NORM | ops.QK_ROPE | ops.QK_STORE | ops.QK_QOUT
+    x = qkv.double().view(T, nh + 2 * nkv, hd)
+    qn = plain.rotary_half(plain.rms_norm(x[:, :nh], qg.double(), eps), positions, theta)
+    kn = plain.rotary_half(plain.rms_norm(x[:, nh:nh + nkv], kg.double(), eps), positions, theta)
+    want = torch.zeros(pages, 2, nkv, ps, hd, dtype=torch.float64)
+    live = slot >= 0
+    for t in live.nonzero()[:, 0].tolist():
+        page, off = int(table[slot[t], positions[t] // ps]), int(positions[t] % ps)
+        want[page, 0, :, off], want[page, 1, :, off] = kn[t], x[t, nh + nkv:]
+    scale = max(qn.abs().max().item(), 1.0)
+    results = []
+    for with_table in (False, True):
+        cache = torch.zeros((pages, 2, nkv, ps, hd), dtype=dtype, device="cuda")
+        q_out = torch.full((T, nh * hd), 9.0, dtype=dtype, device="cuda")
+        rope_table = ops.rope_table(dev(positions), dev(inv_freq)) if with_table else None
+        ops.qk_norm_rope_store(dev(qkv), dev(qg), dev(kg), eps, dev(inv_freq), hd, dev(positions), dev(slot),
+                               dev(table), cache, ps, q_out, nh, nkv, hd, flags, table=rope_table)
+        q_h = q_out.cpu().double().view(T, nh, hd)
+        assert (q_h[live] - qn[live]).abs().max() < tol(dtype, scale)
+        assert (q_h[~live] == 9.0).all()
+        assert (cache.cpu().double() - want).abs().max() < tol(dtype, scale)
+        assert (cache.cpu()[want == 0] == 0).all()
+        results.append((q_out, cache))
+    assert torch.equal(results[0][0], results[1][0]) and torch.equal(results[0][1], results[1][1])
 
 
 def fill_cache(cache, table, slot, keys, vals, ps):

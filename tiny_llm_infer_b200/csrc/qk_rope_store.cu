@@ -138,10 +138,16 @@ template <> struct HeadVec8<float> {
     static __device__ __forceinline__ float inv_root(float x) { return 1.0f / sqrtf(x); }   // the 32-bit path: exact root and quotient
 };
 
-template <typename T, typename TG, int HD>
+// TABLE: the cosines and sines of the step's tokens come from `rope_table` ([tokens][2][HD / 2]
+// float32, made once per step by rope_table_kernel and shared by all layers) instead of being
+// computed here, which takes 64 sincosf, the shared memory and the barrier out of every block.
+// ROUNDS: how many heads a warp loads before it works on the first.  With many tokens a block of four
+// warps with six loads each in flight keeps more bytes on their way per SM than eight warps with three
+// (the kernel is bound by the latency of its loads, not by its instructions).
+template <typename T, typename TG, int HD, bool TABLE, int ROUNDS>
 __global__ void __launch_bounds__(256) qk_norm_rope_store_vec_kernel(
     T* qkv, const TG* __restrict__ q_gain, const TG* __restrict__ k_gain, float eps,
-    const float* __restrict__ inv_freq, const int* __restrict__ positions,
+    const float* __restrict__ inv_freq, const float* rope_table, const int* __restrict__ positions,
     const int* __restrict__ token_slot, const int* __restrict__ block_table, int max_pages,
     T* __restrict__ cache, int page_size, T* __restrict__ q_out, int q_heads, int kv_heads, int flags) {
     constexpr int HALF = HD / 2, LPH = HD / 8, HPW = 32 / LPH;   // lanes per head, heads per warp
@@ -161,7 +167,7 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_vec_kernel(
     // with many a warp takes several rounds of heads, and loads kRounds of them before it works on
     // the first, so that their latencies overlap.  The first loads are issued before the angles
     // are computed and before the page is looked up.
-    constexpr int kRounds = 3;
+    constexpr int kRounds = ROUNDS;
     const int stride = warps * HPW * gridDim.y;
     const int head0 = (blockIdx.y * warps + warp) * HPW + sub;
     typename HeadVec8<T>::Raw xs[kRounds];
@@ -173,8 +179,20 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_vec_kernel(
         }
     };
     load_heads(head0);
-    if (rope)
-        for (int i = threadIdx.x; i < HALF; i += blockDim.x) sincosf((float)pos * inv_freq[i], &sn[i], &cs[i]);
+    const bool low = l < LPH / 2;
+    float4 tc0, tc1, ts0, ts1;                        // TABLE: this lane's eight cosines and sines, on their way
+    if constexpr (TABLE) {
+        if (rope) {
+            const float* row_c = rope_table + (size_t)t * HD + (low ? e0 : e0 - HALF);
+            tc0 = *reinterpret_cast<const float4*>(row_c);
+            tc1 = *reinterpret_cast<const float4*>(row_c + 4);
+            ts0 = *reinterpret_cast<const float4*>(row_c + HALF);
+            ts1 = *reinterpret_cast<const float4*>(row_c + HALF + 4);
+        }
+    } else {
+        if (rope)
+            for (int i = threadIdx.x; i < HALF; i += blockDim.x) sincosf((float)pos * inv_freq[i], &sn[i], &cs[i]);
+    }
     float gq[8], gk[8];
     if (norm) {
 #pragma unroll
@@ -182,15 +200,19 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_vec_kernel(
     }
     int page = -1;
     if (flags & kFlagStore) page = block_table[(size_t)slot * max_pages + pos / page_size];
-    __syncthreads();
+    if constexpr (!TABLE) __syncthreads();
     // pair (i, i + HALF): x'_i = x_i cos a - x_{i+HALF} sin a; x'_{i+HALF} = x_i sin a + x_{i+HALF} cos a,
     // for both halves x' = x cos a + partner * (-+ sin a): cosines and signed sines of this lane's elements
-    const bool low = l < LPH / 2;
     float cc[8], sx[8];
     if (rope) {
         const int f0 = low ? e0 : e0 - HALF;
-        const float4 c0 = *reinterpret_cast<const float4*>(cs + f0), c1 = *reinterpret_cast<const float4*>(cs + f0 + 4);
-        const float4 s0 = *reinterpret_cast<const float4*>(sn + f0), s1 = *reinterpret_cast<const float4*>(sn + f0 + 4);
+        float4 c0, c1, s0, s1;
+        if constexpr (TABLE) {
+            c0 = tc0; c1 = tc1; s0 = ts0; s1 = ts1;
+        } else {
+            c0 = *reinterpret_cast<const float4*>(cs + f0); c1 = *reinterpret_cast<const float4*>(cs + f0 + 4);
+            s0 = *reinterpret_cast<const float4*>(sn + f0); s1 = *reinterpret_cast<const float4*>(sn + f0 + 4);
+        }
         cc[0] = c0.x; cc[1] = c0.y; cc[2] = c0.z; cc[3] = c0.w; cc[4] = c1.x; cc[5] = c1.y; cc[6] = c1.z; cc[7] = c1.w;
         sx[0] = s0.x; sx[1] = s0.y; sx[2] = s0.z; sx[3] = s0.w; sx[4] = s1.x; sx[5] = s1.y; sx[6] = s1.z; sx[7] = s1.w;
         if (low) {
@@ -245,15 +267,41 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_vec_kernel(
     }
 }
 
+// table[t][0][i] = cos(pos_t * inv_freq[i]), table[t][1][i] = sin(pos_t * inv_freq[i]), i < half: the
+// angle is the float32 product, as in the kernels above that compute it themselves.
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq, int half,
+                                  int tokens, float* __restrict__ table) {
+    TLLM_PDL_ENTER();
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= tokens * half) return;
+    const int t = idx / half, i = idx - t * half;
+    float s, c;
+    sincosf((float)positions[t] * inv_freq[i], &s, &c);
+    table[(size_t)t * 2 * half + i] = c;
+    table[(size_t)t * 2 * half + half + i] = s;
+}
+
 }  // namespace tllm
 
 using namespace tllm;
 
+extern "C" int tllm_rope_table(const int* positions, const float* inv_freq, int half, int tokens, float* table,
+                               cudaStream_t stream) {
+    TLLM_REQUIRE(tokens >= 0 && half > 0 && positions && inv_freq && table, "rope_table: bad arguments");
+    if (tokens == 0) return 0;
+    const long long n = (long long)tokens * half;
+    launch_pdl(kPdlOther, rope_table_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, positions, inv_freq,
+               half, tokens, table);
+    return finish_launch("rope_table");
+}
+
+// rope_table: optional, [tokens][2][head_dim / 2] float32 from tllm_rope_table for the same positions and
+// frequencies (used by the vector form when the whole head is rotated; ignored otherwise).
 extern "C" int tllm_qk_norm_rope_store(
     void* qkv, const void* q_gain, const void* k_gain, int gain_dtype, float eps,
     const float* inv_freq, int rotary_dim, const int* positions, const int* token_slot,
     const int* block_table, int max_pages, void* cache, int page_size, void* q_out, int dtype,
-    int tokens, int q_heads, int kv_heads, int head_dim, int flags, cudaStream_t stream) {
+    int tokens, int q_heads, int kv_heads, int head_dim, int flags, const float* rope_table, cudaStream_t stream) {
     TLLM_REQUIRE(tokens >= 0 && q_heads > 0 && kv_heads > 0, "qk_norm_rope_store: bad sizes");
     TLLM_REQUIRE(head_dim > 0 && head_dim <= kMaxHeadDim,
                  "qk_norm_rope_store: head_dim %d outside 1..%d", head_dim, kMaxHeadDim);
@@ -275,10 +323,19 @@ extern "C" int tllm_qk_norm_rope_store(
             const int vblock = 256;
             const int per_block = 8 * (32 / (head_dim / 8));           // heads a block takes in one round
             const int vgroups = tokens <= 64 ? (q_heads + 2 * kv_heads + per_block - 1) / per_block : 1;
-#define VLAUNCH(T, TG, HD)                                                                          \
-    launch_pdl(kPdlQk, qk_norm_rope_store_vec_kernel<T, TG, HD>, dim3(tokens, vgroups), dim3(vblock), 0, stream, \
-        (T*)qkv, (const TG*)q_gain, (const TG*)k_gain, eps, inv_freq, positions, token_slot,        \
+            const bool table = rope_table != nullptr && (flags & kFlagRope) && al(rope_table, 16);
+            const bool deep = tokens > 64;                                  // see ROUNDS above
+#define VLAUNCH1(T, TG, HD, TAB, ROUNDS, BLOCK)                                                     \
+    launch_pdl(kPdlQk, qk_norm_rope_store_vec_kernel<T, TG, HD, TAB, ROUNDS>, dim3(tokens, vgroups), dim3(BLOCK), 0, stream, \
+        (T*)qkv, (const TG*)q_gain, (const TG*)k_gain, eps, inv_freq, rope_table, positions, token_slot, \
         block_table, max_pages, (T*)cache, page_size, (T*)q_out, q_heads, kv_heads, flags)
+#define VLAUNCH(T, TG, HD)                                                                          \
+    do {                                                                                            \
+        if (table && deep) VLAUNCH1(T, TG, HD, true, 6, 128);                                       \
+        else if (table) VLAUNCH1(T, TG, HD, true, 3, vblock);                                       \
+        else if (deep) VLAUNCH1(T, TG, HD, false, 6, 128);                                          \
+        else VLAUNCH1(T, TG, HD, false, 3, vblock);                                                 \
+    } while (0)
 #define VDISPATCH(T, TG)                                              \
     do {                                                              \
         if (head_dim == 64) VLAUNCH(T, TG, 64);                       \
@@ -292,6 +349,7 @@ extern "C" int tllm_qk_norm_rope_store(
             }
 #undef VDISPATCH
 #undef VLAUNCH
+#undef VLAUNCH1
             return finish_launch("qk_norm_rope_store");
         }
     }

@@ -59,4 +59,8 @@ class StepContext:
     decode_only: bool = False
     max_context: int = 0          # largest position + 1 among the rows
     max_segment: int = 0          # longest segment
-    extras: dict = field(default_factory=dict)
+    extras: dict = field(default_factory=dict)   # further inputs of the step that some part may need (nobody fills it today)
+    # what parts have made for this forward pass and share (the rotary table of the step's positions);
+    # emptied by the model at the start of every forward pass, so that a pass recorded as a CUDA graph
+    # records the making too
+    memo: dict = field(default_factory=dict)

@@ -114,6 +114,8 @@ class Model:
     def forward(self, ctx, caches) -> torch.Tensor:
         """Logits [len(ctx.want_rows), vocab] float32.  ``caches.view(cache_id, writes)``
         gives the ``LayerCacheView`` of a visit's mixer (a list of them for a block with several)."""
+        if hasattr(ctx, "memo"):
+            ctx.memo.clear()
         h = self.embedding.forward(ctx.token_ids)
         pending = None
         for layer, cache_ids, writes in self.order:

@@ -67,7 +67,8 @@ def _declare(h) -> None:
         "tllm_cast": [vp, i32, vp, i32, i64, vp],
         "tllm_feed_tokens": [vp, vp, vp, vp, i32, vp],
         "tllm_qk_norm_rope_store": [vp, vp, vp, i32, f32, vp, i32, vp, vp, vp, i32, vp, i32, vp,
-                                    i32, i32, i32, i32, i32, i32, vp],
+                                    i32, i32, i32, i32, i32, i32, vp, vp],
+        "tllm_rope_table": [vp, vp, i32, i32, vp, vp],
         "tllm_paged_attention_general": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32,
                                          i32, f32, vp, vp],
         "tllm_sample": [vp, i32, i32, i64, vp, vp, vp, vp],
@@ -195,15 +196,29 @@ def feed_tokens(ids: torch.Tensor, places: torch.Tensor, rows: torch.Tensor, sam
     _check(lib().tllm_feed_tokens(_p(ids), _p(places), _p(rows), _p(sampled), places.numel(), _stream()), "feed_tokens")
 
 
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """[tokens, 2, half] float32: cosines and sines of position * inv_freq (the float32 product), made
+    once per step and read by every layer's ``qk_norm_rope_store``."""
+    _cuda(positions, inv_freq)
+    assert positions.dtype == torch.int32 and inv_freq.dtype == torch.float32
+    tokens, half = positions.numel(), inv_freq.numel()
+    table = torch.empty((tokens, 2, half), dtype=torch.float32, device=positions.device)
+    _check(lib().tllm_rope_table(_p(positions), _p(inv_freq), half, tokens, _p(table), _stream()), "rope_table")
+    return table
+
+
 def qk_norm_rope_store(qkv: torch.Tensor, q_gain, k_gain, eps: float, inv_freq, rotary_dim: int,
                        positions: torch.Tensor, token_slot: torch.Tensor, block_table, cache,
                        page_size: int, q_out, q_heads: int, kv_heads: int, head_dim: int,
-                       flags: int) -> None:
+                       flags: int, table: Optional[torch.Tensor] = None) -> None:
     """One pass over the fused q|k|v rows [T, (q_heads + 2 kv_heads) * head_dim]: per-head
     RMSNorm of q and k (QK_NORM), rotate-half rotation (QK_ROPE), write of k and v into
     their page (QK_STORE), write of q to ``q_out`` (QK_QOUT), write of the processed k back
-    in place (QK_KVOUT).  Rows whose token_slot is negative are skipped."""
-    _cuda(qkv, q_gain, k_gain, inv_freq, positions, token_slot, block_table, cache, q_out)
+    in place (QK_KVOUT).  Rows whose token_slot is negative are skipped.  ``table``: the step's
+    ``rope_table`` for these positions and frequencies (same values, no sincosf per layer)."""
+    _cuda(qkv, q_gain, k_gain, inv_freq, positions, token_slot, block_table, cache, q_out, table)
+    if table is not None:
+        assert table.dtype == torch.float32 and tuple(table.shape) == (qkv.shape[0], 2, rotary_dim // 2)
     tokens = qkv.shape[0]
     assert qkv.shape[1] == (q_heads + 2 * kv_heads) * head_dim
     gain_dt = _dt(q_gain) if q_gain is not None else F32
@@ -213,7 +228,7 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_gain, k_gain, eps: float, inv_freq, 
     _check(lib().tllm_qk_norm_rope_store(
         _p(qkv), _p(q_gain), _p(k_gain), gain_dt, float(eps), _p(inv_freq), rotary_dim,
         _p(positions), _p(token_slot), _p(block_table), max_pages, _p(cache), page_size, _p(q_out),
-        _dt(qkv), tokens, q_heads, kv_heads, head_dim, flags, _stream()), "qk_norm_rope_store")
+        _dt(qkv), tokens, q_heads, kv_heads, head_dim, flags, _p(table), _stream()), "qk_norm_rope_store")
 
 
 _workspaces = {}

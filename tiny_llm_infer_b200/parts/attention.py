@@ -94,8 +94,11 @@ class GroupedQueryAttention:
         if self.position is None or fused is not None:
             inv_freq, rotary_dim = fused if fused is not None else (None, 0)
             rope = ops.QK_ROPE if fused is not None else 0
+            table = None
+            if fused is not None and rotary_dim == self.head_dim and hasattr(self.position, "step_table"):
+                table = self.position.step_table(ctx)          # cosines and sines once per step, not per layer
             ops.qk_norm_rope_store(qkv, self.q_gain, self.k_gain, eps, inv_freq, rotary_dim,
-                                   flags=norm | rope | store | ops.QK_QOUT, **args)
+                                   flags=norm | rope | store | ops.QK_QOUT, table=table, **args)
         else:
             # a position encoding the kernel does not know: norm, let the part rotate, then store
             ops.qk_norm_rope_store(qkv, self.q_gain, self.k_gain, eps, None, 0,

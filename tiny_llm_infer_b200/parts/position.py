@@ -6,8 +6,9 @@ x'_i = x_i cos a - x_{i+d/2} sin a,  x'_{i+d/2} = x_i sin a + x_{i+d/2} cos a
 (reference: kernels/src/rope_kernel_cpu.cpp:127-141 for the table,
 kernels/src/rope_kernel_cuda.cu:228-261 for the rotation; it always rotates the whole
 head).  The frequencies are computed once on the host in float64 and rounded to
-float32; the angle, sine and cosine are computed per token in the attention kernel, so
-there is no table whose length bounds the context.
+float32; the angle, sine and cosine are computed per token of the step, once per step for
+all layers with the same frequencies (``step_table``), so there is no table whose length
+bounds the context.
 """
 from __future__ import annotations
 
@@ -42,3 +43,15 @@ class RotaryHalf:
 
     def fused_rotary(self) -> Tuple[torch.Tensor, int]:
         return self.inv_freq, self.rotary_dim
+
+    def step_table(self, ctx) -> Optional[torch.Tensor]:
+        """Cosines and sines of this step's positions, [tokens, 2, rotary_dim / 2] float32, made by the
+        first layer of the step that asks and kept in the step's context for the others."""
+        memo = getattr(ctx, "memo", None)
+        if memo is None or not self.inv_freq.is_cuda:
+            return None
+        key = ("rotary_half", self.theta, self.rotary_dim)
+        table = memo.get(key)
+        if table is None:
+            table = memo[key] = ops.rope_table(ctx.positions, self.inv_freq)
+        return table
