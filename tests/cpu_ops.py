@@ -7,7 +7,6 @@ signatures.  They are test doubles, not a fallback: nothing in the package impor
 """
 from __future__ import annotations
 
-import math
 
 import torch
 

@@ -1,7 +1,6 @@
 """The engine's host side (LLM entry point, scheduler, sampler keys, toy parts) with the
 CUDA kernels swapped for torch stand-ins."""
 import pytest
-import torch
 
 import plain_qwen3 as plain
 from tiny import TINIES, make_folder, prompt

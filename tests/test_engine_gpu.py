@@ -4,14 +4,12 @@ temperature sampling that does not depend on batching, and the generality of the
 a toy mixer with state of its own and a run order that names a layer twice and lets a
 layer read another layer's cache, all registered from this file."""
 import json
-from pathlib import Path
 
-import numpy as np
 import pytest
 import torch
 
 import plain_qwen3 as plain
-from tiny import TINIES, make_folder, prompt, sharpen
+from tiny import TINIES, make_folder, prompt
 
 pytestmark = pytest.mark.gpu
 

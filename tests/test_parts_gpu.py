@@ -2,7 +2,6 @@
 it: norm, position encoding, attention mixer (through a cache of its own, in two portions),
 feed-forward, the block arrangement, embedding and head.  Sizes differ from the tiny
 models'."""
-import math
 
 import pytest
 import torch

@@ -7,7 +7,6 @@ import io
 import sys
 from pathlib import Path
 
-import numpy as np
 import pytest
 import torch
 

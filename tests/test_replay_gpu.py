@@ -19,7 +19,6 @@ from pathlib import Path
 
 import numpy as np
 import pytest
-import torch
 
 import plain_qwen3 as plain
 import replay

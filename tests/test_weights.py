@@ -1,6 +1,5 @@
 """Weights by tensor name: container, storage rule, the one error that lists everything,
 random-weights mode."""
-import json
 
 import pytest
 import torch

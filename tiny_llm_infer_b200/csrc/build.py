@@ -16,7 +16,7 @@ import sys
 import tempfile
 import time
 from pathlib import Path
-from typing import List, Optional
+from typing import List
 
 CSRC = Path(__file__).resolve().parent
 LIB_NAME = "libtllm_kernels.so"

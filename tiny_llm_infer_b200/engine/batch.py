@@ -10,7 +10,7 @@ given back.  Rows of one entry are consecutive with consecutive positions (a seg
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Hashable, List, Optional, Sequence
+from typing import Hashable, List, Optional, Sequence
 
 import torch
 

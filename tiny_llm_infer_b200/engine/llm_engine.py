@@ -11,7 +11,6 @@ through a ``tokenizers`` tokenizer.
 from __future__ import annotations
 
 import threading
-import time
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence as Seq, Union
 
@@ -22,7 +21,7 @@ from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler, draw_key
 from .batch import StepEntry
 from .runner import DTYPES, ModelRunner, PreparedStep, load_model
-from .scheduler import BatchPlan, Scheduler, SchedulerConfig, Sequence, Status
+from .scheduler import BatchPlan, Scheduler, SchedulerConfig, Sequence
 
 
 @dataclass

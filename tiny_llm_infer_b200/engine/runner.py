@@ -13,8 +13,7 @@ from __future__ import annotations
 import contextlib
 from dataclasses import dataclass
 
-from pathlib import Path
-from typing import Dict, Hashable, List, Optional, Sequence, Tuple
+from typing import Hashable, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -25,7 +24,6 @@ from ..cache.manager import CacheManager
 from ..config.base import ModelConfig, describe_model, load_config
 from ..models.model import Model, expected_tensors
 from ..weights.loader import load_weights
-from ..weights.random_init import random_tensors
 from .batch import Segment, StepContext, StepEntry
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,

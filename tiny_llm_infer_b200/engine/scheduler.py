@@ -32,7 +32,7 @@ from __future__ import annotations
 import enum
 from collections import deque
 from dataclasses import dataclass, field
-from typing import Callable, Deque, Hashable, List, Optional, Sequence as Seq
+from typing import Callable, Deque, List, Optional, Sequence as Seq
 
 from ..sampling.params import SamplingParams
 

@@ -14,7 +14,7 @@ reference, which has full attention only.
 from __future__ import annotations
 
 import math
-from typing import Any, Dict, Optional
+from typing import Dict, Optional
 
 import torch
 

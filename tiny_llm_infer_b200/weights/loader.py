@@ -14,8 +14,7 @@ business of the part that owns them.
 """
 from __future__ import annotations
 
-from pathlib import Path
-from typing import Dict, Iterable, List, Optional, Tuple
+from typing import Dict, Iterable, Optional
 
 import torch
 
