@@ -69,11 +69,11 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 // chains of products are resident and fetching long before their turn (norm + q/k + SwiGLU +
 // combine: 4.93 ms).  So the default is none; the environment variable TLLM_PDL holds the sum of
 // the classes to switch on, for measurements.  All kernels still let their successor start early.
-enum PdlClass { kPdlNorm = 1, kPdlQk = 2, kPdlSwiglu = 4, kPdlAttention = 8, kPdlCombine = 16, kPdlOther = 32 };
+enum PdlClass { kPdlNorm = 1, kPdlQk = 2, kPdlSwiglu = 4, kPdlAttention = 8, kPdlCombine = 16, kPdlOther = 32, kPdlAlways = 1 << 20 };
 
 inline bool pdl_enabled(int cls) {
     static const int mask = [] { const char* v = getenv("TLLM_PDL"); return v != nullptr ? atoi(v) : 0; }();
-    return (mask & cls) != 0;
+    return cls == kPdlAlways || (mask & cls) != 0;
 }
 
 template <typename... KArgs, typename... Args>
