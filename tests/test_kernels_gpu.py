@@ -78,6 +78,28 @@ def test_add_rmsnorm(ops, dtype, width, eps):
     assert torch.equal(h2.cpu(), h)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [1024, 4096, 5120, 1000])
+def test_add_rmsnorm_of_many_rows_is_that_of_few(ops, dtype, width):
+    """Thousands of rows in one launch give to the bit what the same rows give a few at a time (a
+    token's logits must not depend on how many tokens share its step), with and without a delta."""
+    T, eps = 2500, 1e-6
+    h = rnd(T, width, seed=12, scale=3.0).float()
+    delta = rnd(T, width, seed=13).to(dtype)
+    gain = (rnd(width, seed=14) * 0.2 + 1).to(dtype)
+    for with_delta in (True, False):
+        h_all, out_all = dev(h), torch.empty((T, width), dtype=dtype, device="cuda")
+        ops.add_rmsnorm(h_all, dev(delta) if with_delta else None, dev(gain), eps, out_all)
+        h_few, out_few = dev(h), torch.empty((T, width), dtype=dtype, device="cuda")
+        for a in range(0, T, 500):
+            ops.add_rmsnorm(h_few[a:a + 500], dev(delta[a:a + 500]) if with_delta else None, dev(gain), eps, out_few[a:a + 500])
+        assert torch.equal(out_all, out_few) and torch.equal(h_all, h_few)
+        v = h.double() + (delta.double() if with_delta else 0)
+        want = gain.double() * v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps)
+        assert (out_all.cpu().double() - want).abs().max() < tol(dtype, want.abs().max().item())
+        assert torch.equal(h_all.cpu(), v.float()) or (h_all.cpu().double() - v).abs().max() < 1e-5
+
+
 def interleaved_columns(t):
     """[rows, 2 I] with gate columns first, up columns after -> gate and up interleaved by eight."""
     rows, two_i = t.shape
