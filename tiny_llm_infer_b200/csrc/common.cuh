@@ -67,12 +67,15 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 // short kernels between them an ordinary launch is as fast or faster (norm 4.17 ms, q/k 4.17,
 // SwiGLU 4.22, attention 4.22, combine 4.24), and when several classes start early at once whole
 // chains of products are resident and fetching long before their turn (norm + q/k + SwiGLU +
-// combine: 4.93 ms).  So the default is none; the environment variable TLLM_PDL holds the sum of
-// the classes to switch on, for measurements.  All kernels still let their successor start early.
+// combine: 4.93 ms).  A later measurement, three runs each way on one GPU, found the residual add + norm
+// to gain a little after all (batch 8: 4.086 to 4.052 ms, batch 1: 3.33 to 3.32, batch 64: 9.59 to
+// 9.58), so that class is on by default and the others are off; the environment variable TLLM_PDL
+// holds the sum of the classes to switch on instead, for measurements.  All kernels still let their
+// successor start early.
 enum PdlClass { kPdlNorm = 1, kPdlQk = 2, kPdlSwiglu = 4, kPdlAttention = 8, kPdlCombine = 16, kPdlOther = 32, kPdlAlways = 1 << 20 };
 
 inline bool pdl_enabled(int cls) {
-    static const int mask = [] { const char* v = getenv("TLLM_PDL"); return v != nullptr ? atoi(v) : 0; }();
+    static const int mask = [] { const char* v = getenv("TLLM_PDL"); return v != nullptr ? atoi(v) : (int)kPdlNorm; }();
     return cls == kPdlAlways || (mask & cls) != 0;
 }
 
