@@ -289,14 +289,8 @@ static int launch_decode(const void* q, const void* cache, const int* positions,
     // it still runs and has its first keys and values on their way when that one ends (a decode step of
     // Qwen3-8B sizes at batch 1: 3.33 instead of 3.38 ms); with more blocks than that the early ones
     // are in the way of the kernel before (batch 8: 4.12 instead of 4.08 ms).
-    static int sm_count[OncePerDevice::kMax] = {};
-    int device = 0;
-    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= OncePerDevice::kMax) device = -1;
-    if (device >= 0 && sm_count[device] == 0 &&
-        cudaDeviceGetAttribute(&sm_count[device], cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
-        sm_count[device] = 0;
     const long long blocks = (long long)splits * kv_heads * n_rows;
-    const int cls = device >= 0 && blocks <= sm_count[device] ? kPdlAlways : kPdlAttention;
+    const int cls = blocks <= sm_count_cached() ? kPdlAlways : kPdlAttention;
     launch_pdl(cls, paged_attention_decode_kernel<HD>, grid, dim3(kDecWarps * 32), smem, stream,
         (const bf16*)q, (const bf16*)cache, positions, token_slot, rows, block_table, max_pages, page_size,
         q_heads, kv_heads, window, scale * 1.4426950408889634f, splits, part_o, part_ml, (bf16*)out);

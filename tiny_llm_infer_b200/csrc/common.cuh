@@ -110,6 +110,17 @@ struct OncePerDevice {
     void done() { if (device >= 0) seen[device] = true; }
 };
 
+// Multiprocessors of the current device (0 if that cannot be told), looked up once per device.
+inline int sm_count_cached() {
+    static int count[OncePerDevice::kMax] = {};
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= OncePerDevice::kMax) return 0;
+    if (count[device] == 0 &&
+        cudaDeviceGetAttribute(&count[device], cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
+        count[device] = 0;
+    return count[device];
+}
+
 // Host side: the last error text of this thread's most recent failing entry point.
 void set_error(const char* fmt, ...);
 

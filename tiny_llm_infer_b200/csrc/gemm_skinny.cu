@@ -81,7 +81,7 @@ __device__ __noinline__ void skinny_epilogue(float (*red)[16][NT * 8 + 1], TOut*
 // that belong to them as its lower half, so that a gate sum and its up sum meet in one thread's
 // accumulator; it writes silu(gate) * up: y is [M, N].  The grid, the bytes per block, the memory
 // pattern and the registers are those of the plain product of the 2 N rows.
-template <int NT, typename TOut, bool SWIGLU>
+template <int NT, typename TOut, bool SWIGLU, int STAGES>
 __global__ void __launch_bounds__(kSkinnyWarps * 32)
 skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, TOut* y, int M, int N, int K) {
     __shared__ float red[kSkinnyWarps][16][NT * 8 + 1];
@@ -143,22 +143,21 @@ skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, TOut* y, int M, in
         }
     };
 
-    SkinnyStage<NT> s0, s1, s2;
-    load_w(s0, kb0);                                         // weights depend on no earlier kernel
-    load_w(s1, kb0 + kSkinnyUnroll);
+    // STAGES - 1 stages are on their way while one is multiplied
+    SkinnyStage<NT> st[STAGES];
+#pragma unroll
+    for (int i = 0; i < STAGES - 1; ++i) load_w(st[i], kb0 + i * kSkinnyUnroll);   // weights depend on no earlier kernel
     asm volatile("griddepcontrol.wait;\n" ::: "memory");     // from here on x may be read, y written
-    load_x(s0, kb0);
-    load_x(s1, kb0 + kSkinnyUnroll);
-    for (int kb = kb0; kb < kb1; kb += 3 * kSkinnyUnroll) {
-        load_w(s2, kb + 2 * kSkinnyUnroll);
-        load_x(s2, kb + 2 * kSkinnyUnroll);
-        multiply(s0);
-        load_w(s0, kb + 3 * kSkinnyUnroll);
-        load_x(s0, kb + 3 * kSkinnyUnroll);
-        multiply(s1);
-        load_w(s1, kb + 4 * kSkinnyUnroll);
-        load_x(s1, kb + 4 * kSkinnyUnroll);
-        multiply(s2);
+#pragma unroll
+    for (int i = 0; i < STAGES - 1; ++i) load_x(st[i], kb0 + i * kSkinnyUnroll);
+    for (int kb = kb0; kb < kb1; kb += STAGES * kSkinnyUnroll) {
+#pragma unroll
+        for (int i = 0; i < STAGES; ++i) {
+            constexpr int kLast = STAGES - 1;
+            load_w(st[(i + kLast) % STAGES], kb + (i + kLast) * kSkinnyUnroll);
+            load_x(st[(i + kLast) % STAGES], kb + (i + kLast) * kSkinnyUnroll);
+            multiply(st[i]);
+        }
     }
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
@@ -171,7 +170,7 @@ skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, TOut* y, int M, in
     skinny_epilogue<NT, TOut, SWIGLU>(red, y, M, N, r0);
 }
 
-template <int NT, typename TOut, bool SWIGLU>
+template <int NT, typename TOut, bool SWIGLU, int STAGES = 3>
 static int launch_skinny(const void* x, const void* w, void* y, int M, int N, int K, cudaStream_t stream) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(SWIGLU ? (N + 7) / 8 : (N + 15) / 16);
@@ -183,7 +182,7 @@ static int launch_skinny(const void* x, const void* w, void* y, int M, int N, in
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<NT, TOut, SWIGLU>, (const bf16*)x, (const bf16*)w,
+    cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<NT, TOut, SWIGLU, STAGES>, (const bf16*)x, (const bf16*)w,
                                        (TOut*)y, M, N, K);
     if (e != cudaSuccess) {
         set_error("gemm_skinny: %s", cudaGetErrorString(e));
@@ -208,6 +207,18 @@ extern "C" int tllm_gemm_skinny(const void* x, const void* w, void* y, int out_d
     TLLM_REQUIRE(out_dtype == kBF16 || out_dtype == kF32, "gemm_skinny: unknown output dtype");
     if (M == 0) return 0;
     if (out_dtype == kBF16) {
+        // A grid that leaves room on the GPU takes its registers for a deeper pipeline instead (the
+        // kernel of three stages holds three blocks per SM, of four two, of six one): alone, the o and
+        // down products of Qwen3-8B sizes (256 blocks) 8.4 to 7.9 and 20.0 to 18.6 us with four stages,
+        // those of Qwen3-0.6B sizes (64 blocks) 3.8 to 2.7 and 4.5 to 3.5 us with six.  With more blocks
+        // than places (320 blocks of Qwen3-32B sizes on 296) four stages take 14 us instead of 10, and a
+        // warp with four k-blocks or fewer to walk (K = 1024) has nothing to put into them.
+        if (M <= 8) {
+            const int sms = sm_count_cached();
+            const long long blocks = ((long long)N + 15) / 16;
+            if (blocks <= sms && K >= 2048) return launch_skinny<1, bf16, false, 6>(x, w, y, M, N, K, stream);
+            if (blocks <= 2ll * sms && K >= 4096) return launch_skinny<1, bf16, false, 4>(x, w, y, M, N, K, stream);
+        }
         if (M <= 8) return launch_skinny<1, bf16, false>(x, w, y, M, N, K, stream);
         if (M <= 16) return launch_skinny<2, bf16, false>(x, w, y, M, N, K, stream);
         return launch_skinny<4, bf16, false>(x, w, y, M, N, K, stream);
